@@ -1,0 +1,181 @@
+// Host launchers for the tcgen05 grouped GEMM template (gemm.cuh) and tensor-map creation.
+#include <cudaTypedefs.h>
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "gemm.cuh"
+#include "kernels.h"
+
+namespace wm {
+
+// ------------------------------------------------------------------ error text (thread local)
+static thread_local char g_error[512] = "";
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+const char* last_error() { return g_error; }
+
+// ------------------------------------------------------------------ tensor maps
+static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  });
+  return fn;
+}
+
+int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
+                 uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  auto fn = encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+    return 3;
+  }
+  if (box_inner * elem_bytes != 128 || box_outer > 256 || (row_stride_bytes % 16) ||
+      (reinterpret_cast<uintptr_t>(base) % 16)) {
+    set_error("tensor map: box %ux%u / stride %llu / base %p violate TMA rules", box_inner,
+              box_outer, (unsigned long long)row_stride_bytes, base);
+    return 2;
+  }
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+                  2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (inner %llu outer %llu)", (int)r,
+              (unsigned long long)inner, (unsigned long long)outer);
+    return 3;
+  }
+  return 0;
+}
+
+// ------------------------------------------------------------------ launch helper
+template <int BLOCK_N, bool A_MN, bool B_MN, bool GATE_UP, bool K_GROUPED, class Epi>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, const Epi& epi,
+                  int sms, cudaStream_t stream) {
+  auto kernel = gemm_kernel<BLOCK_N, A_MN, B_MN, GATE_UP, K_GROUPED, Epi>;
+  constexpr int smem = GemmSmem<BLOCK_N>::kTotal;
+  static bool configured = false;  // one flag per template instantiation
+  if (!configured) {
+    WM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  kernel<<<sms, kGemmThreads, smem, stream>>>(ta, tb, args, epi);
+  WM_CUDA(cudaGetLastError());
+  return 0;
+}
+
+static GemmArgs base_args(const Schedule& s, int* status) {
+  GemmArgs a{};
+  a.num_m_tiles = s.num_m_tiles;
+  a.tile_group = s.tile_group;
+  a.group_row_start = s.group_row_start;
+  a.groups = s.groups;
+  a.status = status;
+  return a;
+}
+
+int launch_fc1(const Schedule& s, const __nv_bfloat16* x, const __nv_bfloat16* w1, __nv_bfloat16* u,
+               __nv_bfloat16* ab, const float* row_prob, int hidden, int inter, int* status,
+               int sms, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap_2d(&ta, x, 2, hidden, s.row_capacity, (uint64_t)hidden * 2, 64, 128)) return rc;
+  if (int rc = make_tmap_2d(&tb, w1, 2, hidden, (uint64_t)s.groups * 2 * inter, (uint64_t)hidden * 2, 64, 128))
+    return rc;
+  GemmArgs a = base_args(s, status);
+  a.n_tiles = inter / 128;
+  a.k_total = hidden;
+  a.b_group_rows = 2 * inter;
+  a.gate_up_half = inter;
+  EpilogueSwiglu epi{u, ab, row_prob, inter};
+  return launch<256, false, false, true, false>(ta, tb, a, epi, sms, stream);
+}
+
+template <bool B_MN>
+static int launch_mgrouped(const Schedule& s, const __nv_bfloat16* a_ptr, const __nv_bfloat16* b_ptr,
+                           __nv_bfloat16* out, const PushTarget* push, int n, int k, int* status,
+                           int sms, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap_2d(&ta, a_ptr, 2, k, s.row_capacity, (uint64_t)k * 2, 64, 128)) return rc;
+  const int bn = (n % 256 == 0) ? 256 : 128;
+  if (n % 128) {
+    set_error("grouped GEMM needs N %% 128 == 0, got %d", n);
+    return 2;
+  }
+  if (B_MN) {
+    if (int rc = make_tmap_2d(&tb, b_ptr, 2, n, (uint64_t)s.groups * k, (uint64_t)n * 2, 64, 64)) return rc;
+  } else {
+    if (int rc = make_tmap_2d(&tb, b_ptr, 2, k, (uint64_t)s.groups * n, (uint64_t)k * 2, 64, bn)) return rc;
+  }
+  GemmArgs a = base_args(s, status);
+  a.n_tiles = n / bn;
+  a.k_total = k;
+  a.b_group_rows = B_MN ? k : n;
+  if (push) {
+    if (bn == 256) {
+      EpiloguePush<256> epi{};
+      for (int r = 0; r < kMaxPeers; ++r) epi.mailbox[r] = push->mailbox[r];
+      epi.origin = push->origin; epi.cap = push->cap; epi.top_k = push->top_k; epi.ld = n;
+      return launch<256, false, B_MN, false, false>(ta, tb, a, epi, sms, stream);
+    }
+    EpiloguePush<128> epi{};
+    for (int r = 0; r < kMaxPeers; ++r) epi.mailbox[r] = push->mailbox[r];
+    epi.origin = push->origin; epi.cap = push->cap; epi.top_k = push->top_k; epi.ld = n;
+    return launch<128, false, B_MN, false, false>(ta, tb, a, epi, sms, stream);
+  }
+  if (bn == 256) {
+    EpilogueStore<256> epi{out, 0, n};
+    return launch<256, false, B_MN, false, false>(ta, tb, a, epi, sms, stream);
+  }
+  EpilogueStore<128> epi{out, 0, n};
+  return launch<128, false, B_MN, false, false>(ta, tb, a, epi, sms, stream);
+}
+
+int launch_mgrouped_nt(const Schedule& s, const __nv_bfloat16* a, const __nv_bfloat16* b,
+                       __nv_bfloat16* out, const PushTarget* push, int n, int k, int* status,
+                       int sms, cudaStream_t stream) {
+  return launch_mgrouped<false>(s, a, b, out, push, n, k, status, sms, stream);
+}
+int launch_mgrouped_nn(const Schedule& s, const __nv_bfloat16* a, const __nv_bfloat16* b,
+                       __nv_bfloat16* out, const PushTarget* push, int n, int k, int* status,
+                       int sms, cudaStream_t stream) {
+  return launch_mgrouped<true>(s, a, b, out, push, n, k, status, sms, stream);
+}
+
+int launch_kgrouped_tn(const Schedule& s, const __nv_bfloat16* a_ptr, const __nv_bfloat16* b_ptr,
+                       __nv_bfloat16* out, int m, int n, int* status, int sms,
+                       cudaStream_t stream) {
+  if (m % 128 || n % 128) {
+    set_error("K-grouped GEMM needs M %% 128 == 0 and N %% 128 == 0, got %d x %d", m, n);
+    return 2;
+  }
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap_2d(&ta, a_ptr, 2, m, s.row_capacity, (uint64_t)m * 2, 64, 64)) return rc;
+  if (int rc = make_tmap_2d(&tb, b_ptr, 2, n, s.row_capacity, (uint64_t)n * 2, 64, 64)) return rc;
+  const int bn = (n % 256 == 0) ? 256 : 128;
+  GemmArgs a = base_args(s, status);
+  a.m_tiles_per_group = m / 128;
+  a.n_tiles = n / bn;
+  if (bn == 256) {
+    EpilogueStore<256> epi{out, (long long)m * n, n};
+    return launch<256, true, true, false, true>(ta, tb, a, epi, sms, stream);
+  }
+  EpilogueStore<128> epi{out, (long long)m * n, n};
+  return launch<128, true, true, false, true>(ta, tb, a, epi, sms, stream);
+}
+
+}  // namespace wm

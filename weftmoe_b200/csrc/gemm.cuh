@@ -1,0 +1,389 @@
+// Persistent grouped GEMM for sm_100a: TMA -> shared-memory ring -> tcgen05.mma -> TMEM -> epilogue.
+//
+// One kernel template serves the six contractions of the routed-MoE layer
+// (reference dataflow: weftmoe/blackwell_backward.py:192-249 and
+// src/cuda/blackwell/fused/impls/routed_bf16.cuh:620-1139):
+//
+//   M-grouped (rows of one 128-row tile all belong to one expert):
+//     FC1  AB = X  * W1[e]^T   A K-major, B K-major, gate/up pair tile, SwiGLU epilogue
+//     FC2  Y  = U  * W2[e]^T   A K-major, B K-major
+//     dU   dU = dY * W2[e]     A K-major, B MN-major
+//     dX   dX = dAB* W1[e]     A K-major, B MN-major
+//   K-grouped (reduction over the rows of one expert, fixed row order, no split-K):
+//     dW1[e] = dAB_e^T * X_e   A MN-major, B MN-major
+//     dW2[e] = dY_e^T  * U_e   A MN-major, B MN-major
+//
+// CTA = 192 threads: warp 0 TMA producer, warp 1 MMA issuer (+TMEM owner), warps 2-5 epilogue
+// (one TMEM lane quarter each).  Tile 128 x BLOCK_N x 64, UMMA 128 x BLOCK_N x 16, two TMEM
+// accumulator stages so the epilogue of tile i overlaps the MMAs of tile i+1.
+//
+// Batch invariance: a row's accumulator only ever sees that row of A, the K loop always
+// runs k-blocks 0..K/64-1 in order with UMMA_K = 16, and the tile shape never depends on the
+// batch, so an output row's bits do not depend on its position or on co-batched rows.
+#pragma once
+#include "ptx.cuh"
+
+namespace wm {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;   // 64 bf16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kGemmThreads = 192;
+
+struct GemmArgs {
+  // ---- schedule
+  const int* num_m_tiles;      // M-grouped: device scalar, number of live 128-row tiles
+  const int* tile_group;       // M-grouped: expert of each 128-row tile
+  const int* group_row_start;  // K-grouped: [groups + 1] padded row offsets (multiples of 64)
+  int groups;                  // K-grouped: number of experts
+  int m_tiles_per_group;       // K-grouped: M_total / 128
+  int n_tiles;                 // N_total / BLOCK_N  (gate/up pair: I / 128)
+  int k_total;                 // M-grouped: reduction extent in elements
+  int b_group_rows;            // rows one expert occupies in B's 2-D tensor map
+  int gate_up_half;            // gate/up pair: I (row offset of the "up" half inside one expert)
+  int* status;                 // device status word (0 = ok)
+};
+
+template <int BLOCK_N>
+struct GemmSmem {
+  static constexpr int kABytes = kBlockM * kBlockK * 2;
+  static constexpr int kBBytes = BLOCK_N * kBlockK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BLOCK_N == 256) ? 4 : 6;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+};
+
+struct TileCoord {
+  int m_tile;    // M-grouped: 128-row tile index; K-grouped: m tile inside the expert
+  int n_tile;
+  int group;
+  int row0;      // K-grouped: first row of the expert's segment
+  int num_kb;    // number of 64-wide k blocks
+};
+
+template <bool K_GROUPED>
+__device__ __forceinline__ TileCoord decode_tile(const GemmArgs& a, int tile) {
+  TileCoord t;
+  if constexpr (!K_GROUPED) {
+    t.m_tile = tile / a.n_tiles;
+    t.n_tile = tile - t.m_tile * a.n_tiles;
+    t.group = __ldg(a.tile_group + t.m_tile);
+    t.row0 = 0;
+    t.num_kb = a.k_total / kBlockK;
+  } else {
+    const int per_group = a.m_tiles_per_group * a.n_tiles;
+    t.group = tile / per_group;
+    const int rem = tile - t.group * per_group;
+    t.m_tile = rem / a.n_tiles;
+    t.n_tile = rem - t.m_tile * a.n_tiles;
+    t.row0 = __ldg(a.group_row_start + t.group);
+    t.num_kb = (__ldg(a.group_row_start + t.group + 1) - t.row0) / kBlockK;
+  }
+  return t;
+}
+
+// Epilogue functors get: the TMEM address of the accumulator for this warp's lane quarter
+// (lane field already set), the tile, the lane quarter q (rows q*32 .. q*32+31 of the tile),
+// the lane id, and `zero` = the K loop was empty (nothing was accumulated: result is 0).
+//
+// Signature: void operator()(uint32_t taddr, const TileCoord& t, int q, int lane, bool zero) const
+
+template <int BLOCK_N, bool A_MN, bool B_MN, bool GATE_UP, bool K_GROUPED, class Epilogue>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const GemmArgs args, const Epilogue epilogue) {
+  using S = GemmSmem<BLOCK_N>;
+  constexpr int kStages = S::kStages;
+  constexpr uint32_t kTmemCols = 2 * BLOCK_N;  // two accumulator stages (256 or 512 columns)
+  static_assert(BLOCK_N == 128 || BLOCK_N == 256, "BLOCK_N");
+  static_assert(!GATE_UP || (BLOCK_N == 256 && !B_MN), "gate/up pair tile is 128+128 K-major rows");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full = empty_bar + kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar + s, 1);
+      mbar_init(empty_bar + s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tmem_full + s, 1);
+      mbar_init(tmem_empty + s, 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  int total_tiles;
+  if constexpr (K_GROUPED) {
+    total_tiles = args.groups * args.m_tiles_per_group * args.n_tiles;
+  } else {
+    total_tiles = __ldg(args.num_m_tiles) * args.n_tiles;
+  }
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const TileCoord t = decode_tile<K_GROUPED>(args, tile);
+        for (int kb = 0; kb < t.num_kb; ++kb) {
+          ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, args.status,
+                         kStatusTimeoutSmemEmpty);
+          if (!ok) break;
+          uint8_t* sa = smem + stage * S::kStageBytes;
+          uint8_t* sb = sa + S::kABytes;
+          mbar_expect_tx(full_bar + stage, S::kStageBytes);
+          const int k0 = kb * kBlockK;
+          if constexpr (!A_MN) {
+            tma_load_2d(sa, &tmap_a, full_bar + stage, k0, t.m_tile * kBlockM);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBlockM / 64; ++j)
+              tma_load_2d(sa + j * (kBlockK * 128), &tmap_a, full_bar + stage,
+                          t.m_tile * kBlockM + j * 64, t.row0 + k0);
+          }
+          if constexpr (GATE_UP) {
+            const int r = t.group * args.b_group_rows + t.n_tile * 128;
+            tma_load_2d(sb, &tmap_b, full_bar + stage, k0, r);
+            tma_load_2d(sb + 128 * kBlockK * 2, &tmap_b, full_bar + stage, k0,
+                        r + args.gate_up_half);
+          } else if constexpr (!B_MN) {
+            tma_load_2d(sb, &tmap_b, full_bar + stage, k0,
+                        t.group * args.b_group_rows + t.n_tile * BLOCK_N);
+          } else {
+            const int krow = K_GROUPED ? (t.row0 + k0) : (t.group * args.b_group_rows + k0);
+#pragma unroll
+            for (int j = 0; j < BLOCK_N / 64; ++j)
+              tma_load_2d(sb + j * (kBlockK * 128), &tmap_b, full_bar + stage,
+                          t.n_tile * BLOCK_N + j * 64, krow);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(1u, kBlockM, BLOCK_N, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+      // K-major, 128B swizzle: 8-row groups are 1024 B apart (SBO); LBO unused.
+      // MN-major, 128B swizzle: 64-element MN atoms are kBlockK*128 B apart (LBO), 8-row k groups
+      // 1024 B apart (SBO).
+      constexpr uint32_t kLboA = A_MN ? kBlockK * 128 : 0, kLboB = B_MN ? kBlockK * 128 : 0;
+      constexpr uint32_t kAdvA = (A_MN ? kUmmaK * 128 : kUmmaK * 2) >> 4;
+      constexpr uint32_t kAdvB = (B_MN ? kUmmaK * 128 : kUmmaK * 2) >> 4;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const TileCoord t = decode_tile<K_GROUPED>(args, tile);
+        ok = mbar_wait(tmem_empty + acc, acc_phase ^ 1, abort_flag, args.status,
+                       kStatusTimeoutTmemEmpty);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
+        for (int kb = 0; kb < t.num_kb; ++kb) {
+          ok = mbar_wait(full_bar + stage, phase, abort_flag, args.status, kStatusTimeoutSmemFull);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
+          const uint32_t sb = sa + S::kABytes;
+          const uint64_t da = umma_desc_sw128(sa, kLboA, 1024);
+          const uint64_t db = umma_desc_sw128(sb, kLboB, 1024);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            umma_bf16(tmem_d, da + k * kAdvA, db + k * kAdvB, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar + stage);  // frees the stage once these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(tmem_full + acc);  // accumulator complete (fires at once for an empty K loop)
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const TileCoord t = decode_tile<K_GROUPED>(args, tile);
+      ok = mbar_wait(tmem_full + acc, acc_phase, abort_flag, args.status, kStatusTimeoutTmemFull);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
+      epilogue(taddr, t, q, lane, t.num_kb == 0);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty + acc);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------- epilogues
+
+// Plain BF16 store: out[(group_base) + row, col] with leading dimension ld.
+//   M-grouped: row = m_tile*128 + r.   K-grouped: out + group*group_stride, row = m_tile*128 + r.
+template <int BLOCK_N>
+struct EpilogueStore {
+  __nv_bfloat16* out;
+  long long group_stride;  // elements between experts (K-grouped), 0 for M-grouped
+  int ld;
+
+  __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane,
+                                             bool zero) const {
+    const long long row = static_cast<long long>(t.m_tile) * kBlockM + q * 32 + lane;
+    __nv_bfloat16* dst = out + group_stride * t.group + row * ld + t.n_tile * BLOCK_N;
+#pragma unroll 1
+    for (int c = 0; c < BLOCK_N / 32; ++c) {
+      uint32_t v[32];
+      if (!zero) {
+        tmem_ld_32x32(taddr + c * 32, v);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0;
+      }
+      uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 w;
+        w.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+        w.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+        w.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+        w.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+        d4[j] = w;
+      }
+    }
+  }
+};
+
+// FC1 epilogue (reference: src/cuda/blackwell/fused/impls/routed_bf16.cuh:874-1027):
+// accumulator columns [0,128) are gate, [128,256) are up for intermediate columns
+// n_tile*128 .. +127.  gate and up are rounded to BF16 first (that rounded pair is what the
+// training cache stores), then u = bf16( silu(gate) * up * prob ).
+struct EpilogueSwiglu {
+  __nv_bfloat16* u;         // [rows, I]
+  __nv_bfloat16* ab;        // [rows, 2I] or nullptr (inference)
+  const float* row_prob;    // [rows] gate probability of the routed row (0 on padding rows)
+  int inter;                // I
+
+  __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane,
+                                             bool) const {
+    const long long row = static_cast<long long>(t.m_tile) * kBlockM + q * 32 + lane;
+    const float prob = row_prob[row];
+    const int col0 = t.n_tile * 128;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t g[32], b[32];
+      tmem_ld_32x32(taddr + c * 32, g);
+      tmem_ld_32x32(taddr + 128 + c * 32, b);
+      tmem_ld_wait();
+      uint32_t pg[16], pb[16], pu[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float g0 = bf16_round(__uint_as_float(g[2 * j])), g1 = bf16_round(__uint_as_float(g[2 * j + 1]));
+        const float b0 = bf16_round(__uint_as_float(b[2 * j])), b1 = bf16_round(__uint_as_float(b[2 * j + 1]));
+        pg[j] = pack_bf16x2(g0, g1);
+        pb[j] = pack_bf16x2(b0, b1);
+        const float u0 = (g0 / (1.0f + __expf(-g0))) * b0 * prob;
+        const float u1 = (g1 / (1.0f + __expf(-g1))) * b1 * prob;
+        pu[j] = pack_bf16x2(u0, u1);
+      }
+      uint4* du = reinterpret_cast<uint4*>(u + row * inter + col0 + c * 32);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) du[j] = make_uint4(pu[4 * j], pu[4 * j + 1], pu[4 * j + 2], pu[4 * j + 3]);
+      if (ab != nullptr) {
+        uint4* dg = reinterpret_cast<uint4*>(ab + row * (2 * inter) + col0 + c * 32);
+        uint4* db = reinterpret_cast<uint4*>(ab + row * (2 * inter) + inter + col0 + c * 32);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          dg[j] = make_uint4(pg[4 * j], pg[4 * j + 1], pg[4 * j + 2], pg[4 * j + 3]);
+          db[j] = make_uint4(pb[4 * j], pb[4 * j + 1], pb[4 * j + 2], pb[4 * j + 3]);
+        }
+      }
+    }
+  }
+};
+
+// Return epilogue (FC2 contributions and backward dX rows): each routed row is written as
+// BF16 into the SOURCE rank's mailbox [sorted_slot][token][N] with 16-byte stores, local or
+// over NVLink through the peer-mapped arena (reference: routed_bf16.cuh:1028-1139 and
+// weftmoe/blackwell_backward.py:116-144).  origin = src_rank*cap*K + token*K + sorted_slot,
+// -1 on padding rows.
+constexpr int kMaxRanks = 8;
+template <int BLOCK_N>
+struct EpiloguePush {
+  __nv_bfloat16* mailbox[kMaxRanks];  // peer-mapped base of each rank's mailbox
+  const int* origin;                  // [rows]
+  int cap;                            // tokens capacity per rank
+  int top_k;
+  int ld;                             // N_total (hidden)
+
+  __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane,
+                                             bool) const {
+    const long long row = static_cast<long long>(t.m_tile) * kBlockM + q * 32 + lane;
+    const int org = origin[row];
+    const int per_rank = cap * top_k;
+    const int src = org >= 0 ? org / per_rank : 0;
+    const int rem = org >= 0 ? org - src * per_rank : 0;
+    const int token = rem / top_k, slot = rem - token * top_k;
+    __nv_bfloat16* dst = mailbox[src] +
+                         (static_cast<long long>(slot) * cap + token) * ld + t.n_tile * BLOCK_N;
+#pragma unroll 1
+    for (int c = 0; c < BLOCK_N / 32; ++c) {
+      uint32_t v[32];
+      tmem_ld_32x32(taddr + c * 32, v);  // warp-collective: every lane takes part
+      tmem_ld_wait();
+      if (org >= 0) {
+        uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+          w.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+          w.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+          w.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+          d4[j] = w;
+        }
+      }
+    }
+  }
+};
+
+}  // namespace wm

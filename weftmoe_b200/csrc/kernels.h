@@ -1,0 +1,65 @@
+// Internal C++ interface between the host runtime (runtime.cu, the C ABI) and the kernel
+// translation units.  Nothing here is exported; the public surface is include/weftmoe_b200.h.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace wm {
+
+constexpr int kMaxPeers = 8;
+
+// ------------------------------------------------------------------ error plumbing
+void set_error(const char* fmt, ...);
+const char* last_error();
+#define WM_CUDA(expr)                                                                 \
+  do {                                                                                \
+    cudaError_t e_ = (expr);                                                          \
+    if (e_ != cudaSuccess) {                                                          \
+      ::wm::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), __FILE__, \
+                      __LINE__);                                                      \
+      return 3;                                                                       \
+    }                                                                                 \
+  } while (0)
+
+// ------------------------------------------------------------------ tensor maps
+// 2-D BF16 (elem_bytes = 2) or 8-bit (elem_bytes = 1) row-major tensor, 128-byte swizzle.
+// box_inner * elem_bytes must be 128.  Returns 0 on success.
+int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
+                 uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
+
+// ------------------------------------------------------------------ grouped GEMM launchers
+struct Schedule {
+  const int* num_m_tiles;      // device scalar
+  const int* tile_group;       // device [max tiles]
+  const int* group_row_start;  // device [groups + 1]
+  int groups;
+  int row_capacity;            // rows addressable in the row-indexed operands
+};
+
+struct PushTarget {
+  __nv_bfloat16* mailbox[kMaxPeers];
+  const int* origin;
+  int cap;
+  int top_k;
+};
+
+// FC1: u[rows, I] = swiglu(x[rows, H] * w1[e][2I, H]^T) * prob ; ab optional [rows, 2I].
+int launch_fc1(const Schedule& s, const __nv_bfloat16* x, const __nv_bfloat16* w1, __nv_bfloat16* u,
+               __nv_bfloat16* ab, const float* row_prob, int hidden, int inter, int* status,
+               int sms, cudaStream_t stream);
+// M-grouped, B K-major: out[rows, n] = a[rows, k] * b[e][n, k]^T  (store) or pushed to mailboxes.
+int launch_mgrouped_nt(const Schedule& s, const __nv_bfloat16* a, const __nv_bfloat16* b,
+                       __nv_bfloat16* out, const PushTarget* push, int n, int k, int* status,
+                       int sms, cudaStream_t stream);
+// M-grouped, B MN-major: out[rows, n] = a[rows, k] * b[e][k, n]  (store) or pushed to mailboxes.
+int launch_mgrouped_nn(const Schedule& s, const __nv_bfloat16* a, const __nv_bfloat16* b,
+                       __nv_bfloat16* out, const PushTarget* push, int n, int k, int* status,
+                       int sms, cudaStream_t stream);
+// K-grouped: out[e][m, n] = sum over the expert's rows r of a[r, m] * b[r, n].
+int launch_kgrouped_tn(const Schedule& s, const __nv_bfloat16* a, const __nv_bfloat16* b,
+                       __nv_bfloat16* out, int m, int n, int* status, int sms,
+                       cudaStream_t stream);
+
+}  // namespace wm
