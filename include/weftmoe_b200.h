@@ -12,6 +12,12 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#if defined(__GNUC__)
+#define WM_API __attribute__((visibility("default")))
+#else
+#define WM_API
+#endif
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -28,7 +34,7 @@ enum {
   WM_ERR_STATE = 7         /* call not valid in this state (e.g. tape reused, runtime closed)     */
 };
 
-const char* wm_last_error(void);
+WM_API const char* wm_last_error(void);
 
 /* Diagnostic: one grouped GEMM on caller buffers (synchronises `stream`).
  * kind 0: out[rows,n]   = a[rows,k] * b[g][n,k]^T          (FC2 form)
@@ -37,7 +43,7 @@ const char* wm_last_error(void);
  * kind 3: out=u[rows,n] = swiglu(a[rows,k] * b[g][2n,k]^T) * row_prob, aux_out = ab[rows,2n] or NULL
  * group_rows_host[g] = rows of expert g (multiples of 128).  Mirrors the role of the reference's
  * diagnostic fp8_gemm binding (src/python/fp8.hpp:61-174). */
-int wm_debug_grouped_gemm(int kind, const void* a, const void* b, void* out, void* aux_out,
+WM_API int wm_debug_grouped_gemm(int kind, const void* a, const void* b, void* out, void* aux_out,
                           const float* row_prob, const int* group_rows_host, int groups, int n,
                           int k_or_m, int* status_dev, void* stream);
 
