@@ -2,9 +2,16 @@
  *
  * Plain C linkage, plain pointers and sizes, no C++ or torch types.  Every function returns an
  * int status (WM_OK = 0); wm_last_error() returns the calling thread's last message.  Device
- * pointers are CUDA device addresses of the current device; `stream` is a cudaStream_t passed as
- * void*.  The calls replace the native object behind the reference's Python Tensor API
- * (`TensorRuntime.native`, weftmoe/runtime.py:277-464; pybind surface src/python/runtime.cpp:870-953).
+ * pointers are CUDA device addresses on the current device; `stream` is a cudaStream_t passed as
+ * void*.  Together these calls replace the native object behind the reference's Python Tensor
+ * API (`TensorRuntime.native`, weftmoe/runtime.py:277-464; its pybind surface is
+ * src/python/runtime.cpp:870-953 and, on Blackwell, the Python class weftmoe/blackwell.py:51-178).
+ *
+ * Tensor contract (weftmoe/runtime.py:243-275, docs/usage.md:63-69):
+ *   x[T,H] bf16, routes[T,K] int32 global expert ids (ids outside [0,E) mean "no route"),
+ *   gates[T,K] fp32, w1[E_local,2I,H] bf16 (rows 0..I-1 gate, I..2I-1 up), w2[E_local,H,I] bf16,
+ *   all contiguous device memory; y[T,H] bf16; dx bf16, dgates[T,K] fp32, dw1/dw2 bf16.
+ * Expert e lives on rank e / (E / world) (src/python/runtime.cpp:175-176).
  */
 #ifndef WEFTMOE_B200_H_
 #define WEFTMOE_B200_H_
@@ -22,30 +29,118 @@
 extern "C" {
 #endif
 
-/* Status codes.  The numbering follows the spirit of the reference's NotifyErrorCode
- * (include/weftmoe/api/errors.hpp:12-31): contract violations are distinct from runtime failures. */
+/* Status codes.  Contract violations (-> ValueError) are distinct from runtime failures
+ * (-> RuntimeError), as in the reference's NotifyErrorCode (include/weftmoe/api/errors.hpp:12-31). */
 enum {
   WM_OK = 0,
-  WM_ERR_INVALID = 2,      /* argument / shape / alignment contract violated (ValueError)       */
-  WM_ERR_CUDA = 3,         /* a CUDA call failed (RuntimeError)                                   */
-  WM_ERR_TIMEOUT = 4,      /* a bounded device wait ran out (TransportTimeout in the reference)   */
-  WM_ERR_ROUTE = 5,        /* route id outside [-1, experts) (ExpertOutOfRange)                   */
-  WM_ERR_CAPACITY = 6,     /* rows or tokens exceed the prepared capacity (CapacityExceeded)      */
-  WM_ERR_STATE = 7         /* call not valid in this state (e.g. tape reused, runtime closed)     */
+  WM_ERR_INVALID = 2,  /* argument / shape / alignment contract violated                       */
+  WM_ERR_CUDA = 3,     /* a CUDA call failed                                                    */
+  WM_ERR_TIMEOUT = 4,  /* a bounded device wait ran out (reference: TransportTimeout)           */
+  WM_ERR_ROUTE = 5,    /* reserved: route id rejected (reference: ExpertOutOfRange)             */
+  WM_ERR_CAPACITY = 6, /* rows or tokens exceed the prepared capacity (CapacityExceeded)        */
+  WM_ERR_STATE = 7     /* call not valid in this state (runtime closed, peers not imported ...) */
 };
 
 WM_API const char* wm_last_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Runtime: one persistent workspace per EP group member.
+ * Replaces Runtime.__init__ / BlackwellRuntime.__init__ (src/python/runtime.cpp:113-240,
+ * weftmoe/blackwell.py:54-82) and the symmetric workspace (weftmoe/blackwell_cutlass.py:179-218,
+ * src/cuda/blackwell/fused_host.cpp:32-55). */
+typedef struct wm_runtime wm_runtime;
+
+typedef struct wm_config {
+  int32_t rank;         /* this process' rank in the EP group                                   */
+  int32_t world;        /* EP group size: 1, 2, 4 or 8                                          */
+  int32_t experts;      /* global expert count E, E % world == 0                                */
+  int32_t top_k;        /* 1..32                                                                */
+  int32_t hidden;       /* H, multiple of 256                                                   */
+  int32_t intermediate; /* I, multiple of 128                                                   */
+  int32_t max_tokens;   /* token capacity of this rank                                          */
+  int32_t max_rows;     /* routed rows this rank may receive as an expert owner                 */
+  int32_t training;     /* non-zero: backward buffers are allocated                             */
+  int32_t reserved;
+} wm_config;
+
+typedef struct wm_sizes {
+  int64_t arena_bytes;   /* peer-mapped arena                                                   */
+  int64_t scratch_bytes; /* private device scratch                                              */
+  int64_t tape_bytes;    /* bytes the caller must provide per saved forward (training cache)    */
+  int32_t row_capacity;  /* padded row capacity of the owner-side buffers                       */
+  int32_t ipc_handle_bytes;
+} wm_sizes;
+
+/* Allocates the arena and scratch on the current device (cudaMalloc).  Not capturable. */
+WM_API int wm_runtime_create(const wm_config* config, wm_runtime** out);
+WM_API int wm_runtime_sizes(const wm_runtime* rt, wm_sizes* out);
+/* CUDA-IPC handle of this rank's arena (ipc_handle_bytes bytes).  The caller moves the handles
+ * between ranks (the Python layer uses all_gather_object, as weftmoe/runtime.py:191-196 does for
+ * the bootstrap id; the reference's own IPC exchange is src/cuda/activation_transport.cu:1355-1498). */
+WM_API int wm_runtime_export_handle(wm_runtime* rt, void* handle_out, size_t bytes);
+/* handles: world * ipc_handle_bytes bytes, rank-major.  world == 1 needs no call. */
+WM_API int wm_runtime_import_peers(wm_runtime* rt, const void* handles, size_t bytes);
+/* Collective teardown step: unmap peers (reference: retire_peer_mappings, weftmoe/runtime.py:450-464). */
+WM_API int wm_runtime_retire_peers(wm_runtime* rt);
+WM_API int wm_runtime_destroy(wm_runtime* rt);
+
+/* Forward (reference: BlackwellRuntime._run, weftmoe/blackwell.py:84-127; fused kernel
+ * src/cuda/blackwell/fused/impls/routed_bf16.cuh:22-1312).  Enqueues on `stream`, no host sync.
+ * tape: NULL for inference, else tape_bytes of device memory that receives the training cache
+ * (reference: checkpoint(), weftmoe/blackwell_backward.py:29-52).  All EP ranks must call in the
+ * same order. */
+WM_API int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, const float* gates,
+                      const void* w1, const void* w2, int32_t tokens, void* y, void* tape,
+                      void* stream);
+
+/* Backward (reference: gradients(), weftmoe/blackwell_backward.py:252-285).  `tape` is the cache a
+ * previous wm_forward filled for the same `tokens`; w1/w2 are the same weights. */
+WM_API int wm_backward(wm_runtime* rt, const void* tape, const void* dy, const void* w1,
+                       const void* w2, int32_t tokens, void* dx, float* dgates, void* dw1, void* dw2,
+                       void* stream);
+
+/* Reads (and clears) the device status word; synchronises `stream`.  *code receives a WM_ERR_* value
+ * (reference: TransportDeviceStatus surfaced through profile_inference, src/python/runtime.cpp:295-331). */
+WM_API int wm_status_poll(wm_runtime* rt, int32_t* code, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Stand-alone route planning for tests and tools (reference: build_rank_local_histogram /
+ * materialize_rank_metadata, include/weftmoe/api/notify_dispatch.hpp:49-114).  Two phases, so a
+ * single GPU can play every rank in turn:
+ *   phase 0 (local): fills sorted_slot, sorted_expert, local_offset-independent arrays and row
+ *           `rank` of count_matrix[world*experts];
+ *   phase 1 (global): with every row of count_matrix present, fills the remaining outputs.
+ * All pointers are device pointers; the call allocates and frees temporary device scratch. */
+typedef struct wm_route_out {
+  int32_t* sorted_slot;   /* [T*K] original slot at combine position j                          */
+  int32_t* sorted_expert; /* [T*K] expert at combine position j, -1 = no route                  */
+  int32_t* local_offset;  /* [T*K] by original slot; -1 = no route                              */
+  int32_t* dst_rank;      /* [T*K]                                                              */
+  int32_t* dst_row;       /* [T*K] canonical (unpadded) row inside the owner                    */
+  int32_t* dst_prow;      /* [T*K] physical row in the owner's 128-padded layout                */
+  int32_t* expert_total;  /* [E]                                                                */
+  int32_t* expert_base;   /* [E] unpadded first row inside the owner                            */
+  int32_t* expert_pbase;  /* [E] padded first row inside the owner                              */
+  int32_t* padded_start;  /* [E/world + 1] this rank as owner                                   */
+  int32_t* tile_group;    /* [row_capacity/128]                                                 */
+  int32_t* num_tiles;     /* [1]                                                                */
+  int32_t* padded_rows;   /* [1]                                                                */
+} wm_route_out;
+
+WM_API int wm_route_plan(int32_t phase, int32_t world, int32_t rank, int32_t experts, int32_t top_k,
+                         int32_t tokens, int32_t cap, int32_t row_capacity, const int32_t* routes,
+                         int32_t* count_matrix, const wm_route_out* out, void* stream);
 
 /* Diagnostic: one grouped GEMM on caller buffers (synchronises `stream`).
  * kind 0: out[rows,n]   = a[rows,k] * b[g][n,k]^T          (FC2 form)
  * kind 1: out[rows,n]   = a[rows,k] * b[g][k,n]            (dU / dX form)
  * kind 2: out[g][m,n]   = sum_r a[r,m] * b[r,n]            (dW form; k_or_m = m)
  * kind 3: out=u[rows,n] = swiglu(a[rows,k] * b[g][2n,k]^T) * row_prob, aux_out = ab[rows,2n] or NULL
- * group_rows_host[g] = rows of expert g (multiples of 128).  Mirrors the role of the reference's
+ * group_rows_host[g] = rows of expert g (multiples of 128).  Plays the role of the reference's
  * diagnostic fp8_gemm binding (src/python/fp8.hpp:61-174). */
 WM_API int wm_debug_grouped_gemm(int kind, const void* a, const void* b, void* out, void* aux_out,
-                          const float* row_prob, const int* group_rows_host, int groups, int n,
-                          int k_or_m, int* status_dev, void* stream);
+                                 const float* row_prob, const int* group_rows_host, int groups, int n,
+                                 int k_or_m, int* status_dev, void* stream);
 
 #ifdef __cplusplus
 }

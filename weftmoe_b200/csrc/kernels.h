@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "status.h"
+
 namespace wm {
 
 constexpr int kMaxPeers = 8;

@@ -9,19 +9,9 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
-namespace wm {
+#include "status.h"
 
-// Status codes written to the device status word (first failure wins).
-enum : int {
-  kStatusOk = 0,
-  kStatusTimeoutSmemFull = 101,   // MMA warp waited for a TMA stage
-  kStatusTimeoutSmemEmpty = 102,  // TMA warp waited for a free stage
-  kStatusTimeoutTmemFull = 103,   // epilogue waited for an accumulator
-  kStatusTimeoutTmemEmpty = 104,  // MMA warp waited for a drained accumulator
-  kStatusTimeoutPeerFlag = 110,   // a cross-rank generation flag never arrived
-  kStatusBadRoute = 120,          // route id outside [-1, experts)
-  kStatusRowOverflow = 121,       // received rows exceed the prepared capacity
-};
+namespace wm {
 
 // Wall-clock style budget for every wait, in SM cycles (about 2 s at 2 GHz).
 constexpr long long kWaitBudgetCycles = 4000000000LL;

@@ -1,0 +1,247 @@
+// Route planning ("notify") kernels: per-token combine order, per-expert counts, stable
+// per-source ordinals, count exchange through peer-mapped arenas, destination rows.
+//
+// Integer-only and deterministic: the same routes always give the same rows, which is what
+// makes the weight-gradient reduction order and the combine order reproducible.
+// Reference behaviour restated here (not its code):
+//   combine order  — weftmoe/blackwell.py:10-13, src/cuda/weftmoe_pf/route_plan.cuh:29-50
+//   ordinals       — weftmoe/blackwell_backward.py:20-37
+//   canonical rows — src/metadata/notify_dispatch.cpp:835-906
+//   counts/notify  — src/cuda/blackwell/fused/impls/routed_bf16.cuh:294-373
+// All kernels are HBM/latency-bound integer work over T*K route words.
+#include "kernels.h"
+#include "ptx.cuh"
+#include "route.h"
+
+namespace wm {
+
+constexpr int kChunk = 1024;  // routes per CTA in the counting passes (one per thread)
+
+// ------------------------------------------------------------------ K1: per-token sort
+// One warp per token; lane s < K owns original slot s.  Position = number of slots that sort
+// before it under key (valid ? id : E, slot).
+__global__ void sort_slots_kernel(const int* __restrict__ routes, int tokens, int top_k, int experts,
+                                  int* __restrict__ sorted_slot, int* __restrict__ sorted_expert,
+                                  int* __restrict__ slot_pos) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= tokens) return;
+  const int id = lane < top_k ? routes[warp * top_k + lane] : experts + 1;
+  const bool valid = id >= 0 && id < experts;
+  const int key = lane < top_k ? (valid ? id : experts) : experts + 1;
+  int pos = 0;
+  for (int j = 0; j < top_k; ++j) {
+    const int kj = __shfl_sync(0xffffffffu, key, j);
+    pos += (kj < key) || (kj == key && j < lane);
+  }
+  if (lane < top_k) {
+    sorted_slot[warp * top_k + pos] = lane;
+    sorted_expert[warp * top_k + pos] = valid ? id : -1;
+    slot_pos[warp * top_k + lane] = pos;
+  }
+}
+
+// ------------------------------------------------------------------ K2a: chunk histograms
+__global__ void chunk_hist_kernel(const int* __restrict__ routes, int n, int experts,
+                                  int* __restrict__ chunk_hist) {
+  extern __shared__ int hist[];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int i = blockIdx.x * kChunk + threadIdx.x;
+  if (i < n) {
+    const int id = routes[i];
+    if (id >= 0 && id < experts) atomicAdd(&hist[id], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x)
+    chunk_hist[static_cast<size_t>(blockIdx.x) * experts + e] = hist[e];
+}
+
+// ------------------------------------------------------------------ K2b: scan over chunks
+// One warp per expert: exclusive prefix of the chunk counts (in place), total into
+// local_count[e] and into row `rank` of every rank's count matrix (peer-mapped stores).
+__global__ void chunk_scan_kernel(int* __restrict__ chunk_hist, int chunks, int experts,
+                                  int* __restrict__ local_count, PeerInts count_matrix, int world,
+                                  int rank) {
+  const int e = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (e >= experts) return;
+  int running = 0;
+  for (int base = 0; base < chunks; base += 32) {
+    const int c = base + lane;
+    const int v = c < chunks ? chunk_hist[static_cast<size_t>(c) * experts + e] : 0;
+    int incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += up;
+    }
+    if (c < chunks) chunk_hist[static_cast<size_t>(c) * experts + e] = running + incl - v;
+    running += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) local_count[e] = running;
+  if (lane < world) count_matrix.p[lane][rank * experts + e] = running;
+}
+
+// ------------------------------------------------------------------ Kg: global plan
+// Single CTA.  Waits for every rank's count row of this generation, then derives per expert:
+// total rows, rows from lower ranks, unpadded and padded base inside the owner; and for this
+// rank as owner: padded row start per local expert, the 128-row tile -> expert map, tile count.
+__global__ void global_plan_kernel(const int* __restrict__ count_matrix, const int* flag_counts,
+                                   int generation, int world, int rank, int experts,
+                                   int row_capacity, PlanTables t, int* status) {
+  extern __shared__ int sh[];
+  int* total = sh;               // [experts]
+  int* padded = sh + experts;    // [experts]
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    if (!wait_flag_ge(flag_counts + threadIdx.x * kFlagStride, generation, status)) ok = 0;
+  }
+  __syncthreads();
+  const int e_local = experts / world;
+  if (!ok) {
+    if (threadIdx.x == 0) { *t.num_tiles = 0; *t.padded_rows = 0; }
+    return;
+  }
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    int sum = 0, before = 0;
+    for (int s = 0; s < world; ++s) {
+      const int c = count_matrix[s * experts + e];
+      sum += c;
+      if (s < rank) before += c;
+    }
+    total[e] = sum;
+    padded[e] = (sum + 127) / 128 * 128;
+    t.expert_total[e] = sum;
+    t.expert_before[e] = before;
+  }
+  __syncthreads();
+  // Per-owner exclusive prefixes (unpadded and padded).  One thread per owner; E/EP <= 512.
+  if (threadIdx.x < world) {
+    int base = 0, pbase = 0;
+    for (int l = 0; l < e_local; ++l) {
+      const int e = threadIdx.x * e_local + l;
+      t.expert_base[e] = base;
+      t.expert_pbase[e] = pbase;
+      base += total[e];
+      pbase += padded[e];
+    }
+    if (threadIdx.x == rank) {
+      int tiles = pbase / 128;
+      if (pbase > row_capacity) {
+        atomicCAS(status, 0, kStatusRowOverflow);
+        tiles = 0;
+        pbase = 0;
+      }
+      *t.num_tiles = tiles;
+      *t.padded_rows = pbase;
+      t.padded_start[e_local] = pbase;
+    }
+  }
+  __syncthreads();
+  if (*t.num_tiles == 0 && *t.padded_rows == 0) {
+    // overflow or no rows: still publish zeroed starts so K-grouped GEMMs write zero gradients
+    for (int l = threadIdx.x; l <= e_local; l += blockDim.x) t.padded_start[l] = 0;
+    return;
+  }
+  for (int l = threadIdx.x; l < e_local; l += blockDim.x) {
+    const int e = rank * e_local + l;
+    const int start = t.expert_pbase[e];
+    t.padded_start[l] = start;
+    for (int k = 0; k < padded[e] / 128; ++k) t.tile_group[start / 128 + k] = l;
+  }
+}
+
+// ------------------------------------------------------------------ K2c: destination rows + meta push
+// One route per thread, 1024 routes per CTA in route order.  Stable ordinal inside the chunk
+// = (same-expert routes in earlier warps) + (same-expert lanes below me in my warp).
+__global__ void route_rows_kernel(const int* __restrict__ routes, const float* __restrict__ gates,
+                                  const int* __restrict__ slot_pos, int n, int top_k, int experts,
+                                  int world, int rank, int cap, const int* __restrict__ chunk_base,
+                                  PlanTables t, int* __restrict__ local_offset,
+                                  int* __restrict__ dst_rank, int* __restrict__ dst_row,
+                                  int* __restrict__ dst_prow, PeerInts meta_origin,
+                                  PeerFloats meta_prob) {
+  extern __shared__ unsigned short warp_cnt[];  // [32][experts]
+  for (int k = threadIdx.x; k < 32 * experts; k += blockDim.x) warp_cnt[k] = 0;
+  __syncthreads();
+  const int i = blockIdx.x * kChunk + threadIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int id = i < n ? routes[i] : -1;
+  const bool valid = id >= 0 && id < experts;
+  const int key = valid ? id : experts;
+  const unsigned peers = __match_any_sync(0xffffffffu, key);
+  const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+  if (valid && rank_in_warp == 0) warp_cnt[warp * experts + id] = static_cast<unsigned short>(__popc(peers));
+  __syncthreads();
+  if (i >= n) return;
+  if (!valid) {
+    local_offset[i] = dst_rank[i] = dst_row[i] = dst_prow[i] = -1;
+    return;
+  }
+  int ordinal = chunk_base[static_cast<size_t>(blockIdx.x) * experts + id] + rank_in_warp;
+  for (int w = 0; w < warp; ++w) ordinal += warp_cnt[w * experts + id];
+  const int e_local = experts / world;
+  const int owner = id / e_local;
+  const int within = t.expert_before[id] + ordinal;
+  const int prow = t.expert_pbase[id] + within;
+  local_offset[i] = ordinal;
+  dst_rank[i] = owner;
+  dst_row[i] = t.expert_base[id] + within;
+  dst_prow[i] = prow;
+  if (meta_origin.p[owner] != nullptr) {
+    const int token = i / top_k;
+    meta_origin.p[owner][prow] = rank * cap * top_k + token * top_k + slot_pos[i];
+    meta_prob.p[owner][prow] = gates[i];
+  }
+}
+
+// ------------------------------------------------------------------ host side
+int route_local(const RouteShape& s, const int* routes, int tokens, RouteLocal out,
+                int* chunk_hist, int* local_count, const PeerInts& count_matrix,
+                cudaStream_t stream) {
+  const int n = tokens * s.top_k;
+  const int chunks = (n + kChunk - 1) / kChunk;
+  if (tokens > 0) {
+    sort_slots_kernel<<<(tokens * 32 + 255) / 256, 256, 0, stream>>>(
+        routes, tokens, s.top_k, s.experts, out.sorted_slot, out.sorted_expert, out.slot_pos);
+    chunk_hist_kernel<<<chunks, kChunk, s.experts * sizeof(int), stream>>>(routes, n, s.experts,
+                                                                           chunk_hist);
+  }
+  chunk_scan_kernel<<<(s.experts * 32 + 255) / 256, 256, 0, stream>>>(
+      chunk_hist, chunks, s.experts, local_count, count_matrix, s.world, s.rank);
+  WM_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int route_global(const RouteShape& s, const int* count_matrix, const int* flag_counts,
+                 int generation, int row_capacity, PlanTables t, int* status, cudaStream_t stream) {
+  global_plan_kernel<<<1, 1024, 2 * s.experts * sizeof(int), stream>>>(
+      count_matrix, flag_counts, generation, s.world, s.rank, s.experts, row_capacity, t, status);
+  WM_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int route_rows(const RouteShape& s, const int* routes, const float* gates, int tokens,
+               const RouteLocal& local, const int* chunk_base, PlanTables t, RouteRows out,
+               const PeerInts& meta_origin, const PeerFloats& meta_prob, cudaStream_t stream) {
+  const int n = tokens * s.top_k;
+  if (n == 0) return 0;
+  const int chunks = (n + kChunk - 1) / kChunk;
+  const size_t smem = 32u * s.experts * sizeof(unsigned short);
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    WM_CUDA(cudaFuncSetAttribute(route_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    configured = true;
+  }
+  route_rows_kernel<<<chunks, kChunk, smem, stream>>>(
+      routes, gates, local.slot_pos, n, s.top_k, s.experts, s.world, s.rank, s.cap, chunk_base, t,
+      out.local_offset, out.dst_rank, out.dst_row, out.dst_prow, meta_origin, meta_prob);
+  WM_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace wm

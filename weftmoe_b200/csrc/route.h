@@ -1,0 +1,91 @@
+// Internal structs shared by the route-planning and transport kernels and the host runtime.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace wm {
+
+constexpr int kMaxWorld = 8;
+constexpr int kFlagStride = 32;  // ints between two flags: one 128-byte line each
+
+struct PeerInts { int* p[kMaxWorld]; };
+struct PeerFloats { float* p[kMaxWorld]; };
+struct PeerRows { __nv_bfloat16* p[kMaxWorld]; };
+struct PeerConstRows { const __nv_bfloat16* p[kMaxWorld]; };
+
+struct RouteShape {
+  int experts, top_k, world, rank, cap;  // cap = token capacity per rank
+};
+
+// Source-side, per token: [tokens * top_k] each.
+struct RouteLocal {
+  int* sorted_slot;    // original slot at combine position j
+  int* sorted_expert;  // expert id at combine position j, -1 when the route is invalid
+  int* slot_pos;       // combine position of original slot s
+};
+struct RouteRows {
+  int* local_offset;  // ordinal among this rank's routes to the same expert, -1 invalid
+  int* dst_rank;      // owner rank
+  int* dst_row;       // canonical (unpadded) row inside the owner
+  int* dst_prow;      // physical row inside the owner's 128-padded layout
+};
+
+// Global tables (identical on every rank) and this rank's owner-side schedule.
+struct PlanTables {
+  int* expert_total;   // [experts] rows routed to the expert over all ranks
+  int* expert_before;  // [experts] rows routed to it by lower ranks than this one
+  int* expert_base;    // [experts] unpadded first row inside its owner
+  int* expert_pbase;   // [experts] padded first row inside its owner
+  int* padded_start;   // [experts/world + 1] padded first row of each local expert
+  int* tile_group;     // [row_capacity / 128] local expert of each 128-row tile
+  int* num_tiles;      // scalar
+  int* padded_rows;    // scalar
+};
+
+int route_local(const RouteShape& s, const int* routes, int tokens, RouteLocal out,
+                int* chunk_hist, int* local_count, const PeerInts& count_matrix,
+                cudaStream_t stream);
+int route_global(const RouteShape& s, const int* count_matrix, const int* flag_counts,
+                 int generation, int row_capacity, PlanTables t, int* status, cudaStream_t stream);
+int route_rows(const RouteShape& s, const int* routes, const float* gates, int tokens,
+               const RouteLocal& local, const int* chunk_base, PlanTables t, RouteRows out,
+               const PeerInts& meta_origin, const PeerFloats& meta_prob, cudaStream_t stream);
+
+// ------------------------------------------------------------------ transport (transport.cu)
+struct OwnerRows {
+  const int* padded_start;  // [e_local + 1]
+  const int* tile_group;    // [tiles]
+  const int* padded_rows;   // scalar
+  const int* expert_total;  // [experts] (global ids)
+};
+
+// Wait until flags[r] >= generation for r < world (bounded); flags are kFlagStride apart.
+int wait_flags(const int* flags, int world, int generation, int* status, cudaStream_t stream);
+// Store `generation` into flag slot `slot` of every rank's flag group (peer-mapped).
+int signal_peers(const PeerInts& flag_group, int world, int slot, int generation,
+                 cudaStream_t stream);
+
+// Owner side, forward: pull every live row's activation from its source rank's staging buffer,
+// copy origin/prob words from the meta mailbox to local arrays, zero the padding rows.
+int gather_rows(const OwnerRows& o, int rank, int e_local, int cap, int top_k, int hidden,
+                const PeerConstRows& stage, const int* meta_origin, const float* meta_prob,
+                __nv_bfloat16* rows_out, int* origin_out, float* prob_out, int sms,
+                cudaStream_t stream);
+// Owner side, backward: pull dY rows by the saved origins.
+int gather_by_origin(const int* padded_rows, const int* origin, int cap, int top_k, int hidden,
+                     const PeerConstRows& stage, __nv_bfloat16* rows_out, int sms,
+                     cudaStream_t stream);
+// Source side: out[t] = bf16( sum over combine positions j with a live route of mailbox[j][t] ).
+int combine_rows(const __nv_bfloat16* mailbox, const int* sorted_expert, int tokens, int cap,
+                 int top_k, int hidden, __nv_bfloat16* out, cudaStream_t stream);
+// Source side, backward: dgates[t, original slot] = dgate_box[t*K + j] for live positions, else 0.
+int unpermute_dgates(const float* dgate_box, const int* sorted_slot, const int* sorted_expert,
+                     int tokens, int top_k, float* dgates, cudaStream_t stream);
+// Owner side, backward elementwise: from saved gate/up (ab), dU and prob compute
+// U = bf16(silu(a) b p), dAB, and the per-row dprob, which is sent to the source's dgate box.
+int swiglu_backward(const int* padded_rows, const __nv_bfloat16* ab, const __nv_bfloat16* du,
+                    const float* prob, const int* origin, int inter, int cap, int top_k,
+                    __nv_bfloat16* u, __nv_bfloat16* dab, const PeerFloats& dgate_box, int sms,
+                    cudaStream_t stream);
+
+}  // namespace wm

@@ -1,0 +1,621 @@
+// Host runtime behind the C ABI: arena/scratch layout, CUDA-IPC peer mapping, and the launch
+// sequences of forward and backward.  One process per GPU; every call enqueues on the caller's
+// stream and never synchronises (except the explicit status poll).
+//
+// Cross-rank protocol (world > 1).  Every collective operation (a forward or a backward) takes
+// the next generation number g, identical on all ranks because all ranks call in the same order.
+// Four flag groups live in each rank's arena, one 128-byte line per peer, holding the latest
+// generation for which the event happened; flags only grow and are never reset:
+//   COUNTS [s]  source s stored its per-expert counts into my count matrix
+//   READY  [s]  source s staged its activations and pushed origin/prob words for my rows
+//   PULLED [o]  owner o finished reading my staging buffer and meta words
+//   CONTRIB[o]  owner o finished writing its results into my mailbox
+// A source overwrites its staging buffer only after PULLED >= g-1 from every owner; an owner
+// writes a mailbox only after READY >= g, which the source sends after its previous combine.
+#include <cstring>
+#include <new>
+
+#include "../../include/weftmoe_b200.h"
+#include "kernels.h"
+#include "route.h"
+
+using namespace wm;
+
+namespace {
+
+enum FlagGroup { kCounts = 0, kReady = 1, kPulled = 2, kContrib = 3, kFlagGroups = 4 };
+
+constexpr size_t kAlign = 256;
+size_t align_up(size_t v, size_t a = kAlign) { return (v + a - 1) / a * a; }
+
+struct Carver {
+  size_t cursor = 0;
+  size_t take(size_t bytes) {
+    const size_t at = cursor;
+    cursor = align_up(cursor + bytes);
+    return at;
+  }
+};
+
+struct ArenaLayout {
+  size_t flags, counts, stage, meta_origin, meta_prob, mailbox, dgate_box, total;
+};
+struct ScratchLayout {
+  size_t status, sorted_slot, sorted_expert, slot_pos, local_offset, dst_rank, dst_row, dst_prow,
+      chunk_hist, local_count, expert_total, expert_before, expert_base, expert_pbase, padded_start,
+      tile_group, num_tiles, padded_rows, origin, prob, xrows, u, recv, du, dab, total;
+};
+// Training cache carved out of the caller's tape buffer.
+struct TapeLayout {
+  size_t sorted_slot, sorted_expert, padded_start, tile_group, num_tiles, padded_rows, origin, prob,
+      xrows, ab, total;
+};
+
+}  // namespace
+
+struct wm_runtime {
+  wm_config cfg;
+  int e_local = 0, row_cap = 0, sms = 0, device = 0, generation = 0;
+  ArenaLayout al{};
+  ScratchLayout sl{};
+  TapeLayout tl{};
+  uint8_t* arena = nullptr;
+  uint8_t* scratch = nullptr;
+  uint8_t* peer[kMaxWorld] = {};
+  bool peers_ready = false;
+};
+
+namespace {
+
+template <class T>
+T* at(uint8_t* base, size_t off) { return reinterpret_cast<T*>(base + off); }
+
+ArenaLayout arena_layout(const wm_config& c, int row_cap) {
+  Carver k;
+  ArenaLayout a{};
+  a.flags = k.take(sizeof(int) * kFlagGroups * kMaxWorld * kFlagStride);
+  a.counts = k.take(sizeof(int) * c.world * c.experts);
+  a.stage = k.take(2ull * c.max_tokens * c.hidden);
+  a.meta_origin = k.take(sizeof(int) * row_cap);
+  a.meta_prob = k.take(sizeof(float) * row_cap);
+  a.mailbox = k.take(2ull * c.top_k * c.max_tokens * c.hidden);
+  a.dgate_box = k.take(sizeof(float) * c.max_tokens * c.top_k);
+  a.total = align_up(k.cursor, 1 << 16);  // 64 KiB multiple keeps large-page peer mappings
+  return a;
+}
+
+ScratchLayout scratch_layout(const wm_config& c, int row_cap) {
+  Carver k;
+  ScratchLayout s{};
+  const size_t routes = static_cast<size_t>(c.max_tokens) * c.top_k;
+  const size_t chunks = (routes + 1023) / 1024 + 1;
+  const int e_local = c.experts / c.world;
+  s.status = k.take(sizeof(int) * 4);
+  s.sorted_slot = k.take(sizeof(int) * routes);
+  s.sorted_expert = k.take(sizeof(int) * routes);
+  s.slot_pos = k.take(sizeof(int) * routes);
+  s.local_offset = k.take(sizeof(int) * routes);
+  s.dst_rank = k.take(sizeof(int) * routes);
+  s.dst_row = k.take(sizeof(int) * routes);
+  s.dst_prow = k.take(sizeof(int) * routes);
+  s.chunk_hist = k.take(sizeof(int) * chunks * c.experts);
+  s.local_count = k.take(sizeof(int) * c.experts);
+  s.expert_total = k.take(sizeof(int) * c.experts);
+  s.expert_before = k.take(sizeof(int) * c.experts);
+  s.expert_base = k.take(sizeof(int) * c.experts);
+  s.expert_pbase = k.take(sizeof(int) * c.experts);
+  s.padded_start = k.take(sizeof(int) * (e_local + 1));
+  s.tile_group = k.take(sizeof(int) * (row_cap / 128 + 1));
+  s.num_tiles = k.take(sizeof(int));
+  s.padded_rows = k.take(sizeof(int));
+  s.origin = k.take(sizeof(int) * row_cap);
+  s.prob = k.take(sizeof(float) * row_cap);
+  s.xrows = k.take(2ull * row_cap * c.hidden);
+  s.u = k.take(2ull * row_cap * c.intermediate);
+  if (c.training) {
+    s.recv = k.take(2ull * row_cap * c.hidden);
+    s.du = k.take(2ull * row_cap * c.intermediate);
+    s.dab = k.take(4ull * row_cap * c.intermediate);
+  }
+  s.total = k.cursor;
+  return s;
+}
+
+TapeLayout tape_layout(const wm_config& c, int row_cap) {
+  Carver k;
+  TapeLayout t{};
+  const size_t routes = static_cast<size_t>(c.max_tokens) * c.top_k;
+  const int e_local = c.experts / c.world;
+  t.sorted_slot = k.take(sizeof(int) * routes);
+  t.sorted_expert = k.take(sizeof(int) * routes);
+  t.padded_start = k.take(sizeof(int) * (e_local + 1));
+  t.tile_group = k.take(sizeof(int) * (row_cap / 128 + 1));
+  t.num_tiles = k.take(sizeof(int));
+  t.padded_rows = k.take(sizeof(int));
+  t.origin = k.take(sizeof(int) * row_cap);
+  t.prob = k.take(sizeof(float) * row_cap);
+  t.xrows = k.take(2ull * row_cap * c.hidden);
+  t.ab = k.take(4ull * row_cap * c.intermediate);
+  t.total = k.cursor;
+  return t;
+}
+
+int check_config(const wm_config& c) {
+  if (c.world != 1 && c.world != 2 && c.world != 4 && c.world != 8) {
+    set_error("world must be 1, 2, 4 or 8 (got %d)", c.world);
+    return WM_ERR_INVALID;
+  }
+  if (c.rank < 0 || c.rank >= c.world) {
+    set_error("rank %d outside world %d", c.rank, c.world);
+    return WM_ERR_INVALID;
+  }
+  // Shape limits follow weftmoe/runtime.py:113-118.
+  if (c.experts <= 0 || c.experts % c.world || c.experts / c.world > 512 || c.experts > 2048 ||
+      c.top_k < 1 || c.top_k > 32 || c.top_k > c.experts || c.hidden < 256 || c.hidden % 256 ||
+      c.intermediate < 128 || c.intermediate > 4096 || c.intermediate % 128 || c.max_tokens < 0 ||
+      c.max_rows < 0) {
+    set_error("Unsupported expert shape or token capacity (E=%d K=%d H=%d I=%d T=%d rows=%d)",
+              c.experts, c.top_k, c.hidden, c.intermediate, c.max_tokens, c.max_rows);
+    return WM_ERR_INVALID;
+  }
+  const long long origin_span = 1ll * c.world * (c.max_tokens > 0 ? c.max_tokens : 1) * c.top_k;
+  if (origin_span >= (1ll << 31)) {
+    set_error("world * max_tokens * top_k must fit in 31 bits");
+    return WM_ERR_INVALID;
+  }
+  return WM_OK;
+}
+
+PeerInts flag_group(const wm_runtime* rt, int group) {
+  PeerInts p{};
+  for (int r = 0; r < rt->cfg.world; ++r)
+    p.p[r] = at<int>(rt->peer[r], rt->al.flags) + group * kMaxWorld * kFlagStride;
+  return p;
+}
+const int* my_flags(const wm_runtime* rt, int group) {
+  return at<int>(rt->arena, rt->al.flags) + group * kMaxWorld * kFlagStride;
+}
+
+int map_status(int device_code) {
+  switch (device_code) {
+    case 0: return WM_OK;
+    case kStatusRowOverflow: return WM_ERR_CAPACITY;
+    case kStatusBadRoute: return WM_ERR_ROUTE;
+    default: return WM_ERR_TIMEOUT;
+  }
+}
+
+int check_ready(const wm_runtime* rt, const char* what) {
+  if (!rt || !rt->arena) {
+    set_error("%s: runtime is closed", what);
+    return WM_ERR_STATE;
+  }
+  if (rt->cfg.world > 1 && !rt->peers_ready) {
+    set_error("%s: import the peer handles first", what);
+    return WM_ERR_STATE;
+  }
+  return WM_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+// =============================================================================== lifecycle
+extern "C" int wm_runtime_create(const wm_config* config, wm_runtime** out) {
+  if (!config || !out) {
+    set_error("wm_runtime_create: null argument");
+    return WM_ERR_INVALID;
+  }
+  if (int rc = check_config(*config)) return rc;
+  wm_runtime* rt = new (std::nothrow) wm_runtime();
+  if (!rt) {
+    set_error("out of host memory");
+    return WM_ERR_CUDA;
+  }
+  rt->cfg = *config;
+  rt->e_local = config->experts / config->world;
+  const int cap_tokens = config->max_tokens > 0 ? config->max_tokens : 1;
+  rt->cfg.max_tokens = cap_tokens;
+  // Each local expert's rows are padded to 128: at most 127 extra rows per live expert.
+  rt->row_cap = static_cast<int>(align_up(static_cast<size_t>(config->max_rows), 128)) +
+                128 * rt->e_local;
+  rt->al = arena_layout(rt->cfg, rt->row_cap);
+  rt->sl = scratch_layout(rt->cfg, rt->row_cap);
+  rt->tl = tape_layout(rt->cfg, rt->row_cap);
+  auto fail = [&](int rc) {
+    if (rt->arena) cudaFree(rt->arena);
+    if (rt->scratch) cudaFree(rt->scratch);
+    delete rt;
+    return rc;
+  };
+  if (cudaGetDevice(&rt->device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&rt->sms, cudaDevAttrMultiProcessorCount, rt->device) != cudaSuccess) {
+    set_error("no CUDA device is current");
+    return fail(WM_ERR_CUDA);
+  }
+  cudaError_t e = cudaMalloc(&rt->arena, rt->al.total);
+  if (e == cudaSuccess) e = cudaMalloc(&rt->scratch, rt->sl.total);
+  if (e != cudaSuccess) {
+    set_error("workspace allocation failed (arena %zu B, scratch %zu B): %s", rt->al.total,
+              rt->sl.total, cudaGetErrorString(e));
+    return fail(WM_ERR_CUDA);
+  }
+  // Zero only what must start at zero: flags, count matrix, status.  Done on the legacy stream
+  // and synchronised so that peers may write as soon as they have imported the handle.
+  e = cudaMemset(rt->arena, 0, rt->al.stage);
+  if (e == cudaSuccess) e = cudaMemset(rt->scratch + rt->sl.status, 0, sizeof(int) * 4);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    set_error("workspace initialisation failed: %s", cudaGetErrorString(e));
+    return fail(WM_ERR_CUDA);
+  }
+  rt->peer[rt->cfg.rank] = rt->arena;
+  rt->peers_ready = rt->cfg.world == 1;
+  *out = rt;
+  return WM_OK;
+}
+
+extern "C" int wm_runtime_sizes(const wm_runtime* rt, wm_sizes* out) {
+  if (!rt || !out) {
+    set_error("wm_runtime_sizes: null argument");
+    return WM_ERR_INVALID;
+  }
+  out->arena_bytes = static_cast<int64_t>(rt->al.total);
+  out->scratch_bytes = static_cast<int64_t>(rt->sl.total);
+  out->tape_bytes = static_cast<int64_t>(rt->tl.total);
+  out->row_capacity = rt->row_cap;
+  out->ipc_handle_bytes = static_cast<int32_t>(sizeof(cudaIpcMemHandle_t));
+  return WM_OK;
+}
+
+extern "C" int wm_runtime_export_handle(wm_runtime* rt, void* handle_out, size_t bytes) {
+  if (!rt || !rt->arena || !handle_out || bytes < sizeof(cudaIpcMemHandle_t)) {
+    set_error("wm_runtime_export_handle: bad argument");
+    return WM_ERR_INVALID;
+  }
+  cudaIpcMemHandle_t h;
+  WM_CUDA(cudaIpcGetMemHandle(&h, rt->arena));
+  std::memcpy(handle_out, &h, sizeof(h));
+  return WM_OK;
+}
+
+extern "C" int wm_runtime_import_peers(wm_runtime* rt, const void* handles, size_t bytes) {
+  if (!rt || !rt->arena || !handles || bytes < sizeof(cudaIpcMemHandle_t) * rt->cfg.world) {
+    set_error("wm_runtime_import_peers: bad argument");
+    return WM_ERR_INVALID;
+  }
+  if (rt->peers_ready) return WM_OK;
+  const auto* h = static_cast<const cudaIpcMemHandle_t*>(handles);
+  for (int r = 0; r < rt->cfg.world; ++r) {
+    if (r == rt->cfg.rank) continue;
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h[r], cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      set_error("cudaIpcOpenMemHandle for rank %d failed: %s", r, cudaGetErrorString(e));
+      for (int q = 0; q < r; ++q)
+        if (q != rt->cfg.rank && rt->peer[q]) {
+          cudaIpcCloseMemHandle(rt->peer[q]);
+          rt->peer[q] = nullptr;
+        }
+      return WM_ERR_CUDA;
+    }
+    rt->peer[r] = static_cast<uint8_t*>(p);
+  }
+  rt->peers_ready = true;
+  return WM_OK;
+}
+
+extern "C" int wm_runtime_retire_peers(wm_runtime* rt) {
+  if (!rt) return WM_OK;
+  for (int r = 0; r < rt->cfg.world; ++r) {
+    if (r != rt->cfg.rank && rt->peer[r]) {
+      cudaIpcCloseMemHandle(rt->peer[r]);
+      rt->peer[r] = nullptr;
+    }
+  }
+  rt->peers_ready = rt->cfg.world == 1;
+  return WM_OK;
+}
+
+extern "C" int wm_runtime_destroy(wm_runtime* rt) {
+  if (!rt) return WM_OK;
+  wm_runtime_retire_peers(rt);
+  if (rt->arena) cudaFree(rt->arena);
+  if (rt->scratch) cudaFree(rt->scratch);
+  rt->arena = rt->scratch = nullptr;
+  delete rt;
+  return WM_OK;
+}
+
+extern "C" int wm_status_poll(wm_runtime* rt, int32_t* code, void* stream_) {
+  if (int rc = check_ready(rt, "wm_status_poll")) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int device_code = 0;
+  WM_CUDA(cudaMemcpyAsync(&device_code, rt->scratch + rt->sl.status, sizeof(int),
+                          cudaMemcpyDeviceToHost, stream));
+  WM_CUDA(cudaStreamSynchronize(stream));
+  if (device_code != 0) {
+    WM_CUDA(cudaMemsetAsync(rt->scratch + rt->sl.status, 0, sizeof(int), stream));
+    set_error("device status %d (%s)", device_code,
+              device_code == kStatusRowOverflow ? "received rows exceed max_rows"
+                                                : "a bounded device wait ran out");
+  }
+  if (code) *code = map_status(device_code);
+  return WM_OK;
+}
+
+// =============================================================================== forward
+extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, const float* gates,
+                          const void* w1, const void* w2, int32_t tokens, void* y, void* tape,
+                          void* stream_) {
+  if (int rc = check_ready(rt, "wm_forward")) return rc;
+  const wm_config& c = rt->cfg;
+  if (tokens < 0 || tokens > c.max_tokens) {
+    set_error("Activation shape exceeds prepared capacity (%d tokens, capacity %d)", tokens,
+              c.max_tokens);
+    return WM_ERR_CAPACITY;
+  }
+  if (!w1 || !w2 || (tokens > 0 && (!x || !routes || !gates || !y)) || !aligned16(x) ||
+      !aligned16(y) || !aligned16(w1) || !aligned16(w2) || !aligned16(tape)) {
+    set_error("wm_forward: null or misaligned tensor (16-byte alignment required)");
+    return WM_ERR_INVALID;
+  }
+  if (tape && !c.training) {
+    set_error("wm_forward: a training cache needs a runtime created with training=1");
+    return WM_ERR_STATE;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int gen = ++rt->generation;
+  const int world = c.world;
+  uint8_t* S = rt->scratch;
+  uint8_t* T = static_cast<uint8_t*>(tape);
+  int* status = at<int>(S, rt->sl.status);
+
+  // Arrays that the backward pass needs live in the tape when one is given.
+  RouteLocal local{tape ? at<int>(T, rt->tl.sorted_slot) : at<int>(S, rt->sl.sorted_slot),
+                   tape ? at<int>(T, rt->tl.sorted_expert) : at<int>(S, rt->sl.sorted_expert),
+                   at<int>(S, rt->sl.slot_pos)};
+  PlanTables tables{};
+  tables.expert_total = at<int>(S, rt->sl.expert_total);
+  tables.expert_before = at<int>(S, rt->sl.expert_before);
+  tables.expert_base = at<int>(S, rt->sl.expert_base);
+  tables.expert_pbase = at<int>(S, rt->sl.expert_pbase);
+  tables.padded_start = tape ? at<int>(T, rt->tl.padded_start) : at<int>(S, rt->sl.padded_start);
+  tables.tile_group = tape ? at<int>(T, rt->tl.tile_group) : at<int>(S, rt->sl.tile_group);
+  tables.num_tiles = tape ? at<int>(T, rt->tl.num_tiles) : at<int>(S, rt->sl.num_tiles);
+  tables.padded_rows = tape ? at<int>(T, rt->tl.padded_rows) : at<int>(S, rt->sl.padded_rows);
+  int* origin = tape ? at<int>(T, rt->tl.origin) : at<int>(S, rt->sl.origin);
+  float* prob = tape ? at<float>(T, rt->tl.prob) : at<float>(S, rt->sl.prob);
+  auto* xrows = tape ? at<__nv_bfloat16>(T, rt->tl.xrows) : at<__nv_bfloat16>(S, rt->sl.xrows);
+  auto* ab = tape ? at<__nv_bfloat16>(T, rt->tl.ab) : nullptr;
+  auto* u = at<__nv_bfloat16>(S, rt->sl.u);
+
+  RouteShape shape{c.experts, c.top_k, world, c.rank, c.max_tokens};
+  PeerInts counts{}, meta_origin{};
+  PeerFloats meta_prob{};
+  PeerConstRows stage{};
+  PushTarget push{};
+  for (int r = 0; r < world; ++r) {
+    counts.p[r] = at<int>(rt->peer[r], rt->al.counts);
+    meta_origin.p[r] = at<int>(rt->peer[r], rt->al.meta_origin);
+    meta_prob.p[r] = at<float>(rt->peer[r], rt->al.meta_prob);
+    stage.p[r] = at<__nv_bfloat16>(rt->peer[r], rt->al.stage);
+    push.mailbox[r] = at<__nv_bfloat16>(rt->peer[r], rt->al.mailbox);
+  }
+  push.origin = origin;
+  push.cap = c.max_tokens;
+  push.top_k = c.top_k;
+
+  // 1. staging buffer free?  then stage x and plan locally; counts go to every rank.
+  if (world > 1)
+    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, stream)) return rc;
+  if (world == 1)
+    stage.p[0] = static_cast<const __nv_bfloat16*>(x);  // no peers: owners read x itself
+  else if (tokens > 0)
+    WM_CUDA(cudaMemcpyAsync(rt->arena + rt->al.stage, x, 2ull * tokens * c.hidden,
+                            cudaMemcpyDeviceToDevice, stream));
+  if (int rc = route_local(shape, routes, tokens, local, at<int>(S, rt->sl.chunk_hist),
+                           at<int>(S, rt->sl.local_count), counts, stream))
+    return rc;
+  if (world > 1)
+    if (int rc = signal_peers(flag_group(rt, kCounts), world, c.rank, gen, stream)) return rc;
+  // 2. global plan (waits for all count rows), destination rows, origin/prob words to owners.
+  if (int rc = route_global(shape, at<int>(rt->arena, rt->al.counts), my_flags(rt, kCounts),
+                            world > 1 ? gen : 0, rt->row_cap, tables, status, stream))
+    return rc;
+  RouteRows rows{at<int>(S, rt->sl.local_offset), at<int>(S, rt->sl.dst_rank),
+                 at<int>(S, rt->sl.dst_row), at<int>(S, rt->sl.dst_prow)};
+  if (int rc = route_rows(shape, routes, gates, tokens, local, at<int>(S, rt->sl.chunk_hist), tables,
+                          rows, meta_origin, meta_prob, stream))
+    return rc;
+  if (world > 1) {
+    if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
+  }
+  // 3. owner side: pull rows, then the two grouped GEMMs; FC2 pushes into the sources' mailboxes.
+  OwnerRows owner{tables.padded_start, tables.tile_group, tables.padded_rows, tables.expert_total};
+  if (int rc = gather_rows(owner, c.rank, rt->e_local, c.max_tokens, c.top_k, c.hidden, stage,
+                           at<int>(rt->arena, rt->al.meta_origin),
+                           at<float>(rt->arena, rt->al.meta_prob), xrows, origin, prob, rt->sms,
+                           stream))
+    return rc;
+  if (world > 1)
+    if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
+  Schedule sched{tables.num_tiles, tables.tile_group, tables.padded_start, rt->e_local, rt->row_cap};
+  if (int rc = launch_fc1(sched, xrows, static_cast<const __nv_bfloat16*>(w1), u, ab, prob,
+                          c.hidden, c.intermediate, status, rt->sms, stream))
+    return rc;
+  if (int rc = launch_mgrouped_nt(sched, u, static_cast<const __nv_bfloat16*>(w2), nullptr, &push,
+                                  c.hidden, c.intermediate, status, rt->sms, stream))
+    return rc;
+  if (world > 1) {
+    if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
+  }
+  // 4. source side: ordered FP32 combine.
+  return combine_rows(at<__nv_bfloat16>(rt->arena, rt->al.mailbox), local.sorted_expert, tokens,
+                      c.max_tokens, c.top_k, c.hidden, static_cast<__nv_bfloat16*>(y), stream);
+}
+
+// =============================================================================== backward
+extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, const void* w1,
+                           const void* w2, int32_t tokens, void* dx, float* dgates, void* dw1,
+                           void* dw2, void* stream_) {
+  if (int rc = check_ready(rt, "wm_backward")) return rc;
+  const wm_config& c = rt->cfg;
+  if (!c.training) {
+    set_error("Backward requires a runtime prepared with training=True");
+    return WM_ERR_STATE;
+  }
+  if (tokens < 0 || tokens > c.max_tokens) {
+    set_error("Backward token count %d exceeds capacity %d", tokens, c.max_tokens);
+    return WM_ERR_CAPACITY;
+  }
+  if (!tape || !w1 || !w2 || !dw1 || !dw2 || (tokens > 0 && (!dy || !dx || !dgates)) ||
+      !aligned16(tape) || !aligned16(dy) || !aligned16(dx) || !aligned16(dw1) || !aligned16(dw2)) {
+    set_error("wm_backward: null or misaligned tensor (16-byte alignment required)");
+    return WM_ERR_INVALID;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int gen = ++rt->generation;
+  const int world = c.world;
+  uint8_t* S = rt->scratch;
+  const uint8_t* T = static_cast<const uint8_t*>(tape);
+  auto tp = [&](size_t off) { return const_cast<uint8_t*>(T) + off; };
+  int* status = at<int>(S, rt->sl.status);
+  const int* sorted_slot = reinterpret_cast<const int*>(tp(rt->tl.sorted_slot));
+  const int* sorted_expert = reinterpret_cast<const int*>(tp(rt->tl.sorted_expert));
+  const int* padded_start = reinterpret_cast<const int*>(tp(rt->tl.padded_start));
+  const int* tile_group = reinterpret_cast<const int*>(tp(rt->tl.tile_group));
+  const int* num_tiles = reinterpret_cast<const int*>(tp(rt->tl.num_tiles));
+  const int* padded_rows = reinterpret_cast<const int*>(tp(rt->tl.padded_rows));
+  const int* origin = reinterpret_cast<const int*>(tp(rt->tl.origin));
+  const float* prob = reinterpret_cast<const float*>(tp(rt->tl.prob));
+  const auto* xrows = reinterpret_cast<const __nv_bfloat16*>(tp(rt->tl.xrows));
+  const auto* ab = reinterpret_cast<const __nv_bfloat16*>(tp(rt->tl.ab));
+  auto* recv = at<__nv_bfloat16>(S, rt->sl.recv);
+  auto* u = at<__nv_bfloat16>(S, rt->sl.u);
+  auto* du = at<__nv_bfloat16>(S, rt->sl.du);
+  auto* dab = at<__nv_bfloat16>(S, rt->sl.dab);
+
+  PeerConstRows stage{};
+  PeerFloats dgate_box{};
+  PushTarget push{};
+  for (int r = 0; r < world; ++r) {
+    stage.p[r] = at<__nv_bfloat16>(rt->peer[r], rt->al.stage);
+    dgate_box.p[r] = at<float>(rt->peer[r], rt->al.dgate_box);
+    push.mailbox[r] = at<__nv_bfloat16>(rt->peer[r], rt->al.mailbox);
+  }
+  push.origin = origin;
+  push.cap = c.max_tokens;
+  push.top_k = c.top_k;
+
+  // 1. stage dY where the owners can read it.
+  if (world > 1)
+    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, stream)) return rc;
+  if (world == 1)
+    stage.p[0] = static_cast<const __nv_bfloat16*>(dy);  // no peers: owners read dY itself
+  else if (tokens > 0)
+    WM_CUDA(cudaMemcpyAsync(rt->arena + rt->al.stage, dy, 2ull * tokens * c.hidden,
+                            cudaMemcpyDeviceToDevice, stream));
+  if (world > 1) {
+    if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
+  }
+  // 2. owner side: pull dY rows in the saved row order.
+  if (int rc = gather_by_origin(padded_rows, origin, c.max_tokens, c.top_k, c.hidden, stage, recv,
+                                rt->sms, stream))
+    return rc;
+  if (world > 1)
+    if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
+  Schedule sched{num_tiles, tile_group, padded_start, rt->e_local, rt->row_cap};
+  // 3. dU = dY * W2 ; SwiGLU backward (U, dAB, dprob -> sources) ; dX = dAB * W1 -> sources.
+  if (int rc = launch_mgrouped_nn(sched, recv, static_cast<const __nv_bfloat16*>(w2), du, nullptr,
+                                  c.intermediate, c.hidden, status, rt->sms, stream))
+    return rc;
+  if (int rc = swiglu_backward(padded_rows, ab, du, prob, origin, c.intermediate, c.max_tokens,
+                               c.top_k, u, dab, dgate_box, rt->sms, stream))
+    return rc;
+  if (int rc = launch_mgrouped_nn(sched, dab, static_cast<const __nv_bfloat16*>(w1), nullptr, &push,
+                                  c.hidden, 2 * c.intermediate, status, rt->sms, stream))
+    return rc;
+  if (world > 1)
+    if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
+  // 4. weight gradients: reductions over each expert's rows in the saved (fixed) order.
+  if (int rc = launch_kgrouped_tn(sched, dab, xrows, static_cast<__nv_bfloat16*>(dw1),
+                                  2 * c.intermediate, c.hidden, status, rt->sms, stream))
+    return rc;
+  if (int rc = launch_kgrouped_tn(sched, recv, u, static_cast<__nv_bfloat16*>(dw2), c.hidden,
+                                  c.intermediate, status, rt->sms, stream))
+    return rc;
+  // 5. source side: ordered combine of dX, dprob back to the original slots.
+  if (world > 1)
+    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
+  if (int rc = combine_rows(at<__nv_bfloat16>(rt->arena, rt->al.mailbox), sorted_expert, tokens,
+                            c.max_tokens, c.top_k, c.hidden, static_cast<__nv_bfloat16*>(dx), stream))
+    return rc;
+  return unpermute_dgates(at<float>(rt->arena, rt->al.dgate_box), sorted_slot, sorted_expert, tokens,
+                          c.top_k, dgates, stream);
+}
+
+// =============================================================================== stand-alone plan
+extern "C" int wm_route_plan(int32_t phase, int32_t world, int32_t rank, int32_t experts,
+                             int32_t top_k, int32_t tokens, int32_t cap, int32_t row_capacity,
+                             const int32_t* routes, int32_t* count_matrix, const wm_route_out* out,
+                             void* stream_) {
+  if (!out || !count_matrix || world < 1 || world > kMaxWorld || rank < 0 || rank >= world ||
+      experts < 1 || experts % world || experts > 2048 || top_k < 1 || top_k > 32 || tokens < 0 ||
+      tokens > cap || (tokens > 0 && !routes) || row_capacity % 128) {
+    set_error("wm_route_plan: bad argument");
+    return WM_ERR_INVALID;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const size_t n = static_cast<size_t>(tokens) * top_k;
+  const size_t chunks = (n + 1023) / 1024 + 1;
+  Carver k;
+  const size_t o_hist = k.take(sizeof(int) * chunks * experts);
+  const size_t o_pos = k.take(sizeof(int) * (n + 1));
+  const size_t o_cnt = k.take(sizeof(int) * experts);
+  const size_t o_before = k.take(sizeof(int) * experts);
+  const size_t o_status = k.take(sizeof(int));
+  const size_t o_flags = k.take(sizeof(int) * kMaxWorld * kFlagStride);
+  uint8_t* tmp = nullptr;
+  WM_CUDA(cudaMalloc(&tmp, k.cursor));
+  WM_CUDA(cudaMemsetAsync(tmp + o_status, 0, k.cursor - o_status, stream));
+  RouteShape shape{experts, top_k, world, rank, cap};
+  RouteLocal local{out->sorted_slot, out->sorted_expert, at<int>(tmp, o_pos)};
+  PeerInts counts{};
+  for (int r = 0; r < world; ++r) counts.p[r] = count_matrix;  // every "rank" shares one matrix
+  int rc = route_local(shape, routes, tokens, local, at<int>(tmp, o_hist), at<int>(tmp, o_cnt), counts,
+                       stream);
+  int device_code = 0;
+  if (!rc && phase == 1) {
+    PlanTables t{out->expert_total, at<int>(tmp, o_before), out->expert_base, out->expert_pbase,
+                 out->padded_start, out->tile_group, out->num_tiles, out->padded_rows};
+    // No exchange to wait for: generation 0 is satisfied by the zeroed flag words.
+    rc = route_global(shape, count_matrix, at<int>(tmp, o_flags), 0, row_capacity, t,
+                      at<int>(tmp, o_status), stream);
+    RouteRows rows{out->local_offset, out->dst_rank, out->dst_row, out->dst_prow};
+    PeerInts no_origin{};
+    PeerFloats no_prob{};
+    if (!rc)
+      rc = route_rows(shape, routes, nullptr, tokens, local, at<int>(tmp, o_hist), t, rows,
+                      no_origin, no_prob, stream);
+    if (!rc && cudaMemcpyAsync(&device_code, tmp + o_status, sizeof(int), cudaMemcpyDeviceToHost,
+                               stream) != cudaSuccess)
+      rc = WM_ERR_CUDA;
+  }
+  cudaError_t e = cudaStreamSynchronize(stream);
+  cudaFree(tmp);
+  if (rc) return rc;
+  if (e != cudaSuccess) {
+    set_error("wm_route_plan: %s", cudaGetErrorString(e));
+    return WM_ERR_CUDA;
+  }
+  if (device_code) {
+    set_error("wm_route_plan: device status %d", device_code);
+    return map_status(device_code);
+  }
+  return WM_OK;
+}

@@ -1,0 +1,266 @@
+// Activation transport between source ranks (token owners) and expert owners, plus the
+// HBM-bound elementwise stages around the grouped GEMMs.
+//
+// Dispatch is a PULL: the expert owner reads each routed row from the source rank's staging
+// buffer (its own memory at EP1, a CUDA-IPC peer mapping over NVLink otherwise) with 16-byte
+// loads and writes it into its own row buffer.  Return is a PUSH done by the GEMM epilogues
+// (gemm.cuh, EpiloguePush).  Completion is tracked with monotonically growing generation
+// flags, one 128-byte line per (flag kind, peer); nothing is ever reset and every wait is
+// bounded.  Reference dataflow: src/cuda/blackwell/fused/impls/routed_bf16.cuh:378-557
+// (pull), :1147-1306 (combine); weftmoe/blackwell_backward.py:55-176 (gather, SwiGLU
+// backward, return, combine).
+#include "kernels.h"
+#include "ptx.cuh"
+#include "route.h"
+
+namespace wm {
+
+// ------------------------------------------------------------------ flags
+__global__ void wait_flags_kernel(const int* flags, int world, int generation, int* status) {
+  if (threadIdx.x < world) wait_flag_ge(flags + threadIdx.x * kFlagStride, generation, status);
+}
+__global__ void signal_peers_kernel(PeerInts group, int world, int slot, int generation) {
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(group.p[threadIdx.x] + slot * kFlagStride, generation);
+  }
+}
+int wait_flags(const int* flags, int world, int generation, int* status, cudaStream_t stream) {
+  wait_flags_kernel<<<1, 32, 0, stream>>>(flags, world, generation, status);
+  WM_CUDA(cudaGetLastError());
+  return 0;
+}
+int signal_peers(const PeerInts& group, int world, int slot, int generation, cudaStream_t stream) {
+  signal_peers_kernel<<<1, 32, 0, stream>>>(group, world, slot, generation);
+  WM_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// ------------------------------------------------------------------ row copies
+// One warp copies one row of `vecs` uint4 (16 B) words; up to four loads in flight per lane.
+__device__ __forceinline__ void copy_row(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                         int vecs, int lane) {
+  for (int c = lane; c < vecs; c += 128) {
+    uint4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (c + 32 * j < vecs) v[j] = src[c + 32 * j];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (c + 32 * j < vecs) dst[c + 32 * j] = v[j];
+  }
+}
+__device__ __forceinline__ void zero_row(uint4* __restrict__ dst, int vecs, int lane) {
+  for (int c = lane; c < vecs; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+}
+
+__global__ void gather_rows_kernel(OwnerRows o, int rank, int e_local, int cap, int top_k,
+                                   int hidden, PeerConstRows stage,
+                                   const int* __restrict__ meta_origin,
+                                   const float* __restrict__ meta_prob,
+                                   __nv_bfloat16* __restrict__ rows_out,
+                                   int* __restrict__ origin_out, float* __restrict__ prob_out) {
+  const int rows = *o.padded_rows;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int vecs = hidden / 8;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+    const int l = o.tile_group[r >> 7];
+    const int within = r - o.padded_start[l];
+    const bool live = within < o.expert_total[rank * e_local + l];
+    uint4* dst = reinterpret_cast<uint4*>(rows_out + static_cast<size_t>(r) * hidden);
+    if (live) {
+      const int org = meta_origin[r];
+      const int src = org / (cap * top_k);
+      const int token = (org - src * cap * top_k) / top_k;
+      copy_row(reinterpret_cast<const uint4*>(stage.p[src] + static_cast<size_t>(token) * hidden),
+               dst, vecs, lane);
+      if (lane == 0) {
+        origin_out[r] = org;
+        prob_out[r] = meta_prob[r];
+      }
+    } else {
+      zero_row(dst, vecs, lane);
+      if (lane == 0) {
+        origin_out[r] = -1;
+        prob_out[r] = 0.0f;
+      }
+    }
+  }
+}
+
+__global__ void gather_by_origin_kernel(const int* padded_rows, const int* __restrict__ origin,
+                                        int cap, int top_k, int hidden, PeerConstRows stage,
+                                        __nv_bfloat16* __restrict__ rows_out) {
+  const int rows = *padded_rows;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int vecs = hidden / 8;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+    const int org = origin[r];
+    uint4* dst = reinterpret_cast<uint4*>(rows_out + static_cast<size_t>(r) * hidden);
+    if (org >= 0) {
+      const int src = org / (cap * top_k);
+      const int token = (org - src * cap * top_k) / top_k;
+      copy_row(reinterpret_cast<const uint4*>(stage.p[src] + static_cast<size_t>(token) * hidden),
+               dst, vecs, lane);
+    } else {
+      zero_row(dst, vecs, lane);
+    }
+  }
+}
+
+int gather_rows(const OwnerRows& o, int rank, int e_local, int cap, int top_k, int hidden,
+                const PeerConstRows& stage, const int* meta_origin, const float* meta_prob,
+                __nv_bfloat16* rows_out, int* origin_out, float* prob_out, int sms,
+                cudaStream_t stream) {
+  gather_rows_kernel<<<sms * 8, 256, 0, stream>>>(o, rank, e_local, cap, top_k, hidden, stage,
+                                                  meta_origin, meta_prob, rows_out, origin_out,
+                                                  prob_out);
+  WM_CUDA(cudaGetLastError());
+  return 0;
+}
+int gather_by_origin(const int* padded_rows, const int* origin, int cap, int top_k, int hidden,
+                     const PeerConstRows& stage, __nv_bfloat16* rows_out, int sms,
+                     cudaStream_t stream) {
+  gather_by_origin_kernel<<<sms * 8, 256, 0, stream>>>(padded_rows, origin, cap, top_k, hidden,
+                                                       stage, rows_out);
+  WM_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// ------------------------------------------------------------------ combine
+// One CTA per token; each thread owns 8 consecutive columns.  Contributions are added in
+// ascending combine position with sequential FP32 adds: the order defines the bits
+// (reference: routed_bf16.cuh:1209-1306, fused/ptx/utils.cuh:70-79).
+__global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ mailbox,
+                                    const int* __restrict__ sorted_expert, int cap, int top_k,
+                                    int hidden, __nv_bfloat16* __restrict__ out) {
+  const int t = blockIdx.x;
+  const int vecs = hidden / 8;
+  for (int c = threadIdx.x; c < vecs; c += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+    for (int j = 0; j < top_k; ++j) {
+      if (sorted_expert[t * top_k + j] < 0) continue;
+      const uint4 v = *reinterpret_cast<const uint4*>(
+          mailbox + (static_cast<size_t>(j) * cap + t) * hidden + c * 8);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        acc[2 * k] += __uint_as_float(w[k] << 16);
+        acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+      }
+    }
+    uint4 r;
+    r.x = pack_bf16x2(acc[0], acc[1]);
+    r.y = pack_bf16x2(acc[2], acc[3]);
+    r.z = pack_bf16x2(acc[4], acc[5]);
+    r.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * hidden + c * 8) = r;
+  }
+}
+int combine_rows(const __nv_bfloat16* mailbox, const int* sorted_expert, int tokens, int cap,
+                 int top_k, int hidden, __nv_bfloat16* out, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  const int threads = hidden / 8 >= 256 ? 256 : ((hidden / 8 + 31) / 32 * 32);
+  combine_rows_kernel<<<tokens, threads, 0, stream>>>(mailbox, sorted_expert, cap, top_k, hidden,
+                                                      out);
+  WM_CUDA(cudaGetLastError());
+  return 0;
+}
+
+__global__ void unpermute_dgates_kernel(const float* __restrict__ box,
+                                        const int* __restrict__ sorted_slot,
+                                        const int* __restrict__ sorted_expert, int n, int top_k,
+                                        float* __restrict__ dgates) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int t = i / top_k;
+  dgates[t * top_k + sorted_slot[i]] = sorted_expert[i] >= 0 ? box[i] : 0.0f;
+}
+int unpermute_dgates(const float* dgate_box, const int* sorted_slot, const int* sorted_expert,
+                     int tokens, int top_k, float* dgates, cudaStream_t stream) {
+  const int n = tokens * top_k;
+  if (n == 0) return 0;
+  unpermute_dgates_kernel<<<(n + 255) / 256, 256, 0, stream>>>(dgate_box, sorted_slot,
+                                                               sorted_expert, n, top_k, dgates);
+  WM_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// ------------------------------------------------------------------ SwiGLU backward
+// One warp per routed row (reference math: weftmoe/blackwell_backward.py:81-113):
+//   sig = sigmoid(a); silu = a*sig; U = bf16(silu*b*p)
+//   dA = bf16(dU*p*b*sig*(1+a*(1-sig))); dB = bf16(dU*p*silu); dprob = sum_i dU_i*silu_i*b_i
+// The row sum uses a fixed lane->column assignment and a fixed shuffle tree: deterministic.
+__global__ void swiglu_backward_kernel(const int* padded_rows, const __nv_bfloat16* __restrict__ ab,
+                                       const __nv_bfloat16* __restrict__ du,
+                                       const float* __restrict__ prob,
+                                       const int* __restrict__ origin, int inter, int cap,
+                                       int top_k, __nv_bfloat16* __restrict__ u,
+                                       __nv_bfloat16* __restrict__ dab, PeerFloats dgate_box) {
+  const int rows = *padded_rows;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int vecs = inter / 8;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+    const float p = prob[r];
+    const uint4* pa = reinterpret_cast<const uint4*>(ab + static_cast<size_t>(r) * 2 * inter);
+    const uint4* pb = pa + vecs;
+    const uint4* pdu = reinterpret_cast<const uint4*>(du + static_cast<size_t>(r) * inter);
+    uint4* pu = reinterpret_cast<uint4*>(u + static_cast<size_t>(r) * inter);
+    uint4* pda = reinterpret_cast<uint4*>(dab + static_cast<size_t>(r) * 2 * inter);
+    uint4* pdb = pda + vecs;
+    float dsum = 0.0f;
+    for (int c = lane; c < vecs; c += 32) {
+      const uint4 va = pa[c], vb = pb[c], vd = pdu[c];
+      const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w},
+                     wd[4] = {vd.x, vd.y, vd.z, vd.w};
+      uint32_t ou[4], oa[4], ob[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float res_u[2], res_a[2], res_b[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float a = __uint_as_float(h ? (wa[k] & 0xffff0000u) : (wa[k] << 16));
+          const float b = __uint_as_float(h ? (wb[k] & 0xffff0000u) : (wb[k] << 16));
+          const float d = __uint_as_float(h ? (wd[k] & 0xffff0000u) : (wd[k] << 16));
+          const float sig = 1.0f / (1.0f + __expf(-a));
+          const float silu = a * sig;
+          const float act = silu * b;
+          res_u[h] = act * p;
+          res_a[h] = d * p * b * (sig * (1.0f + a * (1.0f - sig)));
+          res_b[h] = d * p * silu;
+          dsum += d * act;
+        }
+        ou[k] = pack_bf16x2(res_u[0], res_u[1]);
+        oa[k] = pack_bf16x2(res_a[0], res_a[1]);
+        ob[k] = pack_bf16x2(res_b[0], res_b[1]);
+      }
+      pu[c] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+      pda[c] = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+      pdb[c] = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, d);
+    const int org = origin[r];
+    if (lane == 0 && org >= 0) {
+      const int per = cap * top_k;
+      const int src = org / per;
+      dgate_box.p[src][org - src * per] = dsum;
+    }
+  }
+}
+int swiglu_backward(const int* padded_rows, const __nv_bfloat16* ab, const __nv_bfloat16* du,
+                    const float* prob, const int* origin, int inter, int cap, int top_k,
+                    __nv_bfloat16* u, __nv_bfloat16* dab, const PeerFloats& dgate_box, int sms,
+                    cudaStream_t stream) {
+  swiglu_backward_kernel<<<sms * 8, 256, 0, stream>>>(padded_rows, ab, du, prob, origin, inter, cap,
+                                                      top_k, u, dab, dgate_box);
+  WM_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace wm

@@ -1,0 +1,445 @@
+"""Tensor API of the routed-MoE expert operator: one persistent native workspace per EP group.
+
+Mirror of the reference's `weftmoe/runtime.py` (`TensorRuntime` :23-464, `_MoE` :467-479, `moe`
+:506-512) with the same constructor keywords, method names, argument meaning and error
+behaviour, over the C ABI in include/weftmoe_b200.h.  `NativeRuntime` plays the part of the
+reference's Blackwell backend object (`weftmoe/blackwell.py:51-178`).  PyTorch is used for
+tensors, streams and the bootstrap collectives only; all compute is in libweftmoe_b200.so.
+
+Preparation is collective: all ranks of the group construct the runtime and call layers in the
+same order.  Expert weights are BF16 [local_experts, 2*intermediate, hidden] (rows 0..I-1 gate,
+I..2I-1 up) and [local_experts, hidden, intermediate].
+"""
+from __future__ import annotations
+
+import ctypes
+import socket
+import weakref
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+class SingleRankGroup:
+    """Stand-in for a one-rank process group, so EP1 needs no torch.distributed initialisation.
+
+    The reference forms its EP1 groups with `dist.new_subgroups(group_size=1)`
+    (tests/torchrun_sm100_invariant.py:27); a real one-rank ProcessGroup works here too."""
+
+    def size(self):
+        return 1
+
+    def rank(self):
+        return 0
+
+
+class _Collectives:
+    """The few bootstrap collectives the runtime needs, over a real group or SingleRankGroup."""
+
+    def __init__(self, group):
+        self.group = group
+        self.single = isinstance(group, SingleRankGroup)
+        self.rank = 0 if self.single else dist.get_rank(group)
+        self.world = 1 if self.single else dist.get_world_size(group)
+
+    def all_gather_object(self, value):
+        if self.single:
+            return [value]
+        out = [None] * self.world
+        dist.all_gather_object(out, value, group=self.group)
+        return out
+
+    def barrier(self):
+        if not self.single:
+            dist.barrier(group=self.group)
+
+
+@dataclass(eq=False)
+class Tape:
+    """Result of a training forward: `output` plus the cache backward consumes
+    (reference: weftmoe/blackwell_backward.py:14-17; src/python/runtime.cpp:880-906)."""
+    output: torch.Tensor
+    state: tuple | None = None
+
+    @property
+    def tensor_bytes(self):
+        return 0 if self.state is None else self.state[0].numel()
+
+    @property
+    def saved_x_bytes(self):
+        return 0 if self.state is None else self.state[-1]
+
+
+class NativeRuntime:
+    """Owner of one `wm_runtime` handle; serialised on the supplied CUDA stream."""
+
+    def __init__(self, collectives, experts, top_k, hidden, intermediate, max_tokens, max_rows,
+                 stream, training, max_saved):
+        self.lib = _lib.load()
+        self.col = collectives
+        # A legacy default stream cannot join a caller's CUDA Graph capture
+        # (same rule as weftmoe/blackwell.py:60-64).
+        self.stream = (torch.cuda.Stream(device=stream.device)
+                       if not training and stream == torch.cuda.default_stream(stream.device)
+                       else stream)
+        self.training, self.max_saved = training, max_saved
+        self.tapes = weakref.WeakSet()
+        self.shape = (experts, top_k, hidden, intermediate)
+        self.local_experts = experts // collectives.world
+        config = _lib.WmConfig(rank=collectives.rank, world=collectives.world, experts=experts,
+                               top_k=top_k, hidden=hidden, intermediate=intermediate,
+                               max_tokens=max_tokens, max_rows=max_rows, training=int(training),
+                               reserved=0)
+        handle = ctypes.c_void_p()
+        # Agree on the outcome of local preparation before any rank touches a peer mapping.
+        error = None
+        try:
+            with torch.cuda.device(stream.device):
+                _lib.check(self.lib.wm_runtime_create(ctypes.byref(config), ctypes.byref(handle)))
+        except (ValueError, RuntimeError) as exc:
+            error = f"{type(exc).__name__}: {exc}"
+        errors = collectives.all_gather_object(error)
+        if any(errors):
+            if handle:
+                self.lib.wm_runtime_destroy(handle)
+            kind = ValueError if all(e is None or e.startswith("ValueError") for e in errors) else RuntimeError
+            raise kind(f"collective preparation failed: {[e for e in errors if e]}")
+        self.handle = handle
+        self.sizes = _lib.WmSizes()
+        _lib.check(self.lib.wm_runtime_sizes(self.handle, ctypes.byref(self.sizes)))
+        if collectives.world > 1:
+            n = self.sizes.ipc_handle_bytes
+            mine = ctypes.create_string_buffer(n)
+            _lib.check(self.lib.wm_runtime_export_handle(self.handle, mine, n))
+            blob = b"".join(collectives.all_gather_object(mine.raw))
+            with torch.cuda.device(stream.device):
+                _lib.check(self.lib.wm_runtime_import_peers(self.handle, blob, len(blob)))
+            collectives.barrier()
+
+    # ------------------------------------------------------------------ helpers
+    def _require(self):
+        if self.handle is None:
+            raise RuntimeError("WeftMoE runtime is closed")
+
+    def _poll(self):
+        code = ctypes.c_int32(0)
+        _lib.check(self.lib.wm_status_poll(self.handle, ctypes.byref(code), self.stream.cuda_stream))
+        _lib.check(code.value)
+
+    def _run(self, x, routes, gates, w1, w2, *, save=False):
+        self._require()
+        caller = torch.cuda.current_stream()
+        if caller.device != self.stream.device or x.device != self.stream.device:
+            raise ValueError("Workspace and tensors must share the current device")
+        if caller != self.stream:
+            self.stream.wait_stream(caller)
+        with torch.cuda.stream(self.stream):
+            y = torch.empty_like(x)
+            blob = None
+            if save:
+                if len(self.tapes) >= self.max_saved:
+                    raise RuntimeError("Blackwell training tape capacity exhausted")
+                blob = torch.empty(self.sizes.tape_bytes, dtype=torch.uint8, device=x.device)
+            _lib.check(self.lib.wm_forward(self.handle, _lib.ptr(x), _lib.ptr(routes), _lib.ptr(gates),
+                                           _lib.ptr(w1), _lib.ptr(w2), x.shape[0], _lib.ptr(y),
+                                           _lib.ptr(blob), self.stream.cuda_stream))
+            if caller != self.stream:
+                for tensor in (x, routes, gates, w1, w2):
+                    tensor.record_stream(self.stream)
+                y.record_stream(caller)
+        if caller != self.stream:
+            caller.wait_stream(self.stream)
+        if not save:
+            return y
+        saved_x = 2 * self.sizes.row_capacity * self.shape[2]
+        tape = Tape(y, (blob, w1, w2, x.shape[0], saved_x))
+        self.tapes.add(tape)
+        return tape
+
+    # ------------------------------------------------------------------ training
+    def forward_async(self, x, routes, gates, w1, w2, retain_backward_state=True):
+        if self.training and retain_backward_state:
+            return self._run(x, routes, gates, w1, w2, save=True)
+        return Tape(self._run(x, routes, gates, w1, w2))
+
+    def forward(self, x, routes, gates, w1, w2):
+        tape = self.forward_async(x, routes, gates, w1, w2)
+        self._poll()
+        return tape
+
+    def backward_async(self, tape, dy):
+        self._require()
+        if tape not in self.tapes or tape.state is None:
+            raise RuntimeError("Backward requires a live training tape from this runtime")
+        blob, w1, w2, tokens, _ = tape.state
+        if dy.dtype != torch.bfloat16 or dy.shape != tape.output.shape or dy.device != blob.device:
+            raise ValueError("Backward requires BF16 dY matching the forward output")
+        k = self.shape[1]
+        dx = torch.empty_like(dy)
+        dgates = torch.empty((tokens, k), dtype=torch.float32, device=dy.device)
+        dw1, dw2 = torch.empty_like(w1), torch.empty_like(w2)
+        _lib.check(self.lib.wm_backward(self.handle, _lib.ptr(blob), _lib.ptr(dy), _lib.ptr(w1),
+                                        _lib.ptr(w2), tokens, _lib.ptr(dx), _lib.ptr(dgates),
+                                        _lib.ptr(dw1), _lib.ptr(dw2), self.stream.cuda_stream))
+        tape.state = None
+        self.tapes.discard(tape)
+        return dx, dgates, dw1, dw2
+
+    def backward(self, tape, dy):
+        result = self.backward_async(tape, dy)
+        self._poll()
+        return result
+
+    # ------------------------------------------------------------------ inference
+    def graph_forward(self, layer, x, routes, gates, w1, w2, caller_stream):
+        return self._run(x, routes, gates, w1, w2)
+
+    def eager_inference_async(self, x, routes, gates, w1, w2, caller_stream, layer=None):
+        return self._run(x, routes, gates, w1, w2)
+
+    def eager_inference(self, x, routes, gates, w1, w2, caller_stream, layer=None):
+        output = self._run(x, routes, gates, w1, w2)
+        self._poll()
+        return output
+
+    def invalidate_inference_layer(self, layer, caller_stream):
+        self.stream.synchronize()
+
+    # ------------------------------------------------------------------ lifecycle
+    def drain_eager_inference(self):
+        if self.handle is not None:
+            self._poll()
+
+    def drain_training(self):
+        if self.handle is not None:
+            self._poll()
+
+    def usage(self):
+        return dict(notify_slots_in_use=len(self.tapes), symmetric_bytes=int(self.sizes.arena_bytes),
+                    scratch_bytes=int(self.sizes.scratch_bytes), tape_bytes=int(self.sizes.tape_bytes),
+                    row_capacity=int(self.sizes.row_capacity))
+
+    def session(self):
+        return None
+
+    def retire_peer_mappings(self):
+        if self.handle is not None:
+            self.lib.wm_runtime_retire_peers(self.handle)
+
+    def destroy(self):
+        if self.handle is not None:
+            self.lib.wm_runtime_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+class TensorRuntime:
+    def __init__(
+        self,
+        *,
+        group,
+        experts: int,
+        top_k: int,
+        hidden: int,
+        intermediate: int,
+        max_tokens: int,
+        max_rows: int,
+        training: bool,
+        max_saved: int = 64,
+        stream=None,
+        input_layout: str = "dp",
+        interconnect: str | None = None,
+        decode_only: bool = False,
+        fp8_workspace: bool = False,
+        precision: str | None = None,
+        nvfp4_scales=None,
+        session=None,
+        batch_invariant: bool = True,
+        allow_unvalidated_shape: bool = False,
+        _native_factory=None,
+    ):
+        if group is None:
+            raise ValueError("Pass the explicit expert process group")
+        self.group = group
+        col = self._collectives = _Collectives(group)
+        self.rank, self.world = col.rank, col.world
+        hosts = col.all_gather_object(socket.gethostname())
+        ordered_hosts = list(dict.fromkeys(hosts))
+        self.nodes = len(ordered_hosts)
+        expected = [host for host in ordered_hosts for _ in range(self.world // self.nodes)]
+        if hosts != expected:
+            raise ValueError("WeftMoE requires equal-size, contiguous node-local EP teams")
+        self.experts, self.top_k = experts, top_k
+        self.hidden, self.intermediate = hidden, intermediate
+        self.training = training
+        self.decode_only = decode_only
+        self.fp8_workspace = fp8_workspace
+        self.precision = precision or ("fp8" if fp8_workspace else "bf16")
+        self.max_tokens = max_tokens
+        self.stream = stream
+        if self.stream is None:
+            self.stream = torch.cuda.current_stream() if training else torch.cuda.Stream()
+        # Agree before any native collective: a bad shape on one rank must be a collective error,
+        # not a peer stranded in the handle exchange (reference: weftmoe/runtime.py:83-105).
+        request = dict(
+            precision=self.precision, nvfp4_scales=nvfp4_scales, experts=experts, top_k=top_k,
+            hidden=hidden, intermediate=intermediate, max_tokens=max_tokens, max_rows=max_rows,
+            max_saved=max_saved, training=training, batch_invariant=batch_invariant,
+            fp8_workspace=fp8_workspace, decode_only=decode_only, input_layout=input_layout,
+        )
+        requests = col.all_gather_object(request)
+        if any(r != request for r in requests):
+            raise ValueError("EP ranks requested incompatible WeftMoE configurations")
+        if nvfp4_scales is not None and self.precision != "nvfp4":
+            raise ValueError("nvfp4_scales requires NVFP4 precision")
+        if self.nodes != 1:
+            raise ValueError("This build serves one NVLink node: EP ranks must share a host")
+        if self.precision not in ("bf16",) or fp8_workspace or input_layout != "dp":
+            raise ValueError("Blackwell requires DP-sharded BF16 or NVFP4")
+        if hidden > 4096 and hidden % 512:
+            raise ValueError("Blackwell combine requires hidden divisible by 512 when hidden > 4096")
+        if (max_tokens < 0 or hidden < 256 or hidden % 256 or not 128 <= intermediate <= 4096
+                or intermediate % 128 or experts % self.world or not 1 <= top_k <= min(32, experts)
+                or experts > 2048 or experts // self.world > 512
+                or self.world not in (1, 2, 4, 8)):
+            raise ValueError("Unsupported Blackwell expert shape or token capacity")
+        factory = _native_factory or NativeRuntime
+        self.native = factory(col, experts, top_k, hidden, intermediate, max_tokens, max_rows,
+                              self.stream, training, max_saved if training else 1)
+        self.stream = getattr(self.native, "stream", self.stream)
+        self.compilation = None
+
+    def _check(self, x, routes, gates, w1, w2):
+        if self.native is None:
+            raise RuntimeError("WeftMoE runtime is closed")
+        if self.fp8_workspace:
+            raise ValueError("Compact FP8 workspace requires forward_fp8 or moe(..., fp8_weights=...)")
+        if self.training and torch.cuda.current_stream() != self.stream:
+            raise RuntimeError("Runtime must be invoked on its preparation stream")
+        if x.ndim != 2 or x.shape[1] != self.hidden or x.shape[0] > self.max_tokens:
+            raise ValueError("Activation shape exceeds prepared capacity")
+        shapes = (
+            (x.shape[0], self.top_k),
+            (x.shape[0], self.top_k),
+            (self.experts // self.world, 2 * self.intermediate, self.hidden),
+            (self.experts // self.world, self.hidden, self.intermediate),
+        )
+        for tensor, shape in zip((routes, gates, w1, w2), shapes):
+            if tensor.shape != shape:
+                raise ValueError(f"Expected {shape}, got {tuple(tensor.shape)}")
+        for tensor, dtype in zip((x, routes, gates, w1, w2),
+                                 (torch.bfloat16, torch.int32, torch.float32, torch.bfloat16,
+                                  torch.bfloat16)):
+            if (tensor.dtype != dtype or tensor.device != x.device or not tensor.is_cuda
+                    or not tensor.is_contiguous()):
+                raise ValueError(f"Expected contiguous CUDA {dtype} on {x.device}")
+
+    def forward(self, x, routes, gates, w1, w2):
+        self._check(x, routes, gates, w1, w2)
+        return self.native.forward(x, routes, gates, w1, w2)
+
+    def forward_async(self, x, routes, gates, w1, w2, *, retain_backward_state=True):
+        """Enqueue FWD, optionally omitting X/AB for checkpoint's no-grad pass."""
+        self._check(x, routes, gates, w1, w2)
+        return self.native.forward_async(x, routes, gates, w1, w2, retain_backward_state)
+
+    def _check_dy(self, dy):
+        if not isinstance(dy, torch.Tensor) or dy.dtype != torch.bfloat16:
+            raise ValueError("Source must be BF16 or FP8Tensor with explicit row scales")
+        if (dy.ndim != 2 or dy.shape[1] != self.hidden or dy.shape[0] > self.max_tokens
+                or not dy.is_cuda or not dy.is_contiguous() or dy.device != self.stream.device):
+            raise ValueError("Source shape/device/layout does not match runtime")
+
+    def backward(self, tape, dy):
+        """Consume BF16 dY; returns (dx, dgates, dw1, dw2)."""
+        if torch.cuda.current_stream() != self.stream:
+            raise RuntimeError("Backward must use the preparation stream")
+        dy = dy.contiguous() if isinstance(dy, torch.Tensor) else dy
+        self._check_dy(dy)
+        return self.native.backward(tape, dy)
+
+    def backward_async(self, tape, dy):
+        """Return stream-ordered gradients without waiting."""
+        if torch.cuda.current_stream() != self.stream:
+            raise RuntimeError("Backward must use the preparation stream")
+        dy = dy.contiguous() if isinstance(dy, torch.Tensor) else dy
+        self._check_dy(dy)
+        return self.native.backward_async(tape, dy)
+
+    def forward_fp8(self, x, routes, gates, weights, *, synchronize=True,
+                    retain_backward_state=True, weight_grad_dtype=torch.float32):
+        raise ValueError("Blackwell requires DP-sharded BF16 or NVFP4")
+
+    def drain(self):
+        """Finish the pending training call before inspecting or releasing leases."""
+        self.native.drain_training()
+
+    def inference(self, layer, x, routes, gates, w1, w2):
+        self._check(x, routes, gates, w1, w2)
+        return self.native.graph_forward(layer, x, routes, gates, w1, w2,
+                                         torch.cuda.current_stream().cuda_stream)
+
+    def inference_eager(self, x, routes, gates, w1, w2, *, layer=None):
+        """Run changing inputs/routes; `layer` is accepted for API compatibility."""
+        self._check(x, routes, gates, w1, w2)
+        return self.native.eager_inference(x, routes, gates, w1, w2,
+                                           torch.cuda.current_stream().cuda_stream,
+                                           *(() if layer is None else (layer,)))
+
+    def inference_eager_async(self, x, routes, gates, w1, w2, *, layer=None):
+        self._check(x, routes, gates, w1, w2)
+        return self.native.eager_inference_async(x, routes, gates, w1, w2,
+                                                 torch.cuda.current_stream().cuda_stream,
+                                                 *(() if layer is None else (layer,)))
+
+    def invalidate_inference_layer(self, layer):
+        self.native.invalidate_inference_layer(layer, torch.cuda.current_stream().cuda_stream)
+
+    def close(self):
+        """Collectively release native CUDA/IPC storage at a phase boundary."""
+        if self.native is None:
+            return
+        torch.cuda.synchronize()
+        self.drain()
+        self.native.drain_eager_inference()
+        if self.training and self.native.usage()["notify_slots_in_use"]:
+            raise RuntimeError("Live backward tapes prevent closing the runtime")
+        self._collectives.barrier()
+        self.native.retire_peer_mappings()
+        # No exporter may free its storage while another rank still has an IPC import.
+        self._collectives.barrier()
+        if hasattr(self.native, "destroy"):
+            self.native.destroy()
+        self.native = None
+
+
+class _MoE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, runtime, x, routes, gates, w1, w2):
+        ctx.runtime = runtime
+        ctx.tape = runtime.forward(x, routes, gates, w1, w2)
+        return ctx.tape.output
+
+    @staticmethod
+    def backward(ctx, dy):
+        dx, dg, dw1, dw2 = ctx.runtime.backward(ctx.tape, dy)
+        ctx.tape = None
+        ctx.runtime = None
+        return None, dx, None, dg, dw1, dw2
+
+
+def moe(runtime, x, routes, gates, w1, w2, *, fp8_weights=None):
+    """Apply the fused operation, preserving router and expert autograd edges."""
+    if torch.is_grad_enabled() and not runtime.training:
+        raise ValueError("Autograd requires a runtime prepared with training=True")
+    if fp8_weights is not None:
+        raise ValueError("Blackwell requires DP-sharded BF16 or NVFP4")
+    return _MoE.apply(runtime, x, routes, gates, w1, w2)
