@@ -1,0 +1,189 @@
+"""GPU: the routed-MoE layer through the public Tensor API (which calls the C ABI) against the CPU
+oracle, the reference's golden vectors, and the reference's invariance protocol
+(tests/torchrun_sm100_invariant.py: repeat / reversal / prefix / interleaved tapes)."""
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+from tests.gpu_util import rel_l2
+from weftmoe_b200 import SingleRankGroup, TensorRuntime, moe
+
+pytestmark = pytest.mark.gpu
+
+# BF16 contract: within 1e-2 relative of an FP32 reference (the reference's own acceptance is
+# relative_l2 < 0.01, benchmarks/training_reference.py:68-74).  Against the oracle that applies
+# the same BF16 rounding points the agreement is an order of magnitude tighter.
+TOL_FP32_REFERENCE = 1e-2
+TOL_ROUNDED_ORACLE = 2e-3
+
+
+def runtime(cfg, tokens, training=True, **kw):
+    return TensorRuntime(group=SingleRankGroup(), experts=cfg["experts"], top_k=cfg["top_k"],
+                         hidden=cfg["hidden"], intermediate=cfg["intermediate"], max_tokens=tokens,
+                         max_rows=tokens * cfg["top_k"], training=training, **kw)
+
+
+def on_gpu(d):
+    return {k: v.cuda() for k, v in d.items()}
+
+
+def bits(t):
+    return t.contiguous().view(torch.int16 if t.dtype == torch.bfloat16 else torch.int32)
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(experts=8, top_k=2, hidden=512, intermediate=512, tokens=256),      # BASELINE config 0 shape
+    dict(experts=16, top_k=4, hidden=768, intermediate=384, tokens=301),     # 128-wide N tiles, ragged T
+    dict(experts=32, top_k=8, hidden=2048, intermediate=512, tokens=96),     # mostly idle experts
+    dict(experts=4, top_k=1, hidden=256, intermediate=128, tokens=5),
+])
+def test_forward_backward_against_oracle(cfg):
+    d = O.make_inputs(cfg, seed=1, bias_std=0.5)
+    if cfg["tokens"] > 3:
+        d["routes"][0] = 3 % cfg["experts"]   # every slot collides on one expert
+        d["routes"][1] = -1                   # a token without routes
+        d["routes"][2, 0] = -1
+    g = on_gpu(d)
+    rt = runtime(cfg, cfg["tokens"])
+    tape = rt.forward(g["x"], g["routes"], g["gates"], g["w1"], g["w2"])
+    grads = rt.backward(tape, g["dy"])
+    rounded = O.moe_layer(d["x"], d["routes"], d["gates"], d["w1"], d["w2"], d["dy"], precision="bf16")
+    exact = O.moe_layer(d["x"], d["routes"], d["gates"], d["w1"], d["w2"], d["dy"], precision="fp32")
+    for name, mine, r, e in zip(("y", "dx", "dgates", "dw1", "dw2"), (tape.output, *grads), rounded, exact):
+        assert rel_l2(mine, r) < TOL_ROUNDED_ORACLE, (name, rel_l2(mine, r))
+        assert rel_l2(mine, e) < TOL_FP32_REFERENCE, (name, rel_l2(mine, e))
+    if cfg["tokens"] > 3:
+        assert (tape.output[1] == 0).all() and (grads[0][1] == 0).all() and (grads[1][1] == 0).all()
+    rt.close()
+
+
+def test_reference_golden_vectors(golden):
+    g = torch.load(golden / "moe_small.pt")["bf16"]
+    cfg = dict(experts=g["w1"].shape[0], top_k=g["routes"].shape[1], hidden=g["x"].shape[1],
+               intermediate=g["w2"].shape[2])
+    rt = runtime(cfg, g["x"].shape[0])
+    c = on_gpu({k: g[k] for k in ("x", "routes", "gates", "w1", "w2", "dy")})
+    tape = rt.forward(c["x"], c["routes"], c["gates"], c["w1"], c["w2"])
+    grads = rt.backward(tape, c["dy"])
+    for name, mine in zip(("y", "dx", "dgates", "dw1", "dw2"), (tape.output, *grads)):
+        assert rel_l2(mine, g[name]) < TOL_FP32_REFERENCE, (name, rel_l2(mine, g[name]))
+    rt.close()
+
+
+def test_forward_is_batch_invariant_and_repeatable():
+    """Repeat, reversal permutation and prefix truncation keep every output bit
+    (tests/torchrun_sm100_invariant.py:52-60)."""
+    cfg = dict(experts=64, top_k=8, hidden=2048, intermediate=512, tokens=128)
+    d = O.make_inputs(cfg, seed=27, x_std=0.03, w_std=0.03)
+    d["routes"][0] = 3
+    d["routes"][1] = -1
+    g = on_gpu(d)
+    rt = runtime(cfg, cfg["tokens"], training=False)
+    args = (g["w1"], g["w2"])
+    local = (g["x"], g["routes"], g["gates"])
+    y = rt.inference_eager(*local, *args)
+    assert torch.equal(bits(rt.inference_eager(*local, *args)), bits(y))
+    perm = torch.arange(cfg["tokens"] - 1, -1, -1, device="cuda")
+    z = rt.inference_eager(*(v[perm].contiguous() for v in local), *args)
+    assert torch.equal(bits(y)[perm], bits(z))
+    short = cfg["tokens"] // 2
+    prefix = rt.inference_eager(*(v[:short].contiguous() for v in local), *args)
+    assert torch.equal(bits(prefix), bits(y[:short]))
+    # co-batched strangers: the same tokens inside a larger batch
+    rt2 = runtime(cfg, 3 * cfg["tokens"], training=False)
+    extra = on_gpu(O.make_inputs(dict(cfg, tokens=2 * cfg["tokens"]), seed=99, x_std=0.03, w_std=0.03))
+    big = tuple(torch.cat([extra[k][:cfg["tokens"]], g[k], extra[k][cfg["tokens"]:]]) for k in ("x", "routes", "gates"))
+    w = rt2.inference_eager(*big, *args)
+    assert torch.equal(bits(w[cfg["tokens"]:2 * cfg["tokens"]]), bits(y))
+    rt.close()
+    rt2.close()
+
+
+def test_training_forward_equals_inference_and_backward_repeats_bitwise():
+    """Two interleaved live tapes, repeated twice: all five tensors identical bit for bit
+    (tests/torchrun_sm100_invariant.py:72-112)."""
+    cfg = dict(experts=64, top_k=8, hidden=2048, intermediate=512, tokens=40)
+    d = O.make_inputs(cfg, seed=53, x_std=0.03, w_std=0.03)
+    d["routes"][:1] = 3
+    d["routes"][1:2] = -1
+    d["routes"].clamp_(max=cfg["experts"] - 2)  # one expert stays idle
+    g = on_gpu(d)
+    rt = runtime(cfg, cfg["tokens"], max_saved=2)
+    expected = None
+    for _ in range(2):
+        t = rt.forward_async(g["x"], g["routes"], g["gates"], g["w1"], g["w2"])
+        other = rt.forward_async(g["x"], g["routes"].roll(1, dims=1).contiguous(), g["gates"], g["w1"], g["w2"])
+        rt.backward_async(other, g["dy"])
+        result = (t.output, *rt.backward_async(t, g["dy"]))
+        if expected is None:
+            expected = tuple(v.clone() for v in result)
+        else:
+            for actual, ref in zip(result, expected):
+                assert torch.equal(actual.view(torch.uint8), ref.view(torch.uint8))
+    assert (expected[3][-1] == 0).all() and (expected[4][-1] == 0).all()  # idle expert: zero dW
+    rt.close()
+    inf = runtime(cfg, cfg["tokens"], training=False)
+    y = inf.inference_eager(g["x"], g["routes"], g["gates"], g["w1"], g["w2"])
+    assert torch.equal(bits(y), bits(expected[0]))
+    inf.close()
+
+
+def test_zero_tokens_and_autograd_entry_point():
+    cfg = dict(experts=8, top_k=2, hidden=256, intermediate=128, tokens=16)
+    d = O.make_inputs(cfg, seed=3)
+    g = on_gpu(d)
+    rt = runtime(cfg, 16)
+    empty = rt.forward(g["x"][:0], g["routes"][:0], g["gates"][:0], g["w1"], g["w2"])
+    dx, dg, dw1, dw2 = rt.backward(empty, g["dy"][:0])
+    assert empty.output.shape == (0, 256) and (dw1 == 0).all() and (dw2 == 0).all()
+    x, gates = g["x"].clone().requires_grad_(), g["gates"].clone().requires_grad_()
+    w1, w2 = g["w1"].clone().requires_grad_(), g["w2"].clone().requires_grad_()
+    y = moe(rt, x, g["routes"], gates, w1, w2)
+    y.backward(g["dy"])
+    ref = O.moe_layer(d["x"], d["routes"], d["gates"], d["w1"], d["w2"], d["dy"], precision="bf16")
+    for mine, r in zip((y, x.grad, gates.grad, w1.grad, w2.grad), ref):
+        assert rel_l2(mine, r) < TOL_ROUNDED_ORACLE
+    rt.close()
+
+
+def test_contract_errors():
+    cfg = dict(experts=8, top_k=2, hidden=256, intermediate=128, tokens=16)
+    g = on_gpu(O.make_inputs(cfg, seed=3))
+    with pytest.raises(ValueError):
+        TensorRuntime(group=None, experts=8, top_k=2, hidden=256, intermediate=128, max_tokens=4, max_rows=8, training=False)
+    with pytest.raises(ValueError):
+        runtime(dict(cfg, hidden=200), 4)
+    rt = runtime(cfg, 8, max_saved=1)
+    with pytest.raises(ValueError, match="capacity"):
+        rt.forward(g["x"], g["routes"], g["gates"], g["w1"], g["w2"])       # 16 tokens > 8
+    with pytest.raises(ValueError):
+        rt.forward(g["x"][:8], g["routes"][:8].long(), g["gates"][:8], g["w1"], g["w2"])
+    with pytest.raises(ValueError):
+        rt.forward(g["x"][:8].float(), g["routes"][:8], g["gates"][:8], g["w1"], g["w2"])
+    tape = rt.forward(g["x"][:8], g["routes"][:8], g["gates"][:8], g["w1"], g["w2"])
+    with pytest.raises(RuntimeError, match="capacity exhausted"):
+        rt.forward(g["x"][:8], g["routes"][:8], g["gates"][:8], g["w1"], g["w2"])
+    with pytest.raises(RuntimeError, match="Live backward tapes"):
+        rt.close()
+    with pytest.raises(ValueError):
+        rt.backward(tape, g["dy"][:4])
+    rt.backward(tape, g["dy"][:8])
+    with pytest.raises(RuntimeError):
+        rt.backward(tape, g["dy"][:8])                                        # tape already consumed
+    with torch.cuda.stream(torch.cuda.Stream()):
+        with pytest.raises(RuntimeError, match="preparation stream"):
+            rt.forward(g["x"][:8], g["routes"][:8], g["gates"][:8], g["w1"], g["w2"])
+    rt.close()
+    rt.close()  # idempotent
+
+
+def test_received_rows_beyond_max_rows_are_reported_not_corrupted():
+    cfg = dict(experts=8, top_k=2, hidden=256, intermediate=128, tokens=2048)
+    g = on_gpu(O.make_inputs(cfg, seed=3))
+    rt = TensorRuntime(group=SingleRankGroup(), experts=8, top_k=2, hidden=256, intermediate=128,
+                       max_tokens=2048, max_rows=256, training=False)
+    with pytest.raises(ValueError, match="max_rows"):
+        rt.inference_eager(g["x"], g["routes"], g["gates"], g["w1"], g["w2"])
+    y = rt.inference_eager(g["x"][:64], g["routes"][:64], g["gates"][:64], g["w1"], g["w2"])  # still usable
+    assert torch.isfinite(y.float()).all()
+    rt.close()
