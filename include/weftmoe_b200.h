@@ -104,6 +104,19 @@ WM_API int wm_backward(wm_runtime* rt, const void* tape, const void* dy, const v
 WM_API int wm_status_poll(wm_runtime* rt, int32_t* code, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Instrumentation (reference: always-on device clocks surfaced as profile_inference /
+ * BackwardMegaKernelTimings, src/python/runtime.cpp:295-331, include/weftmoe/cuda/backward.hpp:48-61).
+ * wm_launch_count: kernels this library launched in this process so far.
+ * Timing: when enabled, every forward/backward brackets each stage with a CUDA event pair on the
+ * caller's stream; wm_runtime_read_timing waits for the recorded events and returns, per stage,
+ * the summed milliseconds and the number of calls (arrays of wm_stage_count() entries). */
+WM_API long long wm_launch_count(void);
+WM_API int wm_stage_count(void);
+WM_API const char* wm_stage_name(int stage);
+WM_API int wm_runtime_enable_timing(wm_runtime* rt, int enable);
+WM_API int wm_runtime_read_timing(wm_runtime* rt, double* total_ms, long long* calls, int reset);
+
+/* ------------------------------------------------------------------------------------------
  * Stand-alone route planning for tests and tools (reference: build_rank_local_histogram /
  * materialize_rank_metadata, include/weftmoe/api/notify_dispatch.hpp:49-114).  Two phases, so a
  * single GPU can play every rank in turn:

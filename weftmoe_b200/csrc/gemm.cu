@@ -1,5 +1,6 @@
 // Host launchers for the tcgen05 grouped GEMM template (gemm.cuh) and tensor-map creation.
 #include <cudaTypedefs.h>
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
@@ -18,6 +19,10 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 const char* last_error() { return g_error; }
+
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 // ------------------------------------------------------------------ tensor maps
 static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
@@ -76,6 +81,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
   }
   kernel<<<sms, kGemmThreads, smem, stream>>>(ta, tb, args, epi);
   WM_CUDA(cudaGetLastError());
+  count_launch();
   return 0;
 }
 

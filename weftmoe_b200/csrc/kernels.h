@@ -15,6 +15,9 @@ constexpr int kMaxPeers = 8;
 // ------------------------------------------------------------------ error plumbing
 void set_error(const char* fmt, ...);
 const char* last_error();
+// Process-wide count of kernels this library has launched (read through wm_launch_count()).
+void count_launch(int n = 1);
+long long launch_count();
 #define WM_CUDA(expr)                                                                 \
   do {                                                                                \
     cudaError_t e_ = (expr);                                                          \

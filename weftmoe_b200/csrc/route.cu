@@ -207,11 +207,14 @@ int route_local(const RouteShape& s, const int* routes, int tokens, RouteLocal o
   if (tokens > 0) {
     sort_slots_kernel<<<(tokens * 32 + 255) / 256, 256, 0, stream>>>(
         routes, tokens, s.top_k, s.experts, out.sorted_slot, out.sorted_expert, out.slot_pos);
+  count_launch();
     chunk_hist_kernel<<<chunks, kChunk, s.experts * sizeof(int), stream>>>(routes, n, s.experts,
                                                                            chunk_hist);
+  count_launch();
   }
   chunk_scan_kernel<<<(s.experts * 32 + 255) / 256, 256, 0, stream>>>(
       chunk_hist, chunks, s.experts, local_count, count_matrix, s.world, s.rank);
+  count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
 }
@@ -220,6 +223,7 @@ int route_global(const RouteShape& s, const int* count_matrix, const int* flag_c
                  int generation, int row_capacity, PlanTables t, int* status, cudaStream_t stream) {
   global_plan_kernel<<<1, 1024, 2 * s.experts * sizeof(int), stream>>>(
       count_matrix, flag_counts, generation, s.world, s.rank, s.experts, row_capacity, t, status);
+  count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
 }
@@ -240,6 +244,7 @@ int route_rows(const RouteShape& s, const int* routes, const float* gates, int t
   route_rows_kernel<<<chunks, kChunk, smem, stream>>>(
       routes, gates, local.slot_pos, n, s.top_k, s.experts, s.world, s.rank, s.cap, chunk_base, t,
       out.local_offset, out.dst_rank, out.dst_row, out.dst_prow, meta_origin, meta_prob);
+  count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
 }

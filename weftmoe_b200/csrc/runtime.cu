@@ -14,6 +14,7 @@
 // writes a mailbox only after READY >= g, which the source sends after its previous combine.
 #include <cstring>
 #include <new>
+#include <vector>
 
 #include "../../include/weftmoe_b200.h"
 #include "kernels.h"
@@ -24,6 +25,23 @@ using namespace wm;
 namespace {
 
 enum FlagGroup { kCounts = 0, kReady = 1, kPulled = 2, kContrib = 3, kFlagGroups = 4 };
+
+// Stages timed when wm_runtime_enable_timing is on: one CUDA event pair per stage and call.
+enum Stage {
+  kStagePlan = 0, kStageGather, kStageFc1, kStageFc2, kStageCombine,
+  kStageGatherDy, kStageDu, kStageSwigluBwd, kStageDx, kStageDw1, kStageDw2, kStageCombineDx,
+  kStageCount
+};
+const char* const kStageNames[kStageCount] = {
+    "route_plan", "gather_rows", "fc1_swiglu", "fc2_push", "combine",
+    "gather_dy", "dgrad_du", "swiglu_backward", "dgrad_dx_push", "wgrad_dw1", "wgrad_dw2",
+    "combine_dx"};
+constexpr int kTimingRing = 32;
+struct TimingSlot {
+  cudaEvent_t start[kStageCount] = {};
+  cudaEvent_t stop[kStageCount] = {};
+  bool used[kStageCount] = {};
+};
 
 constexpr size_t kAlign = 256;
 size_t align_up(size_t v, size_t a = kAlign) { return (v + a - 1) / a * a; }
@@ -63,6 +81,12 @@ struct wm_runtime {
   uint8_t* scratch = nullptr;
   uint8_t* peer[kMaxWorld] = {};
   bool peers_ready = false;
+  // Optional per-stage device timing (CUDA events on the caller's stream).
+  bool timing = false;
+  int timing_slot = 0;
+  std::vector<TimingSlot> slots;
+  double stage_ms[kStageCount] = {};
+  long long stage_calls[kStageCount] = {};
 };
 
 namespace {
@@ -198,6 +222,41 @@ int check_ready(const wm_runtime* rt, const char* what) {
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Fold the finished measurements of one ring slot into the totals (waits for its events).
+void harvest(wm_runtime* rt, TimingSlot& slot) {
+  for (int k = 0; k < kStageCount; ++k) {
+    if (!slot.used[k]) continue;
+    float ms = 0.0f;
+    if (cudaEventSynchronize(slot.stop[k]) == cudaSuccess &&
+        cudaEventElapsedTime(&ms, slot.start[k], slot.stop[k]) == cudaSuccess) {
+      rt->stage_ms[k] += ms;
+      rt->stage_calls[k] += 1;
+    }
+    slot.used[k] = false;
+  }
+}
+TimingSlot* begin_timing(wm_runtime* rt) {
+  if (!rt->timing) return nullptr;
+  TimingSlot& slot = rt->slots[rt->timing_slot];
+  rt->timing_slot = (rt->timing_slot + 1) % kTimingRing;
+  harvest(rt, slot);
+  return &slot;
+}
+struct StageScope {
+  TimingSlot* slot;
+  int stage;
+  cudaStream_t stream;
+  StageScope(TimingSlot* s, int k, cudaStream_t st) : slot(s), stage(k), stream(st) {
+    if (slot) cudaEventRecord(slot->start[stage], stream);
+  }
+  ~StageScope() {
+    if (slot) {
+      cudaEventRecord(slot->stop[stage], stream);
+      slot->used[stage] = true;
+    }
+  }
+};
 
 }  // namespace
 
@@ -415,45 +474,60 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
   else if (tokens > 0)
     WM_CUDA(cudaMemcpyAsync(rt->arena + rt->al.stage, x, 2ull * tokens * c.hidden,
                             cudaMemcpyDeviceToDevice, stream));
-  if (int rc = route_local(shape, routes, tokens, local, at<int>(S, rt->sl.chunk_hist),
-                           at<int>(S, rt->sl.local_count), counts, stream))
-    return rc;
-  if (world > 1)
-    if (int rc = signal_peers(flag_group(rt, kCounts), world, c.rank, gen, stream)) return rc;
-  // 2. global plan (waits for all count rows), destination rows, origin/prob words to owners.
-  if (int rc = route_global(shape, at<int>(rt->arena, rt->al.counts), my_flags(rt, kCounts),
-                            world > 1 ? gen : 0, rt->row_cap, tables, status, stream))
-    return rc;
-  RouteRows rows{at<int>(S, rt->sl.local_offset), at<int>(S, rt->sl.dst_rank),
-                 at<int>(S, rt->sl.dst_row), at<int>(S, rt->sl.dst_prow)};
-  if (int rc = route_rows(shape, routes, gates, tokens, local, at<int>(S, rt->sl.chunk_hist), tables,
-                          rows, meta_origin, meta_prob, stream))
-    return rc;
+  // 1b/2. local plan, count exchange, global plan (waits for all count rows), destination rows,
+  //       origin/prob words to the owners.  At world > 1 the stage time includes the wait.
+  TimingSlot* timing = begin_timing(rt);
+  {
+    StageScope scope(timing, kStagePlan, stream);
+    if (int rc = route_local(shape, routes, tokens, local, at<int>(S, rt->sl.chunk_hist),
+                             at<int>(S, rt->sl.local_count), counts, stream))
+      return rc;
+    if (world > 1)
+      if (int rc = signal_peers(flag_group(rt, kCounts), world, c.rank, gen, stream)) return rc;
+    if (int rc = route_global(shape, at<int>(rt->arena, rt->al.counts), my_flags(rt, kCounts),
+                              world > 1 ? gen : 0, rt->row_cap, tables, status, stream))
+      return rc;
+    RouteRows rows{at<int>(S, rt->sl.local_offset), at<int>(S, rt->sl.dst_rank),
+                   at<int>(S, rt->sl.dst_row), at<int>(S, rt->sl.dst_prow)};
+    if (int rc = route_rows(shape, routes, gates, tokens, local, at<int>(S, rt->sl.chunk_hist),
+                            tables, rows, meta_origin, meta_prob, stream))
+      return rc;
+  }
   if (world > 1) {
     if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
     if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
   }
   // 3. owner side: pull rows, then the two grouped GEMMs; FC2 pushes into the sources' mailboxes.
   OwnerRows owner{tables.padded_start, tables.tile_group, tables.padded_rows, tables.expert_total};
-  if (int rc = gather_rows(owner, c.rank, rt->e_local, c.max_tokens, c.top_k, c.hidden, stage,
-                           at<int>(rt->arena, rt->al.meta_origin),
-                           at<float>(rt->arena, rt->al.meta_prob), xrows, origin, prob, rt->sms,
-                           stream))
-    return rc;
+  {
+    StageScope scope(timing, kStageGather, stream);
+    if (int rc = gather_rows(owner, c.rank, rt->e_local, c.max_tokens, c.top_k, c.hidden, stage,
+                             at<int>(rt->arena, rt->al.meta_origin),
+                             at<float>(rt->arena, rt->al.meta_prob), xrows, origin, prob, rt->sms,
+                             stream))
+      return rc;
+  }
   if (world > 1)
     if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
   Schedule sched{tables.num_tiles, tables.tile_group, tables.padded_start, rt->e_local, rt->row_cap};
-  if (int rc = launch_fc1(sched, xrows, static_cast<const __nv_bfloat16*>(w1), u, ab, prob,
-                          c.hidden, c.intermediate, status, rt->sms, stream))
-    return rc;
-  if (int rc = launch_mgrouped_nt(sched, u, static_cast<const __nv_bfloat16*>(w2), nullptr, &push,
-                                  c.hidden, c.intermediate, status, rt->sms, stream))
-    return rc;
+  {
+    StageScope scope(timing, kStageFc1, stream);
+    if (int rc = launch_fc1(sched, xrows, static_cast<const __nv_bfloat16*>(w1), u, ab, prob,
+                            c.hidden, c.intermediate, status, rt->sms, stream))
+      return rc;
+  }
+  {
+    StageScope scope(timing, kStageFc2, stream);
+    if (int rc = launch_mgrouped_nt(sched, u, static_cast<const __nv_bfloat16*>(w2), nullptr, &push,
+                                    c.hidden, c.intermediate, status, rt->sms, stream))
+      return rc;
+  }
   if (world > 1) {
     if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
     if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
   }
   // 4. source side: ordered FP32 combine.
+  StageScope scope(timing, kStageCombine, stream);
   return combine_rows(at<__nv_bfloat16>(rt->arena, rt->al.mailbox), local.sorted_expert, tokens,
                       c.max_tokens, c.top_k, c.hidden, static_cast<__nv_bfloat16*>(y), stream);
 }
@@ -524,34 +598,54 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
     if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
   }
   // 2. owner side: pull dY rows in the saved row order.
-  if (int rc = gather_by_origin(padded_rows, origin, c.max_tokens, c.top_k, c.hidden, stage, recv,
-                                rt->sms, stream))
-    return rc;
+  TimingSlot* timing = begin_timing(rt);
+  {
+    StageScope scope(timing, kStageGatherDy, stream);
+    if (int rc = gather_by_origin(padded_rows, origin, c.max_tokens, c.top_k, c.hidden, stage, recv,
+                                  rt->sms, stream))
+      return rc;
+  }
   if (world > 1)
     if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
   Schedule sched{num_tiles, tile_group, padded_start, rt->e_local, rt->row_cap};
   // 3. dU = dY * W2 ; SwiGLU backward (U, dAB, dprob -> sources) ; dX = dAB * W1 -> sources.
-  if (int rc = launch_mgrouped_nn(sched, recv, static_cast<const __nv_bfloat16*>(w2), du, nullptr,
-                                  c.intermediate, c.hidden, status, rt->sms, stream))
-    return rc;
-  if (int rc = swiglu_backward(padded_rows, ab, du, prob, origin, c.intermediate, c.max_tokens,
-                               c.top_k, u, dab, dgate_box, rt->sms, stream))
-    return rc;
-  if (int rc = launch_mgrouped_nn(sched, dab, static_cast<const __nv_bfloat16*>(w1), nullptr, &push,
-                                  c.hidden, 2 * c.intermediate, status, rt->sms, stream))
-    return rc;
+  {
+    StageScope scope(timing, kStageDu, stream);
+    if (int rc = launch_mgrouped_nn(sched, recv, static_cast<const __nv_bfloat16*>(w2), du, nullptr,
+                                    c.intermediate, c.hidden, status, rt->sms, stream))
+      return rc;
+  }
+  {
+    StageScope scope(timing, kStageSwigluBwd, stream);
+    if (int rc = swiglu_backward(padded_rows, ab, du, prob, origin, c.intermediate, c.max_tokens,
+                                 c.top_k, u, dab, dgate_box, rt->sms, stream))
+      return rc;
+  }
+  {
+    StageScope scope(timing, kStageDx, stream);
+    if (int rc = launch_mgrouped_nn(sched, dab, static_cast<const __nv_bfloat16*>(w1), nullptr,
+                                    &push, c.hidden, 2 * c.intermediate, status, rt->sms, stream))
+      return rc;
+  }
   if (world > 1)
     if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
   // 4. weight gradients: reductions over each expert's rows in the saved (fixed) order.
-  if (int rc = launch_kgrouped_tn(sched, dab, xrows, static_cast<__nv_bfloat16*>(dw1),
-                                  2 * c.intermediate, c.hidden, status, rt->sms, stream))
-    return rc;
-  if (int rc = launch_kgrouped_tn(sched, recv, u, static_cast<__nv_bfloat16*>(dw2), c.hidden,
-                                  c.intermediate, status, rt->sms, stream))
-    return rc;
+  {
+    StageScope scope(timing, kStageDw1, stream);
+    if (int rc = launch_kgrouped_tn(sched, dab, xrows, static_cast<__nv_bfloat16*>(dw1),
+                                    2 * c.intermediate, c.hidden, status, rt->sms, stream))
+      return rc;
+  }
+  {
+    StageScope scope(timing, kStageDw2, stream);
+    if (int rc = launch_kgrouped_tn(sched, recv, u, static_cast<__nv_bfloat16*>(dw2), c.hidden,
+                                    c.intermediate, status, rt->sms, stream))
+      return rc;
+  }
   // 5. source side: ordered combine of dX, dprob back to the original slots.
   if (world > 1)
     if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
+  StageScope scope(timing, kStageCombineDx, stream);
   if (int rc = combine_rows(at<__nv_bfloat16>(rt->arena, rt->al.mailbox), sorted_expert, tokens,
                             c.max_tokens, c.top_k, c.hidden, static_cast<__nv_bfloat16*>(dx), stream))
     return rc;
@@ -616,6 +710,41 @@ extern "C" int wm_route_plan(int32_t phase, int32_t world, int32_t rank, int32_t
   if (device_code) {
     set_error("wm_route_plan: device status %d", device_code);
     return map_status(device_code);
+  }
+  return WM_OK;
+}
+
+// =============================================================================== instrumentation
+extern "C" long long wm_launch_count(void) { return wm::launch_count(); }
+extern "C" int wm_stage_count(void) { return kStageCount; }
+extern "C" const char* wm_stage_name(int stage) {
+  return stage >= 0 && stage < kStageCount ? kStageNames[stage] : "";
+}
+
+extern "C" int wm_runtime_enable_timing(wm_runtime* rt, int enable) {
+  if (int rc = check_ready(rt, "wm_runtime_enable_timing")) return rc;
+  if (enable && rt->slots.empty()) {
+    rt->slots.resize(kTimingRing);
+    for (auto& slot : rt->slots)
+      for (int k = 0; k < kStageCount; ++k) {
+        WM_CUDA(cudaEventCreate(&slot.start[k]));
+        WM_CUDA(cudaEventCreate(&slot.stop[k]));
+      }
+  }
+  rt->timing = enable != 0;
+  return WM_OK;
+}
+
+extern "C" int wm_runtime_read_timing(wm_runtime* rt, double* total_ms, long long* calls, int reset) {
+  if (int rc = check_ready(rt, "wm_runtime_read_timing")) return rc;
+  for (auto& slot : rt->slots) harvest(rt, slot);
+  for (int k = 0; k < kStageCount; ++k) {
+    if (total_ms) total_ms[k] = rt->stage_ms[k];
+    if (calls) calls[k] = rt->stage_calls[k];
+    if (reset) {
+      rt->stage_ms[k] = 0.0;
+      rt->stage_calls[k] = 0;
+    }
   }
   return WM_OK;
 }

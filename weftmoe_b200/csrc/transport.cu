@@ -27,11 +27,13 @@ __global__ void signal_peers_kernel(PeerInts group, int world, int slot, int gen
 }
 int wait_flags(const int* flags, int world, int generation, int* status, cudaStream_t stream) {
   wait_flags_kernel<<<1, 32, 0, stream>>>(flags, world, generation, status);
+  count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
 }
 int signal_peers(const PeerInts& group, int world, int slot, int generation, cudaStream_t stream) {
   signal_peers_kernel<<<1, 32, 0, stream>>>(group, world, slot, generation);
+  count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
 }
@@ -117,6 +119,7 @@ int gather_rows(const OwnerRows& o, int rank, int e_local, int cap, int top_k, i
   gather_rows_kernel<<<sms * 8, 256, 0, stream>>>(o, rank, e_local, cap, top_k, hidden, stage,
                                                   meta_origin, meta_prob, rows_out, origin_out,
                                                   prob_out);
+  count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
 }
@@ -125,6 +128,7 @@ int gather_by_origin(const int* padded_rows, const int* origin, int cap, int top
                      cudaStream_t stream) {
   gather_by_origin_kernel<<<sms * 8, 256, 0, stream>>>(padded_rows, origin, cap, top_k, hidden,
                                                        stage, rows_out);
+  count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
 }
@@ -167,6 +171,7 @@ int combine_rows(const __nv_bfloat16* mailbox, const int* sorted_expert, int tok
   const int threads = hidden / 8 >= 256 ? 256 : ((hidden / 8 + 31) / 32 * 32);
   combine_rows_kernel<<<tokens, threads, 0, stream>>>(mailbox, sorted_expert, cap, top_k, hidden,
                                                       out);
+  count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
 }
@@ -186,6 +191,7 @@ int unpermute_dgates(const float* dgate_box, const int* sorted_slot, const int* 
   if (n == 0) return 0;
   unpermute_dgates_kernel<<<(n + 255) / 256, 256, 0, stream>>>(dgate_box, sorted_slot,
                                                                sorted_expert, n, top_k, dgates);
+  count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
 }
@@ -259,6 +265,7 @@ int swiglu_backward(const int* padded_rows, const __nv_bfloat16* ab, const __nv_
                     cudaStream_t stream) {
   swiglu_backward_kernel<<<sms * 8, 256, 0, stream>>>(padded_rows, ab, du, prob, origin, inter, cap,
                                                       top_k, u, dab, dgate_box);
+  count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
 }

@@ -225,6 +225,24 @@ class NativeRuntime:
     def session(self):
         return None
 
+    # ------------------------------------------------------------------ instrumentation
+    def enable_timing(self, enable=True):
+        """Bracket every stage of forward/backward with CUDA events on the runtime's stream."""
+        self._require()
+        _lib.check(self.lib.wm_runtime_enable_timing(self.handle, int(enable)))
+
+    def read_timing(self, reset=True):
+        """{stage name: (summed milliseconds, calls)} of the calls made since the last reset."""
+        self._require()
+        n = self.lib.wm_stage_count()
+        ms = (ctypes.c_double * n)()
+        calls = (ctypes.c_longlong * n)()
+        _lib.check(self.lib.wm_runtime_read_timing(self.handle, ms, calls, int(reset)))
+        return {self.lib.wm_stage_name(k).decode(): (ms[k], calls[k]) for k in range(n)}
+
+    def launch_count(self):
+        return int(self.lib.wm_launch_count())
+
     def retire_peer_mappings(self):
         if self.handle is not None:
             self.lib.wm_runtime_retire_peers(self.handle)
