@@ -50,8 +50,10 @@ struct GemmSmem {
   static constexpr int kBBytes = BLOCK_N * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BLOCK_N == 256) ? 4 : 6;
+  // Epilogue staging: each of the 4 epilogue warps owns 32 rows x 256 B (128 BF16 columns).
+  static constexpr int kStagingBytes = 4 * 32 * 256;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
 struct TileCoord {
@@ -87,7 +89,16 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& a, int tile) {
 // (lane field already set), the tile, the lane quarter q (rows q*32 .. q*32+31 of the tile),
 // the lane id, and `zero` = the K loop was empty (nothing was accumulated: result is 0).
 //
-// Signature: void operator()(uint32_t taddr, const TileCoord& t, int q, int lane, bool zero) const
+// `stage` is this warp's private 8 KB of shared memory (32 rows x 256 B).
+//
+// Signature: void operator()(uint32_t taddr, const TileCoord& t, int q, int lane, bool zero,
+//                            uint8_t* stage) const
+//
+// All epilogues write global memory the same way: a 32-row x 128-column BF16 block is first
+// put into `stage` (thread = row, 16-byte chunks XOR-swizzled by the row so that both the
+// row-wise writes and the later chunk-wise reads hit every bank once per 128 B), then written
+// out with each half-warp covering one whole 256-byte row segment: fully coalesced stores,
+// local or over NVLink.
 
 template <int BLOCK_N, bool A_MN, bool B_MN, bool GATE_UP, bool K_GROUPED, class Epilogue>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -102,7 +113,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes);
+  uint8_t* staging = smem + kStages * S::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + S::kStagingBytes);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full = empty_bar + kStages;
   uint64_t* tmem_empty = tmem_full + 2;
@@ -239,7 +251,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
-      epilogue(taddr, t, q, lane, t.num_kb == 0);
+      epilogue(taddr, t, q, lane, t.num_kb == 0, staging + (warp - 2) * (32 * 256));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty + acc);
@@ -257,6 +269,44 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
 // ---------------------------------------------------------------------------- epilogues
 
+// 32 packed BF16 columns (16 words) of row `lane` into chunk group c32 (0..3) of the staging block.
+__device__ __forceinline__ void stage_put32(uint8_t* stage, int lane, int c32, const uint32_t (&w)[16]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int pos = (c32 * 4 + j) ^ (lane & 15);
+    *reinterpret_cast<uint4*>(stage + lane * 256 + pos * 16) =
+        make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+  }
+}
+// Accumulator columns [col, col+32) of this thread's row, rounded to BF16 and packed.
+__device__ __forceinline__ void load_pack32(uint32_t taddr, bool zero, uint32_t (&w)[16]) {
+  if (zero) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) w[j] = 0;
+    return;
+  }
+  uint32_t v[32];
+  tmem_ld_32x32(taddr, v);
+  tmem_ld_wait();
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+    w[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+}
+// Write the staged 32 x 128 block: half-warp h handles row 2*it + h, lane&15 picks the 16-byte
+// chunk.  `row_dst(r)` returns the global address of column 0 of the block in row r (or nullptr
+// to skip the row).
+template <class RowDst>
+__device__ __forceinline__ void stage_flush(const uint8_t* stage, int lane, RowDst row_dst) {
+  const int c = lane & 15;
+#pragma unroll 4
+  for (int it = 0; it < 16; ++it) {
+    const int r = 2 * it + (lane >> 4);
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((c ^ (r & 15)) << 4));
+    __nv_bfloat16* dst = row_dst(r);
+    if (dst != nullptr) *reinterpret_cast<uint4*>(dst + c * 8) = v;
+  }
+}
+
 // Plain BF16 store: out[(group_base) + row, col] with leading dimension ld.
 //   M-grouped: row = m_tile*128 + r.   K-grouped: out + group*group_stride, row = m_tile*128 + r.
 template <int BLOCK_N>
@@ -266,29 +316,22 @@ struct EpilogueStore {
   int ld;
 
   __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane,
-                                             bool zero) const {
-    const long long row = static_cast<long long>(t.m_tile) * kBlockM + q * 32 + lane;
-    __nv_bfloat16* dst = out + group_stride * t.group + row * ld + t.n_tile * BLOCK_N;
+                                             bool zero, uint8_t* stage) const {
+    const long long row0 = static_cast<long long>(t.m_tile) * kBlockM + q * 32;
+    __nv_bfloat16* base = out + group_stride * t.group + row0 * ld + t.n_tile * BLOCK_N;
 #pragma unroll 1
-    for (int c = 0; c < BLOCK_N / 32; ++c) {
-      uint32_t v[32];
-      if (!zero) {
-        tmem_ld_32x32(taddr + c * 32, v);
-        tmem_ld_wait();
-      } else {
+    for (int half = 0; half < BLOCK_N / 128; ++half) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = 0;
+      for (int c = 0; c < 4; ++c) {
+        uint32_t w[16];
+        load_pack32(taddr + half * 128 + c * 32, zero, w);
+        stage_put32(stage, lane, c, w);
       }
-      uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint4 w;
-        w.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
-        w.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-        w.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-        w.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-        d4[j] = w;
-      }
+      __syncwarp();
+      __nv_bfloat16* block = base + half * 128;
+      const int ldl = ld;
+      stage_flush(stage, lane, [block, ldl](int r) { return block + static_cast<long long>(r) * ldl; });
+      __syncwarp();
     }
   }
 };
@@ -304,9 +347,9 @@ struct EpilogueSwiglu {
   int inter;                // I
 
   __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane,
-                                             bool) const {
-    const long long row = static_cast<long long>(t.m_tile) * kBlockM + q * 32 + lane;
-    const float prob = row_prob[row];
+                                             bool, uint8_t* stage) const {
+    const long long row0 = static_cast<long long>(t.m_tile) * kBlockM + q * 32;
+    const float prob = row_prob[row0 + lane];
     const int col0 = t.n_tile * 128;
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
@@ -314,36 +357,47 @@ struct EpilogueSwiglu {
       tmem_ld_32x32(taddr + c * 32, g);
       tmem_ld_32x32(taddr + 128 + c * 32, b);
       tmem_ld_wait();
-      uint32_t pg[16], pb[16], pu[16];
+      uint32_t pu[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const float g0 = bf16_round(__uint_as_float(g[2 * j])), g1 = bf16_round(__uint_as_float(g[2 * j + 1]));
         const float b0 = bf16_round(__uint_as_float(b[2 * j])), b1 = bf16_round(__uint_as_float(b[2 * j + 1]));
-        pg[j] = pack_bf16x2(g0, g1);
-        pb[j] = pack_bf16x2(b0, b1);
         const float u0 = (g0 / (1.0f + __expf(-g0))) * b0 * prob;
         const float u1 = (g1 / (1.0f + __expf(-g1))) * b1 * prob;
         pu[j] = pack_bf16x2(u0, u1);
       }
-      uint4* du = reinterpret_cast<uint4*>(u + row * inter + col0 + c * 32);
+      stage_put32(stage, lane, c, pu);
+    }
+    __syncwarp();
+    {
+      __nv_bfloat16* block = u + row0 * inter + col0;
+      const int ldl = inter;
+      stage_flush(stage, lane, [block, ldl](int r) { return block + static_cast<long long>(r) * ldl; });
+    }
+    __syncwarp();
+    if (ab != nullptr) {
+      // Training cache: the BF16-rounded gate and up halves, re-read from TMEM.
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) du[j] = make_uint4(pu[4 * j], pu[4 * j + 1], pu[4 * j + 2], pu[4 * j + 3]);
-      if (ab != nullptr) {
-        uint4* dg = reinterpret_cast<uint4*>(ab + row * (2 * inter) + col0 + c * 32);
-        uint4* db = reinterpret_cast<uint4*>(ab + row * (2 * inter) + inter + col0 + c * 32);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          dg[j] = make_uint4(pg[4 * j], pg[4 * j + 1], pg[4 * j + 2], pg[4 * j + 3]);
-          db[j] = make_uint4(pb[4 * j], pb[4 * j + 1], pb[4 * j + 2], pb[4 * j + 3]);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t w[16];
+          load_pack32(taddr + half * 128 + c * 32, false, w);
+          stage_put32(stage, lane, c, w);
         }
+        __syncwarp();
+        __nv_bfloat16* block = ab + row0 * (2 * inter) + half * inter + col0;
+        const int ldl = 2 * inter;
+        stage_flush(stage, lane, [block, ldl](int r) { return block + static_cast<long long>(r) * ldl; });
+        __syncwarp();
       }
     }
   }
 };
 
 // Return epilogue (FC2 contributions and backward dX rows): each routed row is written as
-// BF16 into the SOURCE rank's mailbox [sorted_slot][token][N] with 16-byte stores, local or
-// over NVLink through the peer-mapped arena (reference: routed_bf16.cuh:1028-1139 and
+// BF16 into the SOURCE rank's mailbox [sorted_slot][token][N], local or over NVLink through
+// the peer-mapped arena (reference: routed_bf16.cuh:1028-1139 and
 // weftmoe/blackwell_backward.py:116-144).  origin = src_rank*cap*K + token*K + sorted_slot,
 // -1 on padding rows.
 constexpr int kMaxRanks = 8;
@@ -355,33 +409,41 @@ struct EpiloguePush {
   int top_k;
   int ld;                             // N_total (hidden)
 
+  __device__ __forceinline__ __nv_bfloat16* select_mailbox(int src) const {
+    __nv_bfloat16* p = mailbox[0];
+#pragma unroll
+    for (int r = 1; r < kMaxRanks; ++r)
+      if (src == r) p = mailbox[r];
+    return p;
+  }
+
   __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane,
-                                             bool) const {
+                                             bool, uint8_t* stage) const {
     const long long row = static_cast<long long>(t.m_tile) * kBlockM + q * 32 + lane;
     const int org = origin[row];
-    const int per_rank = cap * top_k;
-    const int src = org >= 0 ? org / per_rank : 0;
-    const int rem = org >= 0 ? org - src * per_rank : 0;
-    const int token = rem / top_k, slot = rem - token * top_k;
-    __nv_bfloat16* dst = mailbox[src] +
-                         (static_cast<long long>(slot) * cap + token) * ld + t.n_tile * BLOCK_N;
+    unsigned long long my_dst = 0;  // destination of column n_tile*BLOCK_N of this thread's row
+    if (org >= 0) {
+      const int per_rank = cap * top_k;
+      const int src = org / per_rank;
+      const int rem = org - src * per_rank;
+      const int token = rem / top_k, slot = rem - token * top_k;
+      my_dst = reinterpret_cast<unsigned long long>(
+          select_mailbox(src) + (static_cast<long long>(slot) * cap + token) * ld + t.n_tile * BLOCK_N);
+    }
 #pragma unroll 1
-    for (int c = 0; c < BLOCK_N / 32; ++c) {
-      uint32_t v[32];
-      tmem_ld_32x32(taddr + c * 32, v);  // warp-collective: every lane takes part
-      tmem_ld_wait();
-      if (org >= 0) {
-        uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+    for (int half = 0; half < BLOCK_N / 128; ++half) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 w;
-          w.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
-          w.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-          w.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-          w.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-          d4[j] = w;
-        }
+      for (int c = 0; c < 4; ++c) {
+        uint32_t w[16];
+        load_pack32(taddr + half * 128 + c * 32, false, w);
+        stage_put32(stage, lane, c, w);
       }
+      __syncwarp();
+      stage_flush(stage, lane, [my_dst, half](int r) {
+        const unsigned long long d = __shfl_sync(0xffffffffu, my_dst, r);
+        return d ? reinterpret_cast<__nv_bfloat16*>(d) + half * 128 : nullptr;
+      });
+      __syncwarp();
     }
   }
 };
