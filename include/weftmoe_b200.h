@@ -155,6 +155,11 @@ WM_API int wm_debug_grouped_gemm(int kind, const void* a, const void* b, void* o
                                  const float* row_prob, const int* group_rows_host, int groups, int n,
                                  int k_or_m, int* status_dev, void* stream);
 
+/* Diagnostic: pin the grouped-GEMM kernel choice for this process: -1 automatic (default), 0 the
+ * one-CTA kernel, 1 the CTA-pair (cta_group::2) kernel.  No counterpart in the reference, whose
+ * tile heuristic lives in weftmoe/blackwell_cutlass.py:80-88. */
+WM_API void wm_debug_force_gemm_pairs(int mode);
+
 #ifdef __cplusplus
 }
 #endif

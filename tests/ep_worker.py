@@ -1,0 +1,118 @@
+"""Multi-rank parity worker: run with `python -m torch.distributed.run --nproc-per-node N tests/ep_worker.py`.
+
+Mirrors the reference's torchrun tests (tests/torchrun_sm100_invariant.py,
+tests/torchrun_tensor_runtime.py): every rank runs forward + backward through the Tensor API over
+a real EP group, compares with the CPU oracle, checks that EPn equals EP1 bit for bit on the
+forward output, that repeated interleaved tapes repeat bit for bit, and that a rank with zero
+tokens and an idle expert are handled.  Backend nccl on GPUs (bootstrap collectives only).
+"""
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+from oracle import moe_oracle as O  # noqa: E402
+from weftmoe_b200 import SingleRankGroup, TensorRuntime  # noqa: E402
+
+
+def rel_l2(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return ((a - b).norm() / b.norm().clamp_min(1e-30)).item()
+
+
+def bits(t):
+    return t.contiguous().view(torch.int16 if t.dtype == torch.bfloat16 else torch.int32)
+
+
+def main():
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    E, K, H, I = 16 * world // 2 if world > 2 else 16, 4, 512, 256
+    E = max(E, 2 * world)
+    e_local = E // world
+    # ---- per-rank inputs; rank 1 holds no tokens in the second scenario
+    for scenario, counts in (("ragged", [37 + 11 * r for r in range(world)]),
+                             ("zero-token rank", [0 if r == 1 else 20 + r for r in range(world)])):
+        g = torch.Generator().manual_seed(1234)
+        w1 = (torch.randn(E, 2 * I, H, generator=g) * 0.03).bfloat16()
+        w2 = (torch.randn(E, H, I, generator=g) * 0.03).bfloat16()
+        xs, rs, gs, dys = [], [], [], []
+        for r in range(world):
+            t = counts[r]
+            xs.append((torch.randn(t, H, generator=g)).bfloat16())
+            dys.append((torch.randn(t, H, generator=g)).bfloat16())
+            ids = torch.rand(t, E, generator=g).topk(K).indices.int()
+            ids.clamp_(max=E - 2)  # the last expert stays idle (and duplicates appear)
+            if t > 2:
+                ids[0] = 3
+                ids[1] = -1
+            rs.append(ids)
+            gs.append(torch.rand(t, K, generator=g))
+        cap = max(max(counts), 1)
+        rt = TensorRuntime(group=dist.group.WORLD, experts=E, top_k=K, hidden=H, intermediate=I,
+                           max_tokens=cap, max_rows=sum(counts) * K, training=True, max_saved=2)
+        dev = lambda t: t.cuda()
+        lw1, lw2 = dev(w1.chunk(world)[rank]), dev(w2.chunk(world)[rank])
+        x, routes, gates, dy = dev(xs[rank]), dev(rs[rank]), dev(gs[rank]), dev(dys[rank])
+        expected = None
+        for _ in range(2):
+            t = rt.forward_async(x, routes, gates, lw1, lw2)
+            other = rt.forward_async(x, routes.roll(1, dims=1).contiguous(), gates, lw1, lw2)
+            rt.backward_async(other, dy)
+            result = (t.output, *rt.backward_async(t, dy))
+            rt.drain()
+            if expected is None:
+                expected = tuple(v.clone() for v in result)
+            else:
+                for a, b in zip(result, expected):
+                    assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), (scenario, "repeat differs")
+        ys, dxs, dgs, dw1s, dw2s = O.moe_layer_ep(xs, rs, gs, list(w1.chunk(world)), list(w2.chunk(world)), dys)
+        for name, mine, ref in zip(("y", "dx", "dgates", "dw1", "dw2"), expected,
+                                   (ys[rank], dxs[rank], dgs[rank], dw1s[rank], dw2s[rank])):
+            if ref.numel():
+                err = rel_l2(mine, ref)
+                assert err < 2e-3, (scenario, rank, name, err)
+        assert (expected[3][-1] == 0).all() if rank == world - 1 else True  # idle expert: zero dW
+        rt.close()
+        # ---- EPn forward bits == EP1 forward bits on the same tokens
+        ep1 = TensorRuntime(group=SingleRankGroup(), experts=E, top_k=K, hidden=H, intermediate=I,
+                            max_tokens=max(sum(counts), 1), max_rows=sum(counts) * K, training=False)
+        y1 = ep1.inference_eager(dev(torch.cat(xs)), dev(torch.cat(rs)), dev(torch.cat(gs)), dev(w1), dev(w2))
+        begin = sum(counts[:rank])
+        assert torch.equal(bits(y1[begin:begin + counts[rank]]), bits(expected[0])), (scenario, "EP1 != EPn bits")
+        ep1.close()
+        if rank == 0:
+            print(f"EP{world} {scenario}: oracle parity, bitwise repeat and EP1 == EP{world} bits passed", flush=True)
+    # ---- received rows beyond max_rows: a collective, reported error, runtime stays usable
+    small = TensorRuntime(group=dist.group.WORLD, experts=E, top_k=K, hidden=H, intermediate=I,
+                          max_tokens=64, max_rows=128, training=False)
+    g = torch.Generator().manual_seed(5 + rank)
+    x = torch.randn(64, H, generator=g).bfloat16().cuda()
+    routes = torch.zeros(64, K, dtype=torch.int32).cuda() + torch.arange(K, dtype=torch.int32).cuda()  # all to rank 0
+    gates = torch.rand(64, K, generator=g).cuda()
+    lw1, lw2 = w1.chunk(world)[rank].cuda(), w2.chunk(world)[rank].cuda()
+    failed = False
+    try:
+        small.inference_eager(x, routes, gates, lw1, lw2)
+    except ValueError:
+        failed = True
+    flags = [None] * world
+    dist.all_gather_object(flags, failed)
+    assert flags[0], "rank 0 must report the overflow"
+    y = small.inference_eager(x[:4], routes[:4], gates[:4], lw1, lw2)
+    assert torch.isfinite(y.float()).all()
+    small.close()
+    if rank == 0:
+        print(f"EP{world} overflow reporting passed", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

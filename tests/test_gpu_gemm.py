@@ -3,8 +3,20 @@ import pytest
 import torch
 
 from tests.gpu_util import grouped_gemm, rel_l2
+from weftmoe_b200 import _lib
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(params=[0, 1], ids=["one_cta", "cta_pair"], autouse=True)
+def kernel_choice(request):
+    """Every case runs on the one-CTA kernel and on the CTA-pair (cta_group::2) kernel."""
+    lib = _lib.load()
+    lib.wm_debug_force_gemm_pairs(request.param)
+    yield request.param
+    lib.wm_debug_force_gemm_pairs(-1)
+
+
 TOL = 4e-3  # one BF16 rounding of an FP32-accumulated result (2^-9 relative) plus slack
 
 

@@ -16,19 +16,30 @@ extern "C" int wm_debug_grouped_gemm(int kind, const void* a, const void* b, voi
     set_error("wm_debug_grouped_gemm: groups must be positive");
     return WM_ERR_INVALID;
   }
-  std::vector<int> starts(groups + 1, 0), tile_group;
+  std::vector<int> starts(groups + 1, 0), tile_group, pairs;
   for (int g = 0; g < groups; ++g) {
     if (group_rows_host[g] % 128) {
       set_error("wm_debug_grouped_gemm: group rows must be multiples of 128");
       return WM_ERR_INVALID;
     }
     starts[g + 1] = starts[g] + group_rows_host[g];
-    for (int t = 0; t < group_rows_host[g] / 128; ++t) tile_group.push_back(g);
+    const int first = static_cast<int>(tile_group.size()), tiles = group_rows_host[g] / 128;
+    for (int t = 0; t < tiles; ++t) tile_group.push_back(g);
+    for (int j = 0; j < (tiles + 1) / 2; ++j) {
+      pairs.push_back(first + 2 * j);
+      pairs.push_back(2 * j + 1 < tiles ? first + 2 * j + 1 : -1);
+    }
   }
+  int num_pairs = static_cast<int>(pairs.size() / 2);
+  pairs.push_back(-1);
   const int rows = starts[groups];
   int num_tiles = static_cast<int>(tile_group.size());
   tile_group.push_back(0);
-  int *d_num = nullptr, *d_tiles = nullptr, *d_starts = nullptr;
+  int *d_num = nullptr, *d_tiles = nullptr, *d_starts = nullptr, *d_pairs = nullptr, *d_npairs = nullptr;
+  WM_CUDA(cudaMalloc(&d_pairs, pairs.size() * sizeof(int)));
+  WM_CUDA(cudaMalloc(&d_npairs, sizeof(int)));
+  WM_CUDA(cudaMemcpyAsync(d_pairs, pairs.data(), pairs.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
+  WM_CUDA(cudaMemcpyAsync(d_npairs, &num_pairs, sizeof(int), cudaMemcpyHostToDevice, stream));
   WM_CUDA(cudaMalloc(&d_num, sizeof(int)));
   WM_CUDA(cudaMalloc(&d_tiles, tile_group.size() * sizeof(int)));
   WM_CUDA(cudaMalloc(&d_starts, starts.size() * sizeof(int)));
@@ -40,7 +51,7 @@ extern "C" int wm_debug_grouped_gemm(int kind, const void* a, const void* b, voi
   int sms = 0, dev = 0;
   WM_CUDA(cudaGetDevice(&dev));
   WM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  Schedule s{d_num, d_tiles, d_starts, groups, rows};
+  Schedule s{d_num, d_tiles, d_starts, groups, rows, d_npairs, d_pairs, rows >= 1024 * groups};
   auto A = static_cast<const __nv_bfloat16*>(a);
   auto B = static_cast<const __nv_bfloat16*>(b);
   auto O = static_cast<__nv_bfloat16*>(out);
@@ -61,6 +72,8 @@ extern "C" int wm_debug_grouped_gemm(int kind, const void* a, const void* b, voi
   cudaFree(d_num);
   cudaFree(d_tiles);
   cudaFree(d_starts);
+  cudaFree(d_pairs);
+  cudaFree(d_npairs);
   if (rc) return rc;
   if (e != cudaSuccess) {
     set_error("wm_debug_grouped_gemm: %s", cudaGetErrorString(e));
@@ -70,3 +83,5 @@ extern "C" int wm_debug_grouped_gemm(int kind, const void* a, const void* b, voi
 }
 
 extern "C" const char* wm_last_error(void) { return wm::last_error(); }
+
+extern "C" void wm_debug_force_gemm_pairs(int mode) { wm::force_gemm_pairs(mode); }

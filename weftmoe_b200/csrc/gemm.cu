@@ -5,7 +5,10 @@
 #include <cstdio>
 #include <mutex>
 
+#include <cstdlib>
+
 #include "gemm.cuh"
+#include "gemm2.cuh"
 #include "kernels.h"
 
 namespace wm {
@@ -68,10 +71,32 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t in
   return 0;
 }
 
-// ------------------------------------------------------------------ launch helper
+// ------------------------------------------------------------------ launch helpers
+// Kernel choice.  Measured on B200 (35B-A3B-like shape): with about 2048 rows per expert the
+// CTA-pair kernel wins on the long-K backward contractions (dU, dX, dW1, dW2: 6 x 32 KB stages
+// hide the load latency) and loses on FC1/FC2 (epilogue-heavy or short K: the extra cross-CTA
+// hop costs more than it saves); with about 256 rows per expert every second pair is half
+// empty and the one-CTA kernel wins everywhere.  WM_GEMM_PAIR=0/1 forces one kernel (A/B runs).
+static std::atomic<int> g_forced_pairs{-2};  // -2: not read yet, -1: automatic, 0: one CTA, 1: pair
+void force_gemm_pairs(int mode) { g_forced_pairs.store(mode < 0 ? -1 : (mode ? 1 : 0)); }
+static int forced_pairs() {
+  int value = g_forced_pairs.load();
+  if (value == -2) {
+    const char* v = std::getenv("WM_GEMM_PAIR");
+    value = v ? (v[0] == '0' ? 0 : 1) : -1;
+    g_forced_pairs.store(value);
+  }
+  return value;
+}
+static bool use_pairs(const Schedule& s, bool backward_contraction) {
+  const int forced = forced_pairs();
+  if (forced >= 0) return forced == 1;
+  return backward_contraction && s.many_rows_per_expert;
+}
+
 template <int BLOCK_N, bool A_MN, bool B_MN, bool GATE_UP, bool K_GROUPED, class Epi>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, const Epi& epi,
-                  int sms, cudaStream_t stream) {
+static int launch_single(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
+                         const Epi& epi, int sms, cudaStream_t stream) {
   auto kernel = gemm_kernel<BLOCK_N, A_MN, B_MN, GATE_UP, K_GROUPED, Epi>;
   constexpr int smem = GemmSmem<BLOCK_N>::kTotal;
   static bool configured = false;  // one flag per template instantiation
@@ -83,6 +108,31 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
   WM_CUDA(cudaGetLastError());
   count_launch();
   return 0;
+}
+
+template <int BLOCK_N, bool A_MN, bool B_MN, bool GATE_UP, bool K_GROUPED, class Epi>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
+                       const Schedule& s, const Epi& epi, int sms, cudaStream_t stream) {
+  auto kernel = gemm2_kernel<BLOCK_N, A_MN, B_MN, GATE_UP, K_GROUPED, Epi>;
+  constexpr int smem = Gemm2Smem<BLOCK_N>::kTotal;
+  static bool configured = false;
+  if (!configured) {
+    WM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  Gemm2Args a2{args, s.num_pairs, s.pair_tiles};
+  kernel<<<sms & ~1, kGemmThreads, smem, stream>>>(ta, tb, a2, epi);  // clusters of two CTAs
+  WM_CUDA(cudaGetLastError());
+  count_launch();
+  return 0;
+}
+
+template <int BLOCK_N, bool A_MN, bool B_MN, bool GATE_UP, bool K_GROUPED, class Epi>
+static int launch(bool pair, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
+                  const Schedule& s, const Epi& epi, int sms, cudaStream_t stream) {
+  if (pair)
+    return launch_pair<BLOCK_N, A_MN, B_MN, GATE_UP, K_GROUPED>(ta, tb, args, s, epi, sms, stream);
+  return launch_single<BLOCK_N, A_MN, B_MN, GATE_UP, K_GROUPED>(ta, tb, args, epi, sms, stream);
 }
 
 static GemmArgs base_args(const Schedule& s, int* status) {
@@ -108,7 +158,7 @@ int launch_fc1(const Schedule& s, const __nv_bfloat16* x, const __nv_bfloat16* w
   a.b_group_rows = 2 * inter;
   a.gate_up_half = inter;
   EpilogueSwiglu epi{u, ab, row_prob, inter};
-  return launch<256, false, false, true, false>(ta, tb, a, epi, sms, stream);
+  return launch<256, false, false, true, false>(use_pairs(s, false), ta, tb, a, s, epi, sms, stream);
 }
 
 template <bool B_MN>
@@ -122,10 +172,14 @@ static int launch_mgrouped(const Schedule& s, const __nv_bfloat16* a_ptr, const 
     set_error("grouped GEMM needs N %% 128 == 0, got %d", n);
     return 2;
   }
+  const bool pair = use_pairs(s, B_MN);  // B MN-major = dU / dX
   if (B_MN) {
     if (int rc = make_tmap_2d(&tb, b_ptr, 2, n, (uint64_t)s.groups * k, (uint64_t)n * 2, 64, 64)) return rc;
   } else {
-    if (int rc = make_tmap_2d(&tb, b_ptr, 2, k, (uint64_t)s.groups * n, (uint64_t)k * 2, 64, bn)) return rc;
+    // K-major B: one box is the whole N tile (one CTA) or this CTA's half of it (CTA pair)
+    if (int rc = make_tmap_2d(&tb, b_ptr, 2, k, (uint64_t)s.groups * n, (uint64_t)k * 2, 64,
+                              pair ? bn / 2 : bn))
+      return rc;
   }
   GemmArgs a = base_args(s, status);
   a.n_tiles = n / bn;
@@ -136,19 +190,19 @@ static int launch_mgrouped(const Schedule& s, const __nv_bfloat16* a_ptr, const 
       EpiloguePush<256> epi{};
       for (int r = 0; r < kMaxPeers; ++r) epi.mailbox[r] = push->mailbox[r];
       epi.origin = push->origin; epi.cap = push->cap; epi.top_k = push->top_k; epi.ld = n;
-      return launch<256, false, B_MN, false, false>(ta, tb, a, epi, sms, stream);
+      return launch<256, false, B_MN, false, false>(pair, ta, tb, a, s, epi, sms, stream);
     }
     EpiloguePush<128> epi{};
     for (int r = 0; r < kMaxPeers; ++r) epi.mailbox[r] = push->mailbox[r];
     epi.origin = push->origin; epi.cap = push->cap; epi.top_k = push->top_k; epi.ld = n;
-    return launch<128, false, B_MN, false, false>(ta, tb, a, epi, sms, stream);
+    return launch<128, false, B_MN, false, false>(pair, ta, tb, a, s, epi, sms, stream);
   }
   if (bn == 256) {
     EpilogueStore<256> epi{out, 0, n};
-    return launch<256, false, B_MN, false, false>(ta, tb, a, epi, sms, stream);
+    return launch<256, false, B_MN, false, false>(pair, ta, tb, a, s, epi, sms, stream);
   }
   EpilogueStore<128> epi{out, 0, n};
-  return launch<128, false, B_MN, false, false>(ta, tb, a, epi, sms, stream);
+  return launch<128, false, B_MN, false, false>(pair, ta, tb, a, s, epi, sms, stream);
 }
 
 int launch_mgrouped_nt(const Schedule& s, const __nv_bfloat16* a, const __nv_bfloat16* b,
@@ -173,15 +227,16 @@ int launch_kgrouped_tn(const Schedule& s, const __nv_bfloat16* a_ptr, const __nv
   if (int rc = make_tmap_2d(&ta, a_ptr, 2, m, s.row_capacity, (uint64_t)m * 2, 64, 64)) return rc;
   if (int rc = make_tmap_2d(&tb, b_ptr, 2, n, s.row_capacity, (uint64_t)n * 2, 64, 64)) return rc;
   const int bn = (n % 256 == 0) ? 256 : 128;
+  const bool pair = use_pairs(s, true) && m % 256 == 0;  // a pair covers 256 output rows
   GemmArgs a = base_args(s, status);
   a.m_tiles_per_group = m / 128;
   a.n_tiles = n / bn;
   if (bn == 256) {
     EpilogueStore<256> epi{out, (long long)m * n, n};
-    return launch<256, true, true, false, true>(ta, tb, a, epi, sms, stream);
+    return launch<256, true, true, false, true>(pair, ta, tb, a, s, epi, sms, stream);
   }
   EpilogueStore<128> epi{out, (long long)m * n, n};
-  return launch<128, true, true, false, true>(ta, tb, a, epi, sms, stream);
+  return launch<128, true, true, false, true>(pair, ta, tb, a, s, epi, sms, stream);
 }
 
 }  // namespace wm

@@ -267,185 +267,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
 }
 
-// ---------------------------------------------------------------------------- epilogues
-
-// 32 packed BF16 columns (16 words) of row `lane` into chunk group c32 (0..3) of the staging block.
-__device__ __forceinline__ void stage_put32(uint8_t* stage, int lane, int c32, const uint32_t (&w)[16]) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int pos = (c32 * 4 + j) ^ (lane & 15);
-    *reinterpret_cast<uint4*>(stage + lane * 256 + pos * 16) =
-        make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-  }
-}
-// Accumulator columns [col, col+32) of this thread's row, rounded to BF16 and packed.
-__device__ __forceinline__ void load_pack32(uint32_t taddr, bool zero, uint32_t (&w)[16]) {
-  if (zero) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) w[j] = 0;
-    return;
-  }
-  uint32_t v[32];
-  tmem_ld_32x32(taddr, v);
-  tmem_ld_wait();
-#pragma unroll
-  for (int j = 0; j < 16; ++j)
-    w[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-}
-// Write the staged 32 x 128 block: half-warp h handles row 2*it + h, lane&15 picks the 16-byte
-// chunk.  `row_dst(r)` returns the global address of column 0 of the block in row r (or nullptr
-// to skip the row).
-template <class RowDst>
-__device__ __forceinline__ void stage_flush(const uint8_t* stage, int lane, RowDst row_dst) {
-  const int c = lane & 15;
-#pragma unroll 4
-  for (int it = 0; it < 16; ++it) {
-    const int r = 2 * it + (lane >> 4);
-    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((c ^ (r & 15)) << 4));
-    __nv_bfloat16* dst = row_dst(r);
-    if (dst != nullptr) *reinterpret_cast<uint4*>(dst + c * 8) = v;
-  }
-}
-
-// Plain BF16 store: out[(group_base) + row, col] with leading dimension ld.
-//   M-grouped: row = m_tile*128 + r.   K-grouped: out + group*group_stride, row = m_tile*128 + r.
-template <int BLOCK_N>
-struct EpilogueStore {
-  __nv_bfloat16* out;
-  long long group_stride;  // elements between experts (K-grouped), 0 for M-grouped
-  int ld;
-
-  __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane,
-                                             bool zero, uint8_t* stage) const {
-    const long long row0 = static_cast<long long>(t.m_tile) * kBlockM + q * 32;
-    __nv_bfloat16* base = out + group_stride * t.group + row0 * ld + t.n_tile * BLOCK_N;
-#pragma unroll 1
-    for (int half = 0; half < BLOCK_N / 128; ++half) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t w[16];
-        load_pack32(taddr + half * 128 + c * 32, zero, w);
-        stage_put32(stage, lane, c, w);
-      }
-      __syncwarp();
-      __nv_bfloat16* block = base + half * 128;
-      const int ldl = ld;
-      stage_flush(stage, lane, [block, ldl](int r) { return block + static_cast<long long>(r) * ldl; });
-      __syncwarp();
-    }
-  }
-};
-
-// FC1 epilogue (reference: src/cuda/blackwell/fused/impls/routed_bf16.cuh:874-1027):
-// accumulator columns [0,128) are gate, [128,256) are up for intermediate columns
-// n_tile*128 .. +127.  gate and up are rounded to BF16 first (that rounded pair is what the
-// training cache stores), then u = bf16( silu(gate) * up * prob ).
-struct EpilogueSwiglu {
-  __nv_bfloat16* u;         // [rows, I]
-  __nv_bfloat16* ab;        // [rows, 2I] or nullptr (inference)
-  const float* row_prob;    // [rows] gate probability of the routed row (0 on padding rows)
-  int inter;                // I
-
-  __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane,
-                                             bool, uint8_t* stage) const {
-    const long long row0 = static_cast<long long>(t.m_tile) * kBlockM + q * 32;
-    const float prob = row_prob[row0 + lane];
-    const int col0 = t.n_tile * 128;
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      uint32_t g[32], b[32];
-      tmem_ld_32x32(taddr + c * 32, g);
-      tmem_ld_32x32(taddr + 128 + c * 32, b);
-      tmem_ld_wait();
-      uint32_t pu[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float g0 = bf16_round(__uint_as_float(g[2 * j])), g1 = bf16_round(__uint_as_float(g[2 * j + 1]));
-        const float b0 = bf16_round(__uint_as_float(b[2 * j])), b1 = bf16_round(__uint_as_float(b[2 * j + 1]));
-        const float u0 = (g0 / (1.0f + __expf(-g0))) * b0 * prob;
-        const float u1 = (g1 / (1.0f + __expf(-g1))) * b1 * prob;
-        pu[j] = pack_bf16x2(u0, u1);
-      }
-      stage_put32(stage, lane, c, pu);
-    }
-    __syncwarp();
-    {
-      __nv_bfloat16* block = u + row0 * inter + col0;
-      const int ldl = inter;
-      stage_flush(stage, lane, [block, ldl](int r) { return block + static_cast<long long>(r) * ldl; });
-    }
-    __syncwarp();
-    if (ab != nullptr) {
-      // Training cache: the BF16-rounded gate and up halves, re-read from TMEM.
-#pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t w[16];
-          load_pack32(taddr + half * 128 + c * 32, false, w);
-          stage_put32(stage, lane, c, w);
-        }
-        __syncwarp();
-        __nv_bfloat16* block = ab + row0 * (2 * inter) + half * inter + col0;
-        const int ldl = 2 * inter;
-        stage_flush(stage, lane, [block, ldl](int r) { return block + static_cast<long long>(r) * ldl; });
-        __syncwarp();
-      }
-    }
-  }
-};
-
-// Return epilogue (FC2 contributions and backward dX rows): each routed row is written as
-// BF16 into the SOURCE rank's mailbox [sorted_slot][token][N], local or over NVLink through
-// the peer-mapped arena (reference: routed_bf16.cuh:1028-1139 and
-// weftmoe/blackwell_backward.py:116-144).  origin = src_rank*cap*K + token*K + sorted_slot,
-// -1 on padding rows.
-constexpr int kMaxRanks = 8;
-template <int BLOCK_N>
-struct EpiloguePush {
-  __nv_bfloat16* mailbox[kMaxRanks];  // peer-mapped base of each rank's mailbox
-  const int* origin;                  // [rows]
-  int cap;                            // tokens capacity per rank
-  int top_k;
-  int ld;                             // N_total (hidden)
-
-  __device__ __forceinline__ __nv_bfloat16* select_mailbox(int src) const {
-    __nv_bfloat16* p = mailbox[0];
-#pragma unroll
-    for (int r = 1; r < kMaxRanks; ++r)
-      if (src == r) p = mailbox[r];
-    return p;
-  }
-
-  __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane,
-                                             bool, uint8_t* stage) const {
-    const long long row = static_cast<long long>(t.m_tile) * kBlockM + q * 32 + lane;
-    const int org = origin[row];
-    unsigned long long my_dst = 0;  // destination of column n_tile*BLOCK_N of this thread's row
-    if (org >= 0) {
-      const int per_rank = cap * top_k;
-      const int src = org / per_rank;
-      const int rem = org - src * per_rank;
-      const int token = rem / top_k, slot = rem - token * top_k;
-      my_dst = reinterpret_cast<unsigned long long>(
-          select_mailbox(src) + (static_cast<long long>(slot) * cap + token) * ld + t.n_tile * BLOCK_N);
-    }
-#pragma unroll 1
-    for (int half = 0; half < BLOCK_N / 128; ++half) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t w[16];
-        load_pack32(taddr + half * 128 + c * 32, false, w);
-        stage_put32(stage, lane, c, w);
-      }
-      __syncwarp();
-      stage_flush(stage, lane, [my_dst, half](int r) {
-        const unsigned long long d = __shfl_sync(0xffffffffu, my_dst, r);
-        return d ? reinterpret_cast<__nv_bfloat16*>(d) + half * 128 : nullptr;
-      });
-      __syncwarp();
-    }
-  }
-};
-
 }  // namespace wm
+
+#include "epilogue.cuh"

@@ -18,6 +18,8 @@ const char* last_error();
 // Process-wide count of kernels this library has launched (read through wm_launch_count()).
 void count_launch(int n = 1);
 long long launch_count();
+// Kernel choice override for tests and A/B runs: -1 automatic, 0 one-CTA kernel, 1 CTA-pair kernel.
+void force_gemm_pairs(int mode);
 #define WM_CUDA(expr)                                                                 \
   do {                                                                                \
     cudaError_t e_ = (expr);                                                          \
@@ -41,6 +43,9 @@ struct Schedule {
   const int* group_row_start;  // device [groups + 1]
   int groups;
   int row_capacity;            // rows addressable in the row-indexed operands
+  const int* num_pairs;        // device scalar: CTA-pair work items (two tiles of one expert)
+  const int* pair_tiles;       // device [2 * pairs]
+  bool many_rows_per_expert;   // host estimate: experts average >= 1024 rows (long K loops, few odd tiles)
 };
 
 struct PushTarget {

@@ -144,13 +144,31 @@ __global__ void global_plan_kernel(const int* __restrict__ count_matrix, const i
   if (*t.num_tiles == 0 && *t.padded_rows == 0) {
     // overflow or no rows: still publish zeroed starts so K-grouped GEMMs write zero gradients
     for (int l = threadIdx.x; l <= e_local; l += blockDim.x) t.padded_start[l] = 0;
+    if (threadIdx.x == 0) *t.num_pairs = 0;
     return;
   }
+  // CTA-pair schedule: consecutive 128-row tiles of one expert are paired; an odd last tile
+  // is paired with -1.  pair_first[l] = pairs of lower local experts (sequential, E/EP <= 512).
+  __shared__ int pair_first[513];
+  if (threadIdx.x == 0) {
+    int p = 0;
+    for (int l = 0; l < e_local; ++l) {
+      pair_first[l] = p;
+      p += (padded[rank * e_local + l] / 128 + 1) / 2;
+    }
+    *t.num_pairs = p;
+  }
+  __syncthreads();
   for (int l = threadIdx.x; l < e_local; l += blockDim.x) {
     const int e = rank * e_local + l;
     const int start = t.expert_pbase[e];
+    const int tiles = padded[e] / 128;
     t.padded_start[l] = start;
-    for (int k = 0; k < padded[e] / 128; ++k) t.tile_group[start / 128 + k] = l;
+    for (int k = 0; k < tiles; ++k) t.tile_group[start / 128 + k] = l;
+    for (int j = 0; j < (tiles + 1) / 2; ++j) {
+      t.pair_tiles[2 * (pair_first[l] + j)] = start / 128 + 2 * j;
+      t.pair_tiles[2 * (pair_first[l] + j) + 1] = (2 * j + 1 < tiles) ? start / 128 + 2 * j + 1 : -1;
+    }
   }
 }
 

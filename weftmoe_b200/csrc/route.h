@@ -40,6 +40,8 @@ struct PlanTables {
   int* tile_group;     // [row_capacity / 128] local expert of each 128-row tile
   int* num_tiles;      // scalar
   int* padded_rows;    // scalar
+  int* pair_tiles;     // [2 * pairs] two 128-row tiles of one expert per CTA pair, -1 = none
+  int* num_pairs;      // scalar
 };
 
 int route_local(const RouteShape& s, const int* routes, int tokens, RouteLocal out,

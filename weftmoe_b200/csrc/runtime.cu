@@ -61,12 +61,13 @@ struct ArenaLayout {
 struct ScratchLayout {
   size_t status, sorted_slot, sorted_expert, slot_pos, local_offset, dst_rank, dst_row, dst_prow,
       chunk_hist, local_count, expert_total, expert_before, expert_base, expert_pbase, padded_start,
-      tile_group, num_tiles, padded_rows, origin, prob, xrows, u, recv, du, dab, total;
+      tile_group, num_tiles, padded_rows, pair_tiles, num_pairs, origin, prob, xrows, u, recv, du, dab,
+      total;
 };
 // Training cache carved out of the caller's tape buffer.
 struct TapeLayout {
-  size_t sorted_slot, sorted_expert, padded_start, tile_group, num_tiles, padded_rows, origin, prob,
-      xrows, ab, total;
+  size_t sorted_slot, sorted_expert, padded_start, tile_group, num_tiles, padded_rows, pair_tiles,
+      num_pairs, origin, prob, xrows, ab, total;
 };
 
 }  // namespace
@@ -132,6 +133,8 @@ ScratchLayout scratch_layout(const wm_config& c, int row_cap) {
   s.tile_group = k.take(sizeof(int) * (row_cap / 128 + 1));
   s.num_tiles = k.take(sizeof(int));
   s.padded_rows = k.take(sizeof(int));
+  s.pair_tiles = k.take(sizeof(int) * 2 * (row_cap / 128 + 1));
+  s.num_pairs = k.take(sizeof(int));
   s.origin = k.take(sizeof(int) * row_cap);
   s.prob = k.take(sizeof(float) * row_cap);
   s.xrows = k.take(2ull * row_cap * c.hidden);
@@ -156,6 +159,8 @@ TapeLayout tape_layout(const wm_config& c, int row_cap) {
   t.tile_group = k.take(sizeof(int) * (row_cap / 128 + 1));
   t.num_tiles = k.take(sizeof(int));
   t.padded_rows = k.take(sizeof(int));
+  t.pair_tiles = k.take(sizeof(int) * 2 * (row_cap / 128 + 1));
+  t.num_pairs = k.take(sizeof(int));
   t.origin = k.take(sizeof(int) * row_cap);
   t.prob = k.take(sizeof(float) * row_cap);
   t.xrows = k.take(2ull * row_cap * c.hidden);
@@ -444,6 +449,8 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
   tables.tile_group = tape ? at<int>(T, rt->tl.tile_group) : at<int>(S, rt->sl.tile_group);
   tables.num_tiles = tape ? at<int>(T, rt->tl.num_tiles) : at<int>(S, rt->sl.num_tiles);
   tables.padded_rows = tape ? at<int>(T, rt->tl.padded_rows) : at<int>(S, rt->sl.padded_rows);
+  tables.pair_tiles = tape ? at<int>(T, rt->tl.pair_tiles) : at<int>(S, rt->sl.pair_tiles);
+  tables.num_pairs = tape ? at<int>(T, rt->tl.num_pairs) : at<int>(S, rt->sl.num_pairs);
   int* origin = tape ? at<int>(T, rt->tl.origin) : at<int>(S, rt->sl.origin);
   float* prob = tape ? at<float>(T, rt->tl.prob) : at<float>(S, rt->sl.prob);
   auto* xrows = tape ? at<__nv_bfloat16>(T, rt->tl.xrows) : at<__nv_bfloat16>(S, rt->sl.xrows);
@@ -509,7 +516,8 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
   }
   if (world > 1)
     if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
-  Schedule sched{tables.num_tiles, tables.tile_group, tables.padded_start, rt->e_local, rt->row_cap};
+  Schedule sched{tables.num_tiles, tables.tile_group, tables.padded_start, rt->e_local, rt->row_cap,
+                 tables.num_pairs, tables.pair_tiles, false};
   {
     StageScope scope(timing, kStageFc1, stream);
     if (int rc = launch_fc1(sched, xrows, static_cast<const __nv_bfloat16*>(w1), u, ab, prob,
@@ -564,6 +572,8 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
   const int* tile_group = reinterpret_cast<const int*>(tp(rt->tl.tile_group));
   const int* num_tiles = reinterpret_cast<const int*>(tp(rt->tl.num_tiles));
   const int* padded_rows = reinterpret_cast<const int*>(tp(rt->tl.padded_rows));
+  const int* pair_tiles = reinterpret_cast<const int*>(tp(rt->tl.pair_tiles));
+  const int* num_pairs = reinterpret_cast<const int*>(tp(rt->tl.num_pairs));
   const int* origin = reinterpret_cast<const int*>(tp(rt->tl.origin));
   const float* prob = reinterpret_cast<const float*>(tp(rt->tl.prob));
   const auto* xrows = reinterpret_cast<const __nv_bfloat16*>(tp(rt->tl.xrows));
@@ -607,7 +617,10 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
   }
   if (world > 1)
     if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
-  Schedule sched{num_tiles, tile_group, padded_start, rt->e_local, rt->row_cap};
+  // Rows per local expert if routing were uniform: tokens * K * world / E.
+  const bool many_rows = 1ll * tokens * c.top_k * world >= 1024ll * c.experts;
+  Schedule sched{num_tiles, tile_group, padded_start, rt->e_local, rt->row_cap, num_pairs, pair_tiles,
+                 many_rows};
   // 3. dU = dY * W2 ; SwiGLU backward (U, dAB, dprob -> sources) ; dX = dAB * W1 -> sources.
   {
     StageScope scope(timing, kStageDu, stream);
@@ -674,6 +687,7 @@ extern "C" int wm_route_plan(int32_t phase, int32_t world, int32_t rank, int32_t
   const size_t o_before = k.take(sizeof(int) * experts);
   const size_t o_status = k.take(sizeof(int));
   const size_t o_flags = k.take(sizeof(int) * kMaxWorld * kFlagStride);
+  const size_t o_pairs = k.take(sizeof(int) * (2 * (row_capacity / 128 + 1) + 1));
   uint8_t* tmp = nullptr;
   WM_CUDA(cudaMalloc(&tmp, k.cursor));
   WM_CUDA(cudaMemsetAsync(tmp + o_status, 0, k.cursor - o_status, stream));
@@ -686,7 +700,8 @@ extern "C" int wm_route_plan(int32_t phase, int32_t world, int32_t rank, int32_t
   int device_code = 0;
   if (!rc && phase == 1) {
     PlanTables t{out->expert_total, at<int>(tmp, o_before), out->expert_base, out->expert_pbase,
-                 out->padded_start, out->tile_group, out->num_tiles, out->padded_rows};
+                 out->padded_start, out->tile_group, out->num_tiles, out->padded_rows,
+                 at<int>(tmp, o_pairs) + 1, at<int>(tmp, o_pairs)};
     // No exchange to wait for: generation 0 is satisfied by the zeroed flag words.
     rc = route_global(shape, count_matrix, at<int>(tmp, o_flags), 0, row_capacity, t,
                       at<int>(tmp, o_status), stream);
