@@ -92,11 +92,11 @@ def main():
             print(f"EP{world} {scenario}: oracle parity, bitwise repeat and EP1 == EP{world} bits passed", flush=True)
     # ---- received rows beyond max_rows: a collective, reported error, runtime stays usable
     small = TensorRuntime(group=dist.group.WORLD, experts=E, top_k=K, hidden=H, intermediate=I,
-                          max_tokens=64, max_rows=128, training=False)
+                          max_tokens=512, max_rows=128, training=False)
     g = torch.Generator().manual_seed(5 + rank)
-    x = torch.randn(64, H, generator=g).bfloat16().cuda()
-    routes = torch.zeros(64, K, dtype=torch.int32).cuda() + torch.arange(K, dtype=torch.int32).cuda()  # all to rank 0
-    gates = torch.rand(64, K, generator=g).cuda()
+    x = torch.randn(512, H, generator=g).bfloat16().cuda()
+    routes = torch.zeros(512, K, dtype=torch.int32).cuda() + torch.arange(K, dtype=torch.int32).cuda()  # all to rank 0
+    gates = torch.rand(512, K, generator=g).cuda()
     lw1, lw2 = w1.chunk(world)[rank].cuda(), w2.chunk(world)[rank].cuda()
     failed = False
     try:
