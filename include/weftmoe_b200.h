@@ -144,6 +144,20 @@ WM_API int wm_route_plan(int32_t phase, int32_t world, int32_t rank, int32_t exp
                          int32_t tokens, int32_t cap, int32_t row_capacity, const int32_t* routes,
                          int32_t* count_matrix, const wm_route_out* out, void* stream);
 
+/* Route planning for callers that must not allocate.  It has no counterpart in the reference.
+ * Same arguments, outputs and phases as wm_route_plan, but no cudaMalloc/cudaFree: the temporaries
+ * live in a fixed 1 MiB __device__ array inside the library (held by every GPU that loads it until
+ * the process exits).  Meant for hosts whose own pool owns all free HBM, and for latency-critical
+ * paths where cudaMalloc's device-wide synchronisation would stall every stream.
+ * Limits: tokens * top_k <= 131072, experts <= 512, row_capacity <= 262144; larger requests return
+ * WM_ERR_CAPACITY with a message that names the limit.  The first call on a device looks up the
+ * array's device address (cudaGetSymbolAddress); make that first call outside stream capture.
+ * All calls on a device share the array, so calls whose GPU work overlaps race: serialise them. */
+WM_API int wm_route_plan_noalloc(int32_t phase, int32_t world, int32_t rank, int32_t experts,
+                                 int32_t top_k, int32_t tokens, int32_t cap, int32_t row_capacity,
+                                 const int32_t* routes, int32_t* count_matrix, const wm_route_out* out,
+                                 void* stream);
+
 /* Diagnostic: one grouped GEMM on caller buffers (synchronises `stream`).
  * kind 0: out[rows,n]   = a[rows,k] * b[g][n,k]^T          (FC2 form)
  * kind 1: out[rows,n]   = a[rows,k] * b[g][k,n]            (dU / dX form)

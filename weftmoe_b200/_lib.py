@@ -53,6 +53,7 @@ SIGNATURES = {
     "wm_runtime_enable_timing": (c_int, [c_void_p, c_int]),
     "wm_runtime_read_timing": (c_int, [c_void_p, POINTER(ctypes.c_double), POINTER(ctypes.c_longlong), c_int]),
     "wm_route_plan": (c_int, [c_int32] * 8 + [c_void_p, c_void_p, POINTER(WmRouteOut), c_void_p]),
+    "wm_route_plan_noalloc": (c_int, [c_int32] * 8 + [c_void_p, c_void_p, POINTER(WmRouteOut), c_void_p]),
     "wm_debug_force_gemm_pairs": (None, [c_int]),
     "wm_debug_grouped_gemm": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       POINTER(c_int), c_int, c_int, c_int, c_void_p, c_void_p]),
