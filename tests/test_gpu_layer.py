@@ -187,3 +187,37 @@ def test_received_rows_beyond_max_rows_are_reported_not_corrupted():
     y = rt.inference_eager(g["x"][:64], g["routes"][:64], g["gates"][:64], g["w1"], g["w2"])  # still usable
     assert torch.isfinite(y.float()).all()
     rt.close()
+
+
+def test_decode_under_cuda_graph_replays_and_matches_eager_bits():
+    """DT contract (docs/usage.md:104-112, tests/torchrun_pf_dt.py:37-79 in the reference): after a
+    warm-up outside capture, `inference` can be captured in a caller's CUDA graph (no host sync, no
+    allocation by the native side), replays read fresh inputs from the same addresses, and decode
+    results equal the prefill/eager path bit for bit."""
+    cfg = dict(experts=32, top_k=6, hidden=1024, intermediate=512, tokens=64)
+    a = on_gpu(O.make_inputs(cfg, seed=1300, x_std=1.0))
+    b = on_gpu(O.make_inputs(cfg, seed=1301, x_std=1.0))
+    rt = runtime(cfg, cfg["tokens"], training=False)
+    x, routes, gates = a["x"].clone(), a["routes"].clone(), a["gates"].clone()
+    eager_a = rt.inference_eager(a["x"], a["routes"], a["gates"], a["w1"], a["w2"])
+    eager_b = rt.inference_eager(b["x"], b["routes"], b["gates"], a["w1"], a["w2"])
+    rt.inference(0, x, routes, gates, a["w1"], a["w2"])          # warm-up of this layer outside capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y = rt.inference(0, x, routes, gates, a["w1"], a["w2"])
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(bits(y), bits(eager_a))
+    x.copy_(b["x"]); routes.copy_(b["routes"]); gates.copy_(b["gates"])
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(bits(y), bits(eager_b))
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(bits(y), bits(eager_b))
+    ref = O.moe_layer(b["x"].cpu(), b["routes"].cpu(), b["gates"].cpu(), a["w1"].cpu(), a["w2"].cpu())[0]
+    assert rel_l2(y, ref) < TOL_ROUNDED_ORACLE
+    del graph
+    rt.close()
