@@ -30,20 +30,19 @@ extern "C" int wm_debug_grouped_gemm(int kind, const void* a, const void* b, voi
       pairs.push_back(2 * j + 1 < tiles ? first + 2 * j + 1 : -1);
     }
   }
-  int num_pairs = static_cast<int>(pairs.size() / 2);
+  const int num_pairs = static_cast<int>(pairs.size() / 2);
   pairs.push_back(-1);
   const int rows = starts[groups];
-  int num_tiles = static_cast<int>(tile_group.size());
+  const int num_tiles = static_cast<int>(tile_group.size());
   tile_group.push_back(0);
-  int *d_num = nullptr, *d_tiles = nullptr, *d_starts = nullptr, *d_pairs = nullptr, *d_npairs = nullptr;
+  int *d_num = nullptr, *d_tiles = nullptr, *d_starts = nullptr, *d_pairs = nullptr;
+  const int split[8] = {num_tiles, num_tiles, num_pairs, num_pairs, rows, rows, 0, 0};
   WM_CUDA(cudaMalloc(&d_pairs, pairs.size() * sizeof(int)));
-  WM_CUDA(cudaMalloc(&d_npairs, sizeof(int)));
   WM_CUDA(cudaMemcpyAsync(d_pairs, pairs.data(), pairs.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
-  WM_CUDA(cudaMemcpyAsync(d_npairs, &num_pairs, sizeof(int), cudaMemcpyHostToDevice, stream));
-  WM_CUDA(cudaMalloc(&d_num, sizeof(int)));
+  WM_CUDA(cudaMalloc(&d_num, sizeof(split)));
   WM_CUDA(cudaMalloc(&d_tiles, tile_group.size() * sizeof(int)));
   WM_CUDA(cudaMalloc(&d_starts, starts.size() * sizeof(int)));
-  WM_CUDA(cudaMemcpyAsync(d_num, &num_tiles, sizeof(int), cudaMemcpyHostToDevice, stream));
+  WM_CUDA(cudaMemcpyAsync(d_num, split, sizeof(split), cudaMemcpyHostToDevice, stream));
   WM_CUDA(cudaMemcpyAsync(d_tiles, tile_group.data(), tile_group.size() * sizeof(int),
                           cudaMemcpyHostToDevice, stream));
   WM_CUDA(cudaMemcpyAsync(d_starts, starts.data(), starts.size() * sizeof(int),
@@ -51,7 +50,7 @@ extern "C" int wm_debug_grouped_gemm(int kind, const void* a, const void* b, voi
   int sms = 0, dev = 0;
   WM_CUDA(cudaGetDevice(&dev));
   WM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  Schedule s{d_num, d_tiles, d_starts, groups, rows, d_npairs, d_pairs, rows >= 1024 * groups};
+  Schedule s{d_num, d_tiles, d_starts, groups, rows, d_pairs, rows >= 1024 * groups, kWhole};
   auto A = static_cast<const __nv_bfloat16*>(a);
   auto B = static_cast<const __nv_bfloat16*>(b);
   auto O = static_cast<__nv_bfloat16*>(out);
@@ -73,7 +72,6 @@ extern "C" int wm_debug_grouped_gemm(int kind, const void* a, const void* b, voi
   cudaFree(d_tiles);
   cudaFree(d_starts);
   cudaFree(d_pairs);
-  cudaFree(d_npairs);
   if (rc) return rc;
   if (e != cudaSuccess) {
     set_error("wm_debug_grouped_gemm: %s", cudaGetErrorString(e));

@@ -120,7 +120,8 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
     WM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  Gemm2Args a2{args, s.num_pairs, s.pair_tiles};
+  const DeviceRange pairs = split_range(s.split, 1, s.half);
+  Gemm2Args a2{args, pairs.begin, pairs.end, s.pair_tiles};
   kernel<<<sms & ~1, kGemmThreads, smem, stream>>>(ta, tb, a2, epi);  // clusters of two CTAs
   WM_CUDA(cudaGetLastError());
   count_launch();
@@ -137,7 +138,9 @@ static int launch(bool pair, const CUtensorMap& ta, const CUtensorMap& tb, const
 
 static GemmArgs base_args(const Schedule& s, int* status) {
   GemmArgs a{};
-  a.num_m_tiles = s.num_m_tiles;
+  const DeviceRange tiles = split_range(s.split, 0, s.half);
+  a.tile_begin = tiles.begin;
+  a.tile_end = tiles.end;
   a.tile_group = s.tile_group;
   a.group_row_start = s.group_row_start;
   a.groups = s.groups;

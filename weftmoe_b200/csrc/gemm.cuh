@@ -32,7 +32,8 @@ constexpr int kGemmThreads = 192;
 
 struct GemmArgs {
   // ---- schedule
-  const int* num_m_tiles;      // M-grouped: device scalar, number of live 128-row tiles
+  const int* tile_begin;       // M-grouped: device scalars, range of live 128-row tiles to process
+  const int* tile_end;
   const int* tile_group;       // M-grouped: expert of each 128-row tile
   const int* group_row_start;  // K-grouped: [groups + 1] padded row offsets (multiples of 64)
   int groups;                  // K-grouped: number of experts
@@ -147,11 +148,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  int total_tiles;
+  int total_tiles, first_tile = 0;
   if constexpr (K_GROUPED) {
     total_tiles = args.groups * args.m_tiles_per_group * args.n_tiles;
   } else {
-    total_tiles = __ldg(args.num_m_tiles) * args.n_tiles;
+    first_tile = __ldg(args.tile_begin) * args.n_tiles;
+    total_tiles = __ldg(args.tile_end) * args.n_tiles;
   }
 
   if (warp == 0) {
@@ -160,7 +162,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const TileCoord t = decode_tile<K_GROUPED>(args, tile);
         for (int kb = 0; kb < t.num_kb; ++kb) {
           ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, args.status,
@@ -212,7 +214,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const TileCoord t = decode_tile<K_GROUPED>(args, tile);
         ok = mbar_wait(tmem_empty + acc, acc_phase ^ 1, abort_flag, args.status,
                        kStatusTimeoutTmemEmpty);
@@ -245,7 +247,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+    for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
       const TileCoord t = decode_tile<K_GROUPED>(args, tile);
       ok = mbar_wait(tmem_full + acc, acc_phase, abort_flag, args.status, kStatusTimeoutTmemFull);
       if (!ok) break;

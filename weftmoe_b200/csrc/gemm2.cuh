@@ -36,7 +36,8 @@ struct Gemm2Smem {
 
 struct Gemm2Args {
   GemmArgs base;
-  const int* num_pairs;   // M-grouped: device scalar
+  const int* pair_begin;  // M-grouped: device scalars, range of pairs to process
+  const int* pair_end;
   const int* pair_tiles;  // M-grouped: [2 * pairs] 128-row tile indices, -1 = none
 };
 
@@ -132,11 +133,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  int total_work;
+  int total_work, first_work = 0;
   if constexpr (K_GROUPED) {
     total_work = args.groups * (args.m_tiles_per_group / 2) * args.n_tiles;
   } else {
-    total_work = __ldg(args2.num_pairs) * args.n_tiles;
+    first_work = __ldg(args2.pair_begin) * args.n_tiles;
+    total_work = __ldg(args2.pair_end) * args.n_tiles;
   }
 
   if (warp == 0) {
@@ -145,7 +147,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int work = cluster_id; ok && work < total_work; work += num_clusters) {
+      for (int work = first_work + cluster_id; ok && work < total_work; work += num_clusters) {
         const PairTile p = decode_pair<K_GROUPED>(args2, work, cta);
         const TileCoord& t = p.t;
         for (int kb = 0; kb < t.num_kb; ++kb) {
@@ -195,7 +197,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int work = cluster_id; ok && work < total_work; work += num_clusters) {
+      for (int work = first_work + cluster_id; ok && work < total_work; work += num_clusters) {
         const PairTile p = decode_pair<K_GROUPED>(args2, work, 0);
         ok = mbar_wait_cluster(tmem_empty + acc, acc_phase ^ 1, abort_flag, args.status,
                                kStatusTimeoutTmemEmpty);
@@ -232,7 +234,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int work = cluster_id; ok && work < total_work; work += num_clusters) {
+    for (int work = first_work + cluster_id; ok && work < total_work; work += num_clusters) {
       const PairTile p = decode_pair<K_GROUPED>(args2, work, cta);
       ok = mbar_wait_cluster(tmem_full + acc, acc_phase, abort_flag, args.status,
                              kStatusTimeoutTmemFull);

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "route.h"
 #include "status.h"
 
 namespace wm {
@@ -38,14 +39,14 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t in
 
 // ------------------------------------------------------------------ grouped GEMM launchers
 struct Schedule {
-  const int* num_m_tiles;      // device scalar
+  const int* split;            // device [8]: tile / pair / row split points and totals (route.h)
   const int* tile_group;       // device [max tiles]
   const int* group_row_start;  // device [groups + 1]
   int groups;
   int row_capacity;            // rows addressable in the row-indexed operands
-  const int* num_pairs;        // device scalar: CTA-pair work items (two tiles of one expert)
-  const int* pair_tiles;       // device [2 * pairs]
+  const int* pair_tiles;       // device [2 * pairs]: CTA-pair work items (two tiles of one expert)
   bool many_rows_per_expert;   // host estimate: experts average >= 1024 rows (long K loops, few odd tiles)
+  int half;                    // which part of the M-grouped work to run: 0 all, 1 first half, 2 second half
 };
 
 struct PushTarget {

@@ -145,6 +145,7 @@ __global__ void global_plan_kernel(const int* __restrict__ count_matrix, const i
     // overflow or no rows: still publish zeroed starts so K-grouped GEMMs write zero gradients
     for (int l = threadIdx.x; l <= e_local; l += blockDim.x) t.padded_start[l] = 0;
     if (threadIdx.x == 0) *t.num_pairs = 0;
+    if (t.split != nullptr && threadIdx.x < 8) t.split[threadIdx.x] = 0;
     return;
   }
   // CTA-pair schedule: consecutive 128-row tiles of one expert are paired; an odd last tile
@@ -157,6 +158,20 @@ __global__ void global_plan_kernel(const int* __restrict__ count_matrix, const i
       p += (padded[rank * e_local + l] / 128 + 1) / 2;
     }
     *t.num_pairs = p;
+    if (t.split != nullptr) {
+      // first expert boundary at or beyond half of the padded rows
+      const int total_rows = *t.padded_rows;
+      int rows = 0, l = 0;
+      while (l < e_local && 2 * rows < total_rows) rows += padded[rank * e_local + l++];
+      t.split[0] = rows / 128;
+      t.split[1] = total_rows / 128;
+      t.split[2] = l < e_local ? pair_first[l] : p;
+      t.split[3] = p;
+      t.split[4] = rows;
+      t.split[5] = total_rows;
+      t.split[6] = 0;
+      t.split[7] = 0;
+    }
   }
   __syncthreads();
   for (int l = threadIdx.x; l < e_local; l += blockDim.x) {

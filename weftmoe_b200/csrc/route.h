@@ -42,7 +42,24 @@ struct PlanTables {
   int* padded_rows;    // scalar
   int* pair_tiles;     // [2 * pairs] two 128-row tiles of one expert per CTA pair, -1 = none
   int* num_pairs;      // scalar
+  // Optional [8]: the owner's work split at an expert boundary near the middle, so that the second
+  // half's transfers can overlap the first half's compute:
+  //   [0] tile split  [1] tiles  [2] pair split  [3] pairs  [4] row split  [5] padded rows  [6] 0
+  int* split;
 };
+
+// A [begin, end) range held in device memory (two pointers into PlanTables::split).
+struct DeviceRange {
+  const int* begin;
+  const int* end;
+};
+enum SplitHalf { kWhole = 0, kFirstHalf = 1, kSecondHalf = 2 };
+inline DeviceRange split_range(const int* split, int what /*0 tiles, 1 pairs, 2 rows*/, int half) {
+  const int* zero = split + 6;
+  const int* mid = split + 2 * what;
+  const int* all = split + 2 * what + 1;
+  return DeviceRange{half == kSecondHalf ? mid : zero, half == kFirstHalf ? mid : all};
+}
 
 int route_local(const RouteShape& s, const int* routes, int tokens, RouteLocal out,
                 int* chunk_hist, int* local_count, const PeerInts& count_matrix,
@@ -57,7 +74,7 @@ int route_rows(const RouteShape& s, const int* routes, const float* gates, int t
 struct OwnerRows {
   const int* padded_start;  // [e_local + 1]
   const int* tile_group;    // [tiles]
-  const int* padded_rows;   // scalar
+  DeviceRange rows;         // padded rows to process
   const int* expert_total;  // [experts] (global ids)
 };
 
@@ -67,15 +84,18 @@ int wait_flags(const int* flags, int world, int generation, int* status, cudaStr
 int signal_peers(const PeerInts& flag_group, int world, int slot, int generation,
                  cudaStream_t stream);
 
+// The row-copy kernels take their CTA count: 8 CTAs of 8 warps per SM when they run alone (enough
+// loads in flight for HBM), 2 per SM when a half is copied beside a grouped GEMM (thread slots
+// must stay free for the GEMM's CTA; NVLink needs far fewer loads in flight than HBM).
 // Owner side, forward: pull every live row's activation from its source rank's staging buffer,
 // copy origin/prob words from the meta mailbox to local arrays, zero the padding rows.
 int gather_rows(const OwnerRows& o, int rank, int e_local, int cap, int top_k, int hidden,
                 const PeerConstRows& stage, const int* meta_origin, const float* meta_prob,
-                __nv_bfloat16* rows_out, int* origin_out, float* prob_out, int sms,
+                __nv_bfloat16* rows_out, int* origin_out, float* prob_out, int ctas,
                 cudaStream_t stream);
 // Owner side, backward: pull dY rows by the saved origins.
-int gather_by_origin(const int* padded_rows, const int* origin, int cap, int top_k, int hidden,
-                     const PeerConstRows& stage, __nv_bfloat16* rows_out, int sms,
+int gather_by_origin(DeviceRange rows, const int* origin, int cap, int top_k, int hidden,
+                     const PeerConstRows& stage, __nv_bfloat16* rows_out, int ctas,
                      cudaStream_t stream);
 // Source side: out[t] = bf16( sum over combine positions j with a live route of mailbox[j][t] ).
 int combine_rows(const __nv_bfloat16* mailbox, const int* sorted_expert, int tokens, int cap,
@@ -85,7 +105,7 @@ int unpermute_dgates(const float* dgate_box, const int* sorted_slot, const int* 
                      int tokens, int top_k, float* dgates, cudaStream_t stream);
 // Owner side, backward elementwise: from saved gate/up (ab), dU and prob compute
 // U = bf16(silu(a) b p), dAB, and the per-row dprob, which is sent to the source's dgate box.
-int swiglu_backward(const int* padded_rows, const __nv_bfloat16* ab, const __nv_bfloat16* du,
+int swiglu_backward(DeviceRange rows, const __nv_bfloat16* ab, const __nv_bfloat16* du,
                     const float* prob, const int* origin, int inter, int cap, int top_k,
                     __nv_bfloat16* u, __nv_bfloat16* dab, const PeerFloats& dgate_box, int sms,
                     cudaStream_t stream);

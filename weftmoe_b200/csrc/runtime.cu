@@ -30,12 +30,14 @@ enum FlagGroup { kCounts = 0, kReady = 1, kPulled = 2, kContrib = 3, kFlagGroups
 enum Stage {
   kStagePlan = 0, kStageGather, kStageFc1, kStageFc2, kStageCombine,
   kStageGatherDy, kStageDu, kStageSwigluBwd, kStageDx, kStageDw1, kStageDw2, kStageCombineDx,
+  // second halves (world > 1 only; the copies of the second half run on the side stream, untimed)
+  kStageFc1B, kStageFc2B, kStageDuB, kStageSwigluBwdB, kStageDxB,
   kStageCount
 };
 const char* const kStageNames[kStageCount] = {
     "route_plan", "gather_rows", "fc1_swiglu", "fc2_push", "combine",
     "gather_dy", "dgrad_du", "swiglu_backward", "dgrad_dx_push", "wgrad_dw1", "wgrad_dw2",
-    "combine_dx"};
+    "combine_dx", "fc1_swiglu_b", "fc2_push_b", "dgrad_du_b", "swiglu_backward_b", "dgrad_dx_push_b"};
 constexpr int kTimingRing = 32;
 struct TimingSlot {
   cudaEvent_t start[kStageCount] = {};
@@ -61,13 +63,13 @@ struct ArenaLayout {
 struct ScratchLayout {
   size_t status, sorted_slot, sorted_expert, slot_pos, local_offset, dst_rank, dst_row, dst_prow,
       chunk_hist, local_count, expert_total, expert_before, expert_base, expert_pbase, padded_start,
-      tile_group, num_tiles, padded_rows, pair_tiles, num_pairs, origin, prob, xrows, u, recv, du, dab,
-      total;
+      tile_group, num_tiles, padded_rows, pair_tiles, num_pairs, split, origin, prob, xrows, u, recv, du,
+      dab, total;
 };
 // Training cache carved out of the caller's tape buffer.
 struct TapeLayout {
   size_t sorted_slot, sorted_expert, padded_start, tile_group, num_tiles, padded_rows, pair_tiles,
-      num_pairs, origin, prob, xrows, ab, total;
+      num_pairs, split, origin, prob, xrows, ab, total;
 };
 
 }  // namespace
@@ -82,6 +84,10 @@ struct wm_runtime {
   uint8_t* scratch = nullptr;
   uint8_t* peer[kMaxWorld] = {};
   bool peers_ready = false;
+  // world > 1: the second half of the owner's rows is pulled on a side stream while the first
+  // half is being computed (inbound NVLink beside compute and outbound pushes).
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_first_pulled = nullptr, ev_second_pulled = nullptr;
   // Optional per-stage device timing (CUDA events on the caller's stream).
   bool timing = false;
   int timing_slot = 0;
@@ -135,6 +141,7 @@ ScratchLayout scratch_layout(const wm_config& c, int row_cap) {
   s.padded_rows = k.take(sizeof(int));
   s.pair_tiles = k.take(sizeof(int) * 2 * (row_cap / 128 + 1));
   s.num_pairs = k.take(sizeof(int));
+  s.split = k.take(sizeof(int) * 8);
   s.origin = k.take(sizeof(int) * row_cap);
   s.prob = k.take(sizeof(float) * row_cap);
   s.xrows = k.take(2ull * row_cap * c.hidden);
@@ -161,6 +168,7 @@ TapeLayout tape_layout(const wm_config& c, int row_cap) {
   t.padded_rows = k.take(sizeof(int));
   t.pair_tiles = k.take(sizeof(int) * 2 * (row_cap / 128 + 1));
   t.num_pairs = k.take(sizeof(int));
+  t.split = k.take(sizeof(int) * 8);
   t.origin = k.take(sizeof(int) * row_cap);
   t.prob = k.take(sizeof(float) * row_cap);
   t.xrows = k.take(2ull * row_cap * c.hidden);
@@ -314,6 +322,15 @@ extern "C" int wm_runtime_create(const wm_config* config, wm_runtime** out) {
     set_error("workspace initialisation failed: %s", cudaGetErrorString(e));
     return fail(WM_ERR_CUDA);
   }
+  if (rt->cfg.world > 1) {
+    e = cudaStreamCreateWithFlags(&rt->side, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&rt->ev_first_pulled, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&rt->ev_second_pulled, cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+      set_error("side stream creation failed: %s", cudaGetErrorString(e));
+      return fail(WM_ERR_CUDA);
+    }
+  }
   rt->peer[rt->cfg.rank] = rt->arena;
   rt->peers_ready = rt->cfg.world == 1;
   *out = rt;
@@ -385,6 +402,9 @@ extern "C" int wm_runtime_retire_peers(wm_runtime* rt) {
 extern "C" int wm_runtime_destroy(wm_runtime* rt) {
   if (!rt) return WM_OK;
   wm_runtime_retire_peers(rt);
+  if (rt->side) cudaStreamDestroy(rt->side);
+  if (rt->ev_first_pulled) cudaEventDestroy(rt->ev_first_pulled);
+  if (rt->ev_second_pulled) cudaEventDestroy(rt->ev_second_pulled);
   if (rt->arena) cudaFree(rt->arena);
   if (rt->scratch) cudaFree(rt->scratch);
   rt->arena = rt->scratch = nullptr;
@@ -451,6 +471,7 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
   tables.padded_rows = tape ? at<int>(T, rt->tl.padded_rows) : at<int>(S, rt->sl.padded_rows);
   tables.pair_tiles = tape ? at<int>(T, rt->tl.pair_tiles) : at<int>(S, rt->sl.pair_tiles);
   tables.num_pairs = tape ? at<int>(T, rt->tl.num_pairs) : at<int>(S, rt->sl.num_pairs);
+  tables.split = tape ? at<int>(T, rt->tl.split) : at<int>(S, rt->sl.split);
   int* origin = tape ? at<int>(T, rt->tl.origin) : at<int>(S, rt->sl.origin);
   float* prob = tape ? at<float>(T, rt->tl.prob) : at<float>(S, rt->sl.prob);
   auto* xrows = tape ? at<__nv_bfloat16>(T, rt->tl.xrows) : at<__nv_bfloat16>(S, rt->sl.xrows);
@@ -505,30 +526,50 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
     if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
   }
   // 3. owner side: pull rows, then the two grouped GEMMs; FC2 pushes into the sources' mailboxes.
-  OwnerRows owner{tables.padded_start, tables.tile_group, tables.padded_rows, tables.expert_total};
-  {
-    StageScope scope(timing, kStageGather, stream);
-    if (int rc = gather_rows(owner, c.rank, rt->e_local, c.max_tokens, c.top_k, c.hidden, stage,
-                             at<int>(rt->arena, rt->al.meta_origin),
-                             at<float>(rt->arena, rt->al.meta_prob), xrows, origin, prob, rt->sms,
-                             stream))
-      return rc;
-  }
-  if (world > 1)
+  //    world > 1: the rows are split at an expert boundary; the second half is pulled on the side
+  //    stream while FC1/FC2 of the first half run (inbound NVLink beside compute and pushes).
+  const bool halves = world > 1;
+  auto owner_rows = [&](int half) {
+    return OwnerRows{tables.padded_start, tables.tile_group, split_range(tables.split, 2, half),
+                     tables.expert_total};
+  };
+  auto pull = [&](int half, cudaStream_t st) {
+    return gather_rows(owner_rows(half), c.rank, rt->e_local, c.max_tokens, c.top_k, c.hidden, stage,
+                       at<int>(rt->arena, rt->al.meta_origin), at<float>(rt->arena, rt->al.meta_prob),
+                       xrows, origin, prob, halves ? rt->sms * 2 : rt->sms * 8, st);
+  };
+  auto compute = [&](int half, int stage_fc1, int stage_fc2) -> int {
+    Schedule sched{tables.split, tables.tile_group, tables.padded_start, rt->e_local, rt->row_cap,
+                   tables.pair_tiles, false, half};
+    {
+      StageScope scope(timing, stage_fc1, stream);
+      if (int rc = launch_fc1(sched, xrows, static_cast<const __nv_bfloat16*>(w1), u, ab, prob,
+                              c.hidden, c.intermediate, status, rt->sms, stream))
+        return rc;
+    }
+    StageScope scope(timing, stage_fc2, stream);
+    return launch_mgrouped_nt(sched, u, static_cast<const __nv_bfloat16*>(w2), nullptr, &push,
+                              c.hidden, c.intermediate, status, rt->sms, stream);
+  };
+  if (!halves) {
+    {
+      StageScope scope(timing, kStageGather, stream);
+      if (int rc = pull(kWhole, stream)) return rc;
+    }
+    if (int rc = compute(kWhole, kStageFc1, kStageFc2)) return rc;
+  } else {
+    {
+      StageScope scope(timing, kStageGather, stream);
+      if (int rc = pull(kFirstHalf, stream)) return rc;
+    }
+    WM_CUDA(cudaEventRecord(rt->ev_first_pulled, stream));
+    WM_CUDA(cudaStreamWaitEvent(rt->side, rt->ev_first_pulled, 0));
+    if (int rc = pull(kSecondHalf, rt->side)) return rc;
+    WM_CUDA(cudaEventRecord(rt->ev_second_pulled, rt->side));
+    if (int rc = compute(kFirstHalf, kStageFc1, kStageFc2)) return rc;
+    WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_second_pulled, 0));
     if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
-  Schedule sched{tables.num_tiles, tables.tile_group, tables.padded_start, rt->e_local, rt->row_cap,
-                 tables.num_pairs, tables.pair_tiles, false};
-  {
-    StageScope scope(timing, kStageFc1, stream);
-    if (int rc = launch_fc1(sched, xrows, static_cast<const __nv_bfloat16*>(w1), u, ab, prob,
-                            c.hidden, c.intermediate, status, rt->sms, stream))
-      return rc;
-  }
-  {
-    StageScope scope(timing, kStageFc2, stream);
-    if (int rc = launch_mgrouped_nt(sched, u, static_cast<const __nv_bfloat16*>(w2), nullptr, &push,
-                                    c.hidden, c.intermediate, status, rt->sms, stream))
-      return rc;
+    if (int rc = compute(kSecondHalf, kStageFc1B, kStageFc2B)) return rc;
   }
   if (world > 1) {
     if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
@@ -570,10 +611,7 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
   const int* sorted_expert = reinterpret_cast<const int*>(tp(rt->tl.sorted_expert));
   const int* padded_start = reinterpret_cast<const int*>(tp(rt->tl.padded_start));
   const int* tile_group = reinterpret_cast<const int*>(tp(rt->tl.tile_group));
-  const int* num_tiles = reinterpret_cast<const int*>(tp(rt->tl.num_tiles));
-  const int* padded_rows = reinterpret_cast<const int*>(tp(rt->tl.padded_rows));
   const int* pair_tiles = reinterpret_cast<const int*>(tp(rt->tl.pair_tiles));
-  const int* num_pairs = reinterpret_cast<const int*>(tp(rt->tl.num_pairs));
   const int* origin = reinterpret_cast<const int*>(tp(rt->tl.origin));
   const float* prob = reinterpret_cast<const float*>(tp(rt->tl.prob));
   const auto* xrows = reinterpret_cast<const __nv_bfloat16*>(tp(rt->tl.xrows));
@@ -607,39 +645,60 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
     if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
     if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
   }
-  // 2. owner side: pull dY rows in the saved row order.
+  // 2./3. owner side: pull dY rows in the saved row order; dU = dY * W2; SwiGLU backward (U, dAB,
+  //       dprob -> sources); dX = dAB * W1 -> sources.  world > 1: two halves, the second half's
+  //       pull runs on the side stream beside the first half's compute and pushes.
   TimingSlot* timing = begin_timing(rt);
-  {
-    StageScope scope(timing, kStageGatherDy, stream);
-    if (int rc = gather_by_origin(padded_rows, origin, c.max_tokens, c.top_k, c.hidden, stage, recv,
-                                  rt->sms, stream))
-      return rc;
-  }
-  if (world > 1)
-    if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
   // Rows per local expert if routing were uniform: tokens * K * world / E.
   const bool many_rows = 1ll * tokens * c.top_k * world >= 1024ll * c.experts;
-  Schedule sched{num_tiles, tile_group, padded_start, rt->e_local, rt->row_cap, num_pairs, pair_tiles,
-                 many_rows};
-  // 3. dU = dY * W2 ; SwiGLU backward (U, dAB, dprob -> sources) ; dX = dAB * W1 -> sources.
-  {
-    StageScope scope(timing, kStageDu, stream);
-    if (int rc = launch_mgrouped_nn(sched, recv, static_cast<const __nv_bfloat16*>(w2), du, nullptr,
-                                    c.intermediate, c.hidden, status, rt->sms, stream))
-      return rc;
+  const int* split = reinterpret_cast<const int*>(tp(rt->tl.split));
+  const bool halves = world > 1;
+  auto pull = [&](int half, cudaStream_t st) {
+    return gather_by_origin(split_range(split, 2, half), origin, c.max_tokens, c.top_k, c.hidden, stage,
+                            recv, halves ? rt->sms * 2 : rt->sms * 8, st);
+  };
+  auto schedule = [&](int half) {
+    return Schedule{split, tile_group, padded_start, rt->e_local, rt->row_cap, pair_tiles, many_rows, half};
+  };
+  auto compute = [&](int half, int stage_du, int stage_sw, int stage_dx) -> int {
+    const Schedule sched = schedule(half);
+    {
+      StageScope scope(timing, stage_du, stream);
+      if (int rc = launch_mgrouped_nn(sched, recv, static_cast<const __nv_bfloat16*>(w2), du, nullptr,
+                                      c.intermediate, c.hidden, status, rt->sms, stream))
+        return rc;
+    }
+    {
+      StageScope scope(timing, stage_sw, stream);
+      if (int rc = swiglu_backward(split_range(split, 2, half), ab, du, prob, origin, c.intermediate,
+                                   c.max_tokens, c.top_k, u, dab, dgate_box, rt->sms, stream))
+        return rc;
+    }
+    StageScope scope(timing, stage_dx, stream);
+    return launch_mgrouped_nn(sched, dab, static_cast<const __nv_bfloat16*>(w1), nullptr, &push,
+                              c.hidden, 2 * c.intermediate, status, rt->sms, stream);
+  };
+  if (!halves) {
+    {
+      StageScope scope(timing, kStageGatherDy, stream);
+      if (int rc = pull(kWhole, stream)) return rc;
+    }
+    if (int rc = compute(kWhole, kStageDu, kStageSwigluBwd, kStageDx)) return rc;
+  } else {
+    {
+      StageScope scope(timing, kStageGatherDy, stream);
+      if (int rc = pull(kFirstHalf, stream)) return rc;
+    }
+    WM_CUDA(cudaEventRecord(rt->ev_first_pulled, stream));
+    WM_CUDA(cudaStreamWaitEvent(rt->side, rt->ev_first_pulled, 0));
+    if (int rc = pull(kSecondHalf, rt->side)) return rc;
+    WM_CUDA(cudaEventRecord(rt->ev_second_pulled, rt->side));
+    if (int rc = compute(kFirstHalf, kStageDu, kStageSwigluBwd, kStageDx)) return rc;
+    WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_second_pulled, 0));
+    if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
+    if (int rc = compute(kSecondHalf, kStageDuB, kStageSwigluBwdB, kStageDxB)) return rc;
   }
-  {
-    StageScope scope(timing, kStageSwigluBwd, stream);
-    if (int rc = swiglu_backward(padded_rows, ab, du, prob, origin, c.intermediate, c.max_tokens,
-                                 c.top_k, u, dab, dgate_box, rt->sms, stream))
-      return rc;
-  }
-  {
-    StageScope scope(timing, kStageDx, stream);
-    if (int rc = launch_mgrouped_nn(sched, dab, static_cast<const __nv_bfloat16*>(w1), nullptr,
-                                    &push, c.hidden, 2 * c.intermediate, status, rt->sms, stream))
-      return rc;
-  }
+  const Schedule sched = schedule(kWhole);
   if (world > 1)
     if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
   // 4. weight gradients: reductions over each expert's rows in the saved (fixed) order.

@@ -62,11 +62,11 @@ __global__ void gather_rows_kernel(OwnerRows o, int rank, int e_local, int cap, 
                                    const float* __restrict__ meta_prob,
                                    __nv_bfloat16* __restrict__ rows_out,
                                    int* __restrict__ origin_out, float* __restrict__ prob_out) {
-  const int rows = *o.padded_rows;
+  const int rows = *o.rows.end;
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const int vecs = hidden / 8;
-  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+  for (int r = *o.rows.begin + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += warps) {
     const int l = o.tile_group[r >> 7];
     const int within = r - o.padded_start[l];
     const bool live = within < o.expert_total[rank * e_local + l];
@@ -91,14 +91,14 @@ __global__ void gather_rows_kernel(OwnerRows o, int rank, int e_local, int cap, 
   }
 }
 
-__global__ void gather_by_origin_kernel(const int* padded_rows, const int* __restrict__ origin,
+__global__ void gather_by_origin_kernel(DeviceRange range, const int* __restrict__ origin,
                                         int cap, int top_k, int hidden, PeerConstRows stage,
                                         __nv_bfloat16* __restrict__ rows_out) {
-  const int rows = *padded_rows;
+  const int rows = *range.end;
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const int vecs = hidden / 8;
-  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+  for (int r = *range.begin + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += warps) {
     const int org = origin[r];
     uint4* dst = reinterpret_cast<uint4*>(rows_out + static_cast<size_t>(r) * hidden);
     if (org >= 0) {
@@ -114,20 +114,20 @@ __global__ void gather_by_origin_kernel(const int* padded_rows, const int* __res
 
 int gather_rows(const OwnerRows& o, int rank, int e_local, int cap, int top_k, int hidden,
                 const PeerConstRows& stage, const int* meta_origin, const float* meta_prob,
-                __nv_bfloat16* rows_out, int* origin_out, float* prob_out, int sms,
+                __nv_bfloat16* rows_out, int* origin_out, float* prob_out, int ctas,
                 cudaStream_t stream) {
-  gather_rows_kernel<<<sms * 8, 256, 0, stream>>>(o, rank, e_local, cap, top_k, hidden, stage,
+  gather_rows_kernel<<<ctas, 256, 0, stream>>>(o, rank, e_local, cap, top_k, hidden, stage,
                                                   meta_origin, meta_prob, rows_out, origin_out,
                                                   prob_out);
   count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
 }
-int gather_by_origin(const int* padded_rows, const int* origin, int cap, int top_k, int hidden,
-                     const PeerConstRows& stage, __nv_bfloat16* rows_out, int sms,
+int gather_by_origin(DeviceRange rows, const int* origin, int cap, int top_k, int hidden,
+                     const PeerConstRows& stage, __nv_bfloat16* rows_out, int ctas,
                      cudaStream_t stream) {
-  gather_by_origin_kernel<<<sms * 8, 256, 0, stream>>>(padded_rows, origin, cap, top_k, hidden,
-                                                       stage, rows_out);
+  gather_by_origin_kernel<<<ctas, 256, 0, stream>>>(rows, origin, cap, top_k, hidden, stage,
+                                                   rows_out);
   count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
@@ -201,17 +201,17 @@ int unpermute_dgates(const float* dgate_box, const int* sorted_slot, const int* 
 //   sig = sigmoid(a); silu = a*sig; U = bf16(silu*b*p)
 //   dA = bf16(dU*p*b*sig*(1+a*(1-sig))); dB = bf16(dU*p*silu); dprob = sum_i dU_i*silu_i*b_i
 // The row sum uses a fixed lane->column assignment and a fixed shuffle tree: deterministic.
-__global__ void swiglu_backward_kernel(const int* padded_rows, const __nv_bfloat16* __restrict__ ab,
+__global__ void swiglu_backward_kernel(DeviceRange range, const __nv_bfloat16* __restrict__ ab,
                                        const __nv_bfloat16* __restrict__ du,
                                        const float* __restrict__ prob,
                                        const int* __restrict__ origin, int inter, int cap,
                                        int top_k, __nv_bfloat16* __restrict__ u,
                                        __nv_bfloat16* __restrict__ dab, PeerFloats dgate_box) {
-  const int rows = *padded_rows;
+  const int rows = *range.end;
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const int vecs = inter / 8;
-  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+  for (int r = *range.begin + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += warps) {
     const float p = prob[r];
     const uint4* pa = reinterpret_cast<const uint4*>(ab + static_cast<size_t>(r) * 2 * inter);
     const uint4* pb = pa + vecs;
@@ -259,11 +259,11 @@ __global__ void swiglu_backward_kernel(const int* padded_rows, const __nv_bfloat
     }
   }
 }
-int swiglu_backward(const int* padded_rows, const __nv_bfloat16* ab, const __nv_bfloat16* du,
+int swiglu_backward(DeviceRange rows, const __nv_bfloat16* ab, const __nv_bfloat16* du,
                     const float* prob, const int* origin, int inter, int cap, int top_k,
                     __nv_bfloat16* u, __nv_bfloat16* dab, const PeerFloats& dgate_box, int sms,
                     cudaStream_t stream) {
-  swiglu_backward_kernel<<<sms * 8, 256, 0, stream>>>(padded_rows, ab, du, prob, origin, inter, cap,
+  swiglu_backward_kernel<<<sms * 8, 256, 0, stream>>>(rows, ab, du, prob, origin, inter, cap,
                                                       top_k, u, dab, dgate_box);
   count_launch();
   WM_CUDA(cudaGetLastError());
