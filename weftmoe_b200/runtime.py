@@ -57,6 +57,24 @@ class _Collectives:
             dist.barrier(group=self.group)
 
 
+def agree_on_preparation(collectives, error):
+    """Every rank reports the outcome of its local preparation (None or a message); if any rank
+    failed, ALL ranks raise, so no rank is left waiting in the handle exchange that follows
+    (reference: weftmoe/runtime.py:181-188).  ValueError only if every failure was a ValueError."""
+    errors = collectives.all_gather_object(error)
+    if any(errors):
+        kind = ValueError if all(e is None or e.startswith("ValueError") for e in errors) else RuntimeError
+        raise kind(f"collective preparation failed: {[e for e in errors if e]}")
+
+
+def exchange_handles(collectives, mine: bytes) -> bytes:
+    """All-gather the ranks' CUDA-IPC handles; returns them concatenated in rank order."""
+    handles = collectives.all_gather_object(bytes(mine))
+    if any(len(h) != len(mine) for h in handles):
+        raise RuntimeError("EP ranks exported IPC handles of different sizes")
+    return b"".join(handles)
+
+
 @dataclass(eq=False)
 class Tape:
     """Result of a training forward: `output` plus the cache backward consumes
@@ -101,12 +119,12 @@ class NativeRuntime:
                 _lib.check(self.lib.wm_runtime_create(ctypes.byref(config), ctypes.byref(handle)))
         except (ValueError, RuntimeError) as exc:
             error = f"{type(exc).__name__}: {exc}"
-        errors = collectives.all_gather_object(error)
-        if any(errors):
+        try:
+            agree_on_preparation(collectives, error)
+        except Exception:
             if handle:
                 self.lib.wm_runtime_destroy(handle)
-            kind = ValueError if all(e is None or e.startswith("ValueError") for e in errors) else RuntimeError
-            raise kind(f"collective preparation failed: {[e for e in errors if e]}")
+            raise
         self.handle = handle
         self.sizes = _lib.WmSizes()
         _lib.check(self.lib.wm_runtime_sizes(self.handle, ctypes.byref(self.sizes)))
@@ -114,7 +132,7 @@ class NativeRuntime:
             n = self.sizes.ipc_handle_bytes
             mine = ctypes.create_string_buffer(n)
             _lib.check(self.lib.wm_runtime_export_handle(self.handle, mine, n))
-            blob = b"".join(collectives.all_gather_object(mine.raw))
+            blob = exchange_handles(collectives, mine.raw)
             with torch.cuda.device(stream.device):
                 _lib.check(self.lib.wm_runtime_import_peers(self.handle, blob, len(blob)))
             collectives.barrier()
