@@ -144,6 +144,24 @@ WM_API int wm_route_plan(int32_t phase, int32_t world, int32_t rank, int32_t exp
                          int32_t tokens, int32_t cap, int32_t row_capacity, const int32_t* routes,
                          int32_t* count_matrix, const wm_route_out* out, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Blockwise FP8 (E4M3) quantisation.  Replaces the reference's fp8 bindings
+ * (src/python/fp8.hpp:61-174: fp8_quantize, fp8_quantize_weight, fp8_transpose_weight) with the same
+ * byte and scale results (src/cuda/fp8/quantization.cuh:35-81): power-of-two FP32 scales, zero block
+ * -> 1, non-finite block -> NaN scale.  dtype: 0 = BF16, 1 = FP32 input.  x is [batches][rows][cols].
+ * wm_fp8_quantize: block_rows 1 (1 x 128 along the last dimension) or 128 (128 x 128); transpose != 0
+ *   quantises x^T.  Output q is [batches][m][ceil128(k)] bytes (padding bytes written), scales
+ *   [batches][ceil(m / block_rows)][ceil(k / 128)] with (m, k) = transpose ? (cols, rows) : (rows, cols).
+ * wm_fp8_quantize_weight: one read of each 128 x 128 block, emits W (q, s) and W^T (qt, st) with the
+ *   same bytes and scales.  Operands must not alias; FP8 outputs must be 4-byte aligned.
+ * wm_fp8_transpose_weight: byte transpose of a 128 x 128-quantised weight, bits preserved. */
+WM_API int wm_fp8_quantize(const void* x, int32_t dtype, int32_t batches, int32_t rows, int32_t cols,
+                           int32_t block_rows, int32_t transpose, void* q, float* scales, void* stream);
+WM_API int wm_fp8_quantize_weight(const void* x, int32_t dtype, int32_t batches, int32_t rows,
+                                  int32_t cols, void* q, float* s, void* qt, float* st, void* stream);
+WM_API int wm_fp8_transpose_weight(const void* q, const float* s, int32_t batches, int32_t rows,
+                                   int32_t cols, void* qt, float* st, void* stream);
+
 /* Route planning for callers that must not allocate.  It has no counterpart in the reference.
  * Same arguments, outputs and phases as wm_route_plan, but no cudaMalloc/cudaFree: the temporaries
  * live in a fixed 1 MiB __device__ array inside the library (held by every GPU that loads it until
