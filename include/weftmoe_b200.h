@@ -162,6 +162,14 @@ WM_API int wm_fp8_quantize_weight(const void* x, int32_t dtype, int32_t batches,
 WM_API int wm_fp8_transpose_weight(const void* q, const float* s, int32_t batches, int32_t rows,
                                    int32_t cols, void* qt, float* st, void* stream);
 
+/* Diagnostic FP8 GEMM out[m,n] (+)= A[m,k] * B[n,k]^T on the block-scaled tensor-core path
+ * (reference: fp8_gemm, weftmoe/fp8.py:129-153).  aq/bq: E4M3 bytes with rows padded to ceil128(k);
+ * as/bs: FP32 power-of-two scales per [block_rows x 128] block; out FP32 or BF16; accumulate needs an
+ * existing FP32 output.  Synchronises `stream`; allocates temporary device memory. */
+WM_API int wm_fp8_gemm(const void* aq, const float* as, const void* bq, const float* bs, void* out,
+                       int32_t m, int32_t n, int32_t k, int32_t a_block_rows, int32_t b_block_rows,
+                       int32_t out_is_f32, int32_t accumulate, void* stream);
+
 /* Route planning for callers that must not allocate.  It has no counterpart in the reference.
  * Same arguments, outputs and phases as wm_route_plan, but no cudaMalloc/cudaFree: the temporaries
  * live in a fixed 1 MiB __device__ array inside the library (held by every GPU that loads it until

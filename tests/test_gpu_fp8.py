@@ -107,3 +107,34 @@ def test_native_validation_and_prepared_weights():
         prepared.wait()
     with pytest.raises(ValueError):
         prepare_fp8_weights(w1[:, :, :100].contiguous(), w2)
+
+
+def global_diff(actual, expected):
+    """The reference's FP8 acceptance metric (benchmarks/fp8_validation.py:23-35)."""
+    a, b = actual.double(), expected.double()
+    den = (a.square() + b.square()).sum().item()
+    return ((a - b).square().sum().item() / den) if den else 0.0
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (65, 137, 259), (128, 256, 4096), (300, 640, 1024),
+                                   (0, 64, 128), (64, 0, 128), (3, 9, 0)])
+@pytest.mark.parametrize("b_block_rows", [1, 128])
+def test_gemm(m, n, k, b_block_rows):
+    """tests/test_fp8.py:146-168 of the reference: different scales per K block, M/N/K tails,
+    diff < 1e-6 against the dequantised FP64 product and < 5e-3 against the original operands."""
+    from weftmoe_b200.fp8 import fp8_gemm
+    torch.manual_seed(1234)
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    if k:
+        a[:, :min(128, k)] *= 4
+        b[:, :min(128, k)] *= 0.0625
+    aq, bq = quantize_fp8(a), quantize_fp8(b, block_rows=b_block_rows)
+    expected = aq.dequantize().double() @ bq.dequantize().double().T
+    original = a.double() @ b.double().T
+    actual = fp8_gemm(aq, bq, dtype=torch.float32)
+    assert global_diff(actual, expected) < 1e-6 and global_diff(actual, original) < 5e-3
+    out = torch.full((m, n), 0.5, device="cuda", dtype=torch.float32)
+    fp8_gemm(aq, bq, dtype=torch.float32, out=out, accumulate=True)
+    assert global_diff(out, expected + 0.5) < 1e-6
+    assert torch.equal(fp8_gemm(aq, bq), actual.bfloat16())

@@ -216,6 +216,65 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Block-scaled UMMA (one CTA): D (+)= (A * SFA) * (B * SFB) with the scale factors read from TMEM.
+// kind::mxf8f6f4: 8-bit (or 6/4-bit padded) operands, one UE8M0 scale per 32 K elements.
+__device__ __forceinline__ void umma_mxf8_block_scaled(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                                       uint32_t idesc, uint32_t accumulate,
+                                                       uint32_t tmem_sfa, uint32_t tmem_sfb) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+// kind::mxf4nvf4 with scale_vec::4X: packed E2M1 operands, one UE4M3 scale per 16 K elements (NVFP4).
+__device__ __forceinline__ void umma_nvf4_block_scaled(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                                       uint32_t idesc, uint32_t accumulate,
+                                                       uint32_t tmem_sfa, uint32_t tmem_sfb) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+// Shared memory -> TMEM copy of one scale-factor chunk: 32 lanes x 16 bytes, replicated to the four
+// lane quarters.  Word (l*4 + j) of the 512-byte chunk lands in lane l, column j.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+// Descriptor of an unswizzled K-major chunk of 16-byte rows (8-row groups 128 bytes apart).
+__device__ __forceinline__ uint64_t umma_desc_noswizzle(uint32_t saddr, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+// Instruction descriptor of the block-scaled kinds:
+//   bits 4-5 SFB byte id; bits 7-9 A format; bits 10-12 B format; bit 15/16 A/B major;
+//   bits 17-22 N >> 3; bit 23 scale format (0 = UE4M3, 1 = UE8M0); bits 24-28 M >> 4; bits 29-30 SFA byte id.
+__host__ __device__ constexpr uint32_t umma_idesc_block_scaled(uint32_t ab_format, uint32_t scale_is_e8m0,
+                                                               uint32_t m, uint32_t n, uint32_t sfa_id,
+                                                               uint32_t sfb_id) {
+  return (sfb_id << 4) | (ab_format << 7) | (ab_format << 10) | ((n >> 3) << 17) | (scale_is_e8m0 << 23) |
+         ((m >> 4) << 24) | (sfa_id << 29);
+}
+// 1-D bulk copy global -> shared (16-byte aligned, size a multiple of 16), credited to `bar`.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes,
+                                             uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
 // Arrive on `bar` when every tcgen05 op issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(

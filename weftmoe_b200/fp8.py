@@ -127,6 +127,32 @@ def transpose_fp8_weight(weight: FP8Tensor) -> FP8Tensor:
     return result
 
 
+def fp8_gemm(a: FP8Tensor, b: FP8Tensor, *, dtype=torch.bfloat16, out: torch.Tensor | None = None,
+             accumulate: bool = False) -> torch.Tensor:
+    """Reference/diagnostic A @ B.T on the block-scaled FP8 tensor-core path (FP32 accumulation).
+
+    This standalone kernel is a diagnostic; the layer uses the grouped kernels."""
+    if (len(a.shape) != 2 or len(b.shape) != 2 or a.shape[1] != b.shape[1]
+            or a.data.device != b.data.device):
+        raise ValueError("FP8 GEMM requires [M,K], [N,K] on the same device")
+    if dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("FP8 GEMM output dtype must be BF16 or FP32")
+    if accumulate and (out is None or out.dtype != torch.float32):
+        raise ValueError("FP8 accumulation requires an existing FP32 output")
+    with torch.cuda.device(a.data.device):
+        if out is None:
+            out = torch.empty((a.shape[0], b.shape[0]), dtype=dtype, device=a.data.device)
+        elif (out.dtype != dtype or out.device != a.data.device or out.shape != (a.shape[0], b.shape[0])
+              or not out.is_contiguous()):
+            raise ValueError("FP8 output shape, dtype, device or layout mismatch")
+        stream = torch.cuda.current_stream()
+        _lib.check(_lib.load().wm_fp8_gemm(
+            _lib.ptr(a.data), _lib.ptr(a.scales), _lib.ptr(b.data), _lib.ptr(b.scales), _lib.ptr(out),
+            a.shape[0], b.shape[0], a.shape[1], a.block_rows, b.block_rows, int(dtype == torch.float32),
+            int(accumulate), stream.cuda_stream))
+    return out
+
+
 @dataclass(frozen=True)
 class PreparedFP8Weights:
     """One immutable weight version, retaining both FWD and Dgrad layouts.
