@@ -170,6 +170,20 @@ WM_API int wm_fp8_gemm(const void* aq, const float* as, const void* bq, const fl
                        int32_t m, int32_t n, int32_t k, int32_t a_block_rows, int32_t b_block_rows,
                        int32_t out_is_f32, int32_t accumulate, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * NVFP4 (E2M1 with an E4M3 scale per 16 elements and an FP32 layer scale).
+ * wm_nvfp4_quantize: x BF16 [rows][cols] -> data [rows][cols/2] bytes (even element in the low nibble)
+ *   and scale bytes, row-major [rows][cols/16] (chunked = 0; reference activation layout,
+ *   weftmoe/nvfp4.py:61-63) or in 512-byte tensor-core chunks (chunked = 1; reference weight/backward
+ *   layout, weftmoe/nvfp4.py:58-60, src/cuda/blackwell/nvfp4_quantize.cuh:48-51).  Same results as the
+ *   reference's `_encode_row` (weftmoe/nvfp4.py:14-31) / `quantize_blocks` (nvfp4_quantize.cuh:53-125).
+ * wm_nvfp4_gemm: diagnostic out[m,n] = alpha * A[m,k] * B[n,k]^T on the block-scaled tensor-core path
+ *   with row-major scale bytes (reference oracle: tests/torchrun_sm100_nvfp4.py:30-33). */
+WM_API int wm_nvfp4_quantize(const void* x, int32_t rows, int32_t cols, float layer_scale, void* data,
+                             void* scales, int32_t chunked, void* stream);
+WM_API int wm_nvfp4_gemm(const void* a, const void* a_sf, const void* b, const void* b_sf, void* out,
+                         int32_t m, int32_t n, int32_t k, float alpha, int32_t out_is_f32, void* stream);
+
 /* Route planning for callers that must not allocate.  It has no counterpart in the reference.
  * Same arguments, outputs and phases as wm_route_plan, but no cudaMalloc/cudaFree: the temporaries
  * live in a fixed 1 MiB __device__ array inside the library (held by every GPU that loads it until

@@ -57,6 +57,8 @@ SIGNATURES = {
     "wm_fp8_quantize_weight": (c_int, [c_void_p] + [c_int32] * 4 + [c_void_p] * 5),
     "wm_fp8_transpose_weight": (c_int, [c_void_p, c_void_p] + [c_int32] * 3 + [c_void_p] * 3),
     "wm_fp8_gemm": (c_int, [c_void_p] * 5 + [c_int32] * 7 + [c_void_p]),
+    "wm_nvfp4_quantize": (c_int, [c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p, c_int32, c_void_p]),
+    "wm_nvfp4_gemm": (c_int, [c_void_p] * 5 + [c_int32] * 3 + [c_float, c_int32, c_void_p]),
     "wm_route_plan_noalloc": (c_int, [c_int32] * 8 + [c_void_p, c_void_p, POINTER(WmRouteOut), c_void_p]),
     "wm_debug_force_gemm_pairs": (None, [c_int]),
     "wm_debug_grouped_gemm": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -5,8 +5,8 @@
 #include <vector>
 
 #include "../../include/weftmoe_b200.h"
-#include "gemm_bs.cuh"
 #include "kernels.h"
+#include "gemm_bs.cuh"
 
 using namespace wm;
 
@@ -46,22 +46,6 @@ int pack_fp8_scales(const float* scales, int rows, int kblocks, int block_rows, 
   const int grid = static_cast<int>((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
   pack_fp8_scales_kernel<<<grid, 256, 0, stream>>>(scales, rows, kblocks, block_rows,
                                                    static_cast<uint32_t*>(out), tiles);
-  WM_CUDA(cudaGetLastError());
-  count_launch();
-  return 0;
-}
-
-template <int KIND, class Epi>
-int launch_bs(const CUtensorMap& ta, const CUtensorMap& tb, const BsArgs& args, const Epi& epi, int sms,
-              cudaStream_t stream) {
-  auto kernel = gemm_bs_kernel<KIND, Epi>;
-  constexpr int smem = BsConfig<KIND>::kTotal;
-  static bool configured = false;
-  if (!configured) {
-    WM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
-  }
-  kernel<<<sms, kGemmThreads, smem, stream>>>(ta, tb, args, epi);
   WM_CUDA(cudaGetLastError());
   count_launch();
   return 0;
@@ -126,8 +110,8 @@ extern "C" int wm_fp8_gemm(const void* aq, const float* as, const void* bq, cons
     args.base.k_total = kp;
     args.base.b_group_rows = n;
     args.base.status = sched + 7;
-    args.sfa = sfa;
-    args.sfb = sfb;
+    args.sfa = SfLayout{sfa, 0, 512ll * kblocks, 512, 512};
+    args.sfb = SfLayout{sfb, 0, 512ll * kblocks, 512, 512};
     EpilogueBounded epi{out, m, n, n, out_is_f32, accumulate, 1.0f};
     rc = launch_bs<kKindFp8>(ta, tb, args, epi, sms, stream);
   }

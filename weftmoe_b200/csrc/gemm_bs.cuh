@@ -40,10 +40,17 @@ struct BsConfig {
   static constexpr uint32_t kTmemCols = 512;
 };
 
+// Where the 512-byte scale-factor chunks of an operand live: chunk (group, tile, k stage, c) is at
+// base + group*group_stride + tile*tile_stride + kstage*kstage_stride + c*chunk_stride (bytes).
+struct SfLayout {
+  const uint8_t* base;
+  long long group_stride, tile_stride, kstage_stride, chunk_stride;
+};
+
 struct BsArgs {
-  GemmArgs base;         // M-grouped schedule; k_total in ELEMENTS; b_group_rows = N_total
-  const uint8_t* sfa;    // [m_tiles][k_stages][chunks][512]
-  const uint8_t* sfb;    // [groups][N_total/128][k_stages][chunks][512]
+  GemmArgs base;   // M-grouped schedule; k_total in ELEMENTS; b_group_rows = N_total
+  SfLayout sfa;    // tile = 128-row tile of A (group_stride unused)
+  SfLayout sfb;    // group = expert, tile = 128-row tile of that expert's B
 };
 
 template <int KIND, class Epilogue>
@@ -92,7 +99,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const int first_tile = __ldg(args.tile_begin) * args.n_tiles;
   const int total_tiles = __ldg(args.tile_end) * args.n_tiles;
-  const int k_stages = args.k_total / C::kElemsPerStage;
+  const int k_stages = (args.k_total + C::kElemsPerStage - 1) / C::kElemsPerStage;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -101,8 +108,8 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       bool ok = true;
       for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const TileCoord t = decode_tile<false>(args, tile);
-        const uint8_t* sfa = bs.sfa + static_cast<size_t>(t.m_tile) * k_stages * C::kSfBytes;
-        const uint8_t* sfb = bs.sfb + (static_cast<size_t>(t.group) * args.n_tiles + t.n_tile) * k_stages * C::kSfBytes;
+        const uint8_t* sfa = bs.sfa.base + t.m_tile * bs.sfa.tile_stride;
+        const uint8_t* sfb = bs.sfb.base + t.group * bs.sfb.group_stride + t.n_tile * bs.sfb.tile_stride;
         for (int kb = 0; kb < k_stages; ++kb) {
           ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, args.status, kStatusTimeoutSmemEmpty);
           if (!ok) break;
@@ -114,8 +121,13 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           tma_load_2d(sa, &tmap_a, full_bar + stage, kb * C::kRowBytes, t.m_tile * kBlockM);
           tma_load_2d(sb, &tmap_b, full_bar + stage, kb * C::kRowBytes,
                       t.group * args.b_group_rows + t.n_tile * C::kBlockN);
-          bulk_load_1d(ssfa, sfa + static_cast<size_t>(kb) * C::kSfBytes, C::kSfBytes, full_bar + stage);
-          bulk_load_1d(ssfb, sfb + static_cast<size_t>(kb) * C::kSfBytes, C::kSfBytes, full_bar + stage);
+#pragma unroll
+          for (int c = 0; c < C::kSfChunks; ++c) {
+            bulk_load_1d(ssfa + c * 512, sfa + kb * bs.sfa.kstage_stride + c * bs.sfa.chunk_stride, 512,
+                         full_bar + stage);
+            bulk_load_1d(ssfb + c * 512, sfb + kb * bs.sfb.kstage_stride + c * bs.sfb.chunk_stride, 512,
+                         full_bar + stage);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -236,5 +248,25 @@ struct EpilogueBounded {
     }
   }
 };
+
+// Host launcher (needs kernels.h for WM_CUDA / count_launch; include it before this header).
+#ifdef WM_CUDA
+template <int KIND, class Epi>
+int launch_bs(const CUtensorMap& ta, const CUtensorMap& tb, const BsArgs& args, const Epi& epi, int sms,
+              cudaStream_t stream) {
+  auto kernel = gemm_bs_kernel<KIND, Epi>;
+  constexpr int smem = BsConfig<KIND>::kTotal;
+  static bool configured = false;
+  if (!configured) {
+    WM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  kernel<<<sms, kGemmThreads, smem, stream>>>(ta, tb, args, epi);
+  WM_CUDA(cudaGetLastError());
+  count_launch();
+  return 0;
+}
+
+#endif
 
 }  // namespace wm
