@@ -60,7 +60,7 @@ typedef struct wm_config {
   int32_t max_tokens;   /* token capacity of this rank                                          */
   int32_t max_rows;     /* routed rows this rank may receive as an expert owner                 */
   int32_t training;     /* non-zero: backward buffers are allocated                             */
-  int32_t reserved;
+  int32_t reserved;     /* precision: 0 BF16, 1 blockwise FP8 (E4M3), 2 NVFP4 (intermediate % 256 == 0)  */
 } wm_config;
 
 typedef struct wm_sizes {
@@ -98,6 +98,29 @@ WM_API int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, cons
 WM_API int wm_backward(wm_runtime* rt, const void* tape, const void* dy, const void* w1,
                        const void* w2, int32_t tokens, void* dx, float* dgates, void* dw1, void* dw2,
                        void* stream);
+
+/* Quantised inference forward (reference: inference_fp8 / forward_fp8 without a tape,
+ * weftmoe/runtime.py:303-352,387-415; NVFP4 inference, weftmoe/nvfp4.py:252-278).  The runtime must have
+ * been created with precision 1 or 2.  x stays BF16 and is quantised online at the source rank
+ * (1 x 128 power-of-two FP32 scales, or block-16 E4M3 scales with layer scale x_scale); weights are
+ * pre-quantised and their scale factors pre-packed in 512-byte tensor-core chunks:
+ *   FP8   w1 [E_local][2I][H] E4M3, w1_sf = wm_fp8_pack_weight_scales(scales [E_local*2I/128][H/128]);
+ *   NVFP4 w1 [E_local][2I][H/2],    w1_sf = chunked scales of wm_nvfp4_quantize over [E_local*2I, H];
+ * w2 likewise over [E_local][H][I].  NVFP4: accumulators are scaled by x_scale*w1_scale and rounded to
+ * BF16, u = silu(a)*b*prob is quantised with u_scale, FC2 is scaled by u_scale*w2_scale. */
+typedef struct wm_quant_weights {
+  const void* w1;
+  const void* w1_sf;
+  const void* w2;
+  const void* w2_sf;
+  float x_scale, w1_scale, u_scale, w2_scale; /* NVFP4 layer scales; ignored for FP8 */
+} wm_quant_weights;
+WM_API int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t* routes, const float* gates,
+                                const wm_quant_weights* weights, int32_t tokens, void* y, void* stream);
+/* scales [rows/128][kblocks] FP32 (128 x 128 blocks of a [rows][K] weight, experts stacked along rows)
+ * -> UE8M0 chunks [rows/128][kblocks][512 bytes]. */
+WM_API int wm_fp8_pack_weight_scales(const float* scales, int32_t rows, int32_t kblocks, void* out,
+                                     void* stream);
 
 /* Reads (and clears) the device status word; synchronises `stream`.  *code receives a WM_ERR_* value
  * (reference: TransportDeviceStatus surfaced through profile_inference, src/python/runtime.cpp:295-331). */

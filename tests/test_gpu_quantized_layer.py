@@ -1,0 +1,97 @@
+"""GPU: quantised inference forward (NVFP4 and blockwise FP8) through the Tensor API against the CPU
+oracles that restate the reference's own checkers (tests/torchrun_sm100_nvfp4.py:36-47, rel-L2 < 0.005;
+FP8 acceptance diff < 5e-3 against the BF16 result, benchmarks/fp8_validation.py:4-35)."""
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+from tests.gpu_util import rel_l2
+from weftmoe_b200 import SingleRankGroup, TensorRuntime
+from weftmoe_b200.fp8 import prepare_fp8_weights
+from weftmoe_b200.nvfp4 import NVFP4Scales, prepare_nvfp4_weights
+
+pytestmark = pytest.mark.gpu
+
+
+def inputs(cfg, seed, x_std, w_std):
+    d = O.make_inputs(cfg, seed=seed, x_std=x_std, w_std=w_std, bias_std=0.5)
+    d["routes"][0] = 3
+    d["routes"][1] = -1
+    return d, {k: v.cuda() for k, v in d.items()}
+
+
+def runtime(cfg, precision, **kw):
+    return TensorRuntime(group=SingleRankGroup(), experts=cfg["experts"], top_k=cfg["top_k"], hidden=cfg["hidden"],
+                         intermediate=cfg["intermediate"], max_tokens=cfg["tokens"],
+                         max_rows=cfg["tokens"] * cfg["top_k"], training=False, precision=precision, **kw)
+
+
+def global_diff(actual, expected):
+    a, b = actual.double().cpu(), expected.double().cpu()
+    return ((a - b).square().sum() / (a.square() + b.square()).sum()).item()
+
+
+@pytest.mark.parametrize("cfg", [dict(experts=16, top_k=4, hidden=512, intermediate=256, tokens=200),
+                                 dict(experts=8, top_k=2, hidden=1024, intermediate=512, tokens=77)])
+def test_nvfp4_forward_against_reference_formula(cfg):
+    d, g = inputs(cfg, 7, 0.16, 0.023)   # the reference test's input scales
+    scales = NVFP4Scales()
+    rt = runtime(cfg, "nvfp4")
+    weights = prepare_nvfp4_weights(g["w1"], g["w2"], weight_scales=(scales.w1, scales.w2))
+    y = rt.inference_nvfp4(0, g["x"], g["routes"], g["gates"], weights)
+    assert torch.equal(rt.inference_nvfp4(0, g["x"], g["routes"], g["gates"], weights).view(torch.int16), y.view(torch.int16))
+    ref = O.quantized_layer(d["x"], d["routes"], d["gates"], d["w1"], d["w2"], kind="nvfp4", scales=tuple(scales[:4]))
+    assert rel_l2(y, ref) < 0.005, rel_l2(y, ref)          # the reference's tolerance
+    assert rel_l2(y, ref) < 2e-3, rel_l2(y, ref)           # same roundings: only accumulation order differs
+    assert (y[1] == 0).all()
+    # against the unquantised layer NVFP4 is a 4-bit format: only a sanity bound
+    bf16 = O.moe_layer(d["x"], d["routes"], d["gates"], d["w1"], d["w2"])[0]
+    assert rel_l2(y, bf16) < 0.25
+    rt.close()
+
+
+def test_nvfp4_calibrated_scales_for_unit_variance_inputs():
+    """BASELINE config 3 draws X ~ N(0,1): the default layer scales were chosen for x0.16 data, so the
+    scales are calibrated (max |x| / (6 * 448) rule) and the same scales go to oracle and kernel."""
+    cfg = dict(experts=8, top_k=2, hidden=512, intermediate=256, tokens=64)
+    d, g = inputs(cfg, 11, 1.0, 0.02)
+    scales = (1 / 4, 1 / 64, 1 / 64, 1 / 64)
+    rt = runtime(cfg, "nvfp4", nvfp4_scales=(*scales, 1 / 32, 1 / 512))
+    weights = prepare_nvfp4_weights(g["w1"], g["w2"], weight_scales=(scales[1], scales[3]))
+    y = rt.inference_nvfp4(0, g["x"], g["routes"], g["gates"], weights)
+    ref = O.quantized_layer(d["x"], d["routes"], d["gates"], d["w1"], d["w2"], kind="nvfp4", scales=scales)
+    assert rel_l2(y, ref) < 0.005
+    rt.close()
+
+
+@pytest.mark.parametrize("cfg", [dict(experts=16, top_k=4, hidden=512, intermediate=256, tokens=200),
+                                 dict(experts=8, top_k=2, hidden=768, intermediate=384, tokens=130)])
+def test_fp8_forward_against_oracle_and_bf16(cfg):
+    d, g = inputs(cfg, 5, 1.0, 0.02)
+    rt = runtime(cfg, "fp8")
+    weights = prepare_fp8_weights(g["w1"], g["w2"], training=False)
+    y = rt.inference_fp8(0, g["x"], g["routes"], g["gates"], weights)
+    tape = rt.forward_fp8(g["x"], g["routes"], g["gates"], weights, retain_backward_state=False)
+    assert torch.equal(tape.output.view(torch.int16), y.view(torch.int16))   # graph path == eager path bits
+    ref = O.quantized_layer(d["x"], d["routes"], d["gates"], d["w1"], d["w2"], kind="fp8")
+    assert rel_l2(y, ref) < 2e-3, rel_l2(y, ref)
+    bf16 = O.moe_layer(d["x"], d["routes"], d["gates"], d["w1"], d["w2"])[0]
+    assert global_diff(y, bf16) < 5e-3, global_diff(y, bf16)                  # the reference's FP8 acceptance
+    rt.close()
+
+
+def test_quantised_runtime_contract_errors():
+    cfg = dict(experts=8, top_k=2, hidden=512, intermediate=256, tokens=16)
+    d, g = inputs(cfg, 3, 1.0, 0.02)
+    with pytest.raises(ValueError):
+        TensorRuntime(group=SingleRankGroup(), experts=8, top_k=2, hidden=512, intermediate=384, max_tokens=4,
+                      max_rows=8, training=False, precision="nvfp4")            # I % 256
+    with pytest.raises(ValueError):
+        TensorRuntime(group=SingleRankGroup(), experts=8, top_k=2, hidden=512, intermediate=256, max_tokens=4,
+                      max_rows=8, training=False, nvfp4_scales=(1, 1, 1, 1, 1, 1))  # scales without nvfp4
+    rt = runtime(cfg, "fp8")
+    with pytest.raises(ValueError):
+        rt.inference_eager(g["x"], g["routes"], g["gates"], g["w1"], g["w2"])   # BF16 call on an FP8 runtime
+    with pytest.raises(TypeError):
+        rt.inference_fp8(0, g["x"], g["routes"], g["gates"], (g["w1"], g["w2"]))
+    rt.close()

@@ -18,12 +18,17 @@ WM_OK, WM_ERR_INVALID, WM_ERR_CUDA, WM_ERR_TIMEOUT, WM_ERR_ROUTE, WM_ERR_CAPACIT
 class WmConfig(Structure):
     _fields_ = [(name, c_int32) for name in (
         "rank", "world", "experts", "top_k", "hidden", "intermediate", "max_tokens", "max_rows",
-        "training", "reserved")]
+        "training", "reserved")]  # reserved = precision: 0 BF16, 1 FP8, 2 NVFP4
 
 
 class WmSizes(Structure):
     _fields_ = [("arena_bytes", c_int64), ("scratch_bytes", c_int64), ("tape_bytes", c_int64),
                 ("row_capacity", c_int32), ("ipc_handle_bytes", c_int32)]
+
+
+class WmQuantWeights(Structure):
+    _fields_ = [("w1", c_void_p), ("w1_sf", c_void_p), ("w2", c_void_p), ("w2_sf", c_void_p),
+                ("x_scale", c_float), ("w1_scale", c_float), ("u_scale", c_float), ("w2_scale", c_float)]
 
 
 class WmRouteOut(Structure):
@@ -46,6 +51,9 @@ SIGNATURES = {
                            c_void_p, c_void_p, c_void_p]),
     "wm_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p,
                             c_void_p, c_void_p, c_void_p, c_void_p]),
+    "wm_forward_quantized": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(WmQuantWeights), c_int32,
+                                     c_void_p, c_void_p]),
+    "wm_fp8_pack_weight_scales": (c_int, [c_void_p, c_int32, c_int32, c_void_p, c_void_p]),
     "wm_status_poll": (c_int, [c_void_p, POINTER(c_int32), c_void_p]),
     "wm_launch_count": (ctypes.c_longlong, []),
     "wm_stage_count": (c_int, []),

@@ -184,4 +184,75 @@ struct EpiloguePush {
   }
 };
 
+// ---------------------------------------------------------------- scaled variants (quantised paths)
+// Same stores as EpilogueStore / EpiloguePush with the FP32 accumulator multiplied by a constant first
+// (the product of the NVFP4 layer scales; 1 for blockwise FP8, whose scales live in the MMA).
+__device__ __forceinline__ void load_pack32_scaled(uint32_t taddr, float alpha, uint32_t (&w)[16]) {
+  uint32_t v[32];
+  tmem_ld_32x32(taddr, v);
+  tmem_ld_wait();
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+    w[j] = pack_bf16x2(__uint_as_float(v[2 * j]) * alpha, __uint_as_float(v[2 * j + 1]) * alpha);
+}
+
+template <int BLOCK_N>
+struct EpilogueStoreScaled {
+  __nv_bfloat16* out;
+  int ld;
+  float alpha;
+
+  __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane, bool,
+                                             uint8_t* stage) const {
+    static_assert(BLOCK_N == 128, "the block-scaled kernel uses 128-wide tiles");
+    const long long row0 = static_cast<long long>(t.m_tile) * kBlockM + q * 32;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t w[16];
+      load_pack32_scaled(taddr + c * 32, alpha, w);
+      stage_put32(stage, lane, c, w);
+    }
+    __syncwarp();
+    __nv_bfloat16* block = out + row0 * ld + t.n_tile * BLOCK_N;
+    const int ldl = ld;
+    stage_flush(stage, lane, [block, ldl](int r) { return block + static_cast<long long>(r) * ldl; });
+    __syncwarp();
+  }
+};
+
+template <int BLOCK_N>
+struct EpiloguePushScaled {
+  EpiloguePush<BLOCK_N> push;
+  float alpha;
+
+  __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane, bool,
+                                             uint8_t* stage) const {
+    static_assert(BLOCK_N == 128, "the block-scaled kernel uses 128-wide tiles");
+    const long long row = static_cast<long long>(t.m_tile) * kBlockM + q * 32 + lane;
+    const int org = push.origin[row];
+    unsigned long long my_dst = 0;
+    if (org >= 0) {
+      const int per_rank = push.cap * push.top_k;
+      const int src = org / per_rank;
+      const int rem = org - src * per_rank;
+      const int token = rem / push.top_k, slot = rem - token * push.top_k;
+      my_dst = reinterpret_cast<unsigned long long>(
+          push.select_mailbox(src) + (static_cast<long long>(slot) * push.cap + token) * push.ld +
+          t.n_tile * BLOCK_N);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t w[16];
+      load_pack32_scaled(taddr + c * 32, alpha, w);
+      stage_put32(stage, lane, c, w);
+    }
+    __syncwarp();
+    stage_flush(stage, lane, [my_dst](int r) {
+      const unsigned long long d = __shfl_sync(0xffffffffu, my_dst, r);
+      return d ? reinterpret_cast<__nv_bfloat16*>(d) : nullptr;
+    });
+    __syncwarp();
+  }
+};
+
 }  // namespace wm

@@ -230,6 +230,22 @@ int check_common(const char* what, const void* x, int dtype, int batches, int ro
 
 }  // namespace
 
+namespace wm {
+// BF16 [rows][cols] (cols % 128 == 0, 16-byte aligned) -> E4M3 bytes + FP32 scales [rows][cols/128].
+int fp8_quantize_rows(const void* x, long long rows, int cols, void* q, float* scales, int sms,
+                      cudaStream_t stream) {
+  const long long blocks = rows * (cols / 128);
+  if (blocks == 0) return 0;
+  const long long want = (blocks * 16 + 255) / 256;
+  const int grid = static_cast<int>(want < sms * 16LL ? want : sms * 16LL);
+  quantize_rows_bf16_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint4*>(x), blocks, cols / 128,
+                                                      static_cast<uint2*>(q), scales);
+  WM_CUDA(cudaGetLastError());
+  count_launch();
+  return 0;
+}
+}  // namespace wm
+
 extern "C" int wm_fp8_quantize(const void* x, int32_t dtype, int32_t batches, int32_t rows,
                                int32_t cols, int32_t block_rows, int32_t transpose, void* q,
                                float* scales, void* stream_) {

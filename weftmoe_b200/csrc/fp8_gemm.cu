@@ -38,6 +38,7 @@ __global__ void pack_fp8_scales_kernel(const float* __restrict__ scales, int row
 
 namespace wm {
 
+// (declared in quant_path.h)
 int pack_fp8_scales(const float* scales, int rows, int kblocks, int block_rows, void* out,
                     cudaStream_t stream) {
   const int tiles = (rows + 127) / 128;

@@ -16,10 +16,9 @@
 // thread copies the chunks into TMEM and issues four MMAs per stage.  Accumulators: 2 x 128 columns.
 #pragma once
 #include "gemm.cuh"
+#include "quant_path.h"
 
 namespace wm {
-
-enum BlockScaledKind { kKindFp8 = 0, kKindNvfp4 = 1 };
 
 template <int KIND>
 struct BsConfig {
@@ -38,13 +37,6 @@ struct BsConfig {
   static constexpr uint32_t kTmemSfa = 2 * kBlockN;              // first scale-factor column
   static constexpr uint32_t kTmemSfb = kTmemSfa + 4 * kSfChunks;
   static constexpr uint32_t kTmemCols = 512;
-};
-
-// Where the 512-byte scale-factor chunks of an operand live: chunk (group, tile, k stage, c) is at
-// base + group*group_stride + tile*tile_stride + kstage*kstage_stride + c*chunk_stride (bytes).
-struct SfLayout {
-  const uint8_t* base;
-  long long group_stride, tile_stride, kstage_stride, chunk_stride;
 };
 
 struct BsArgs {

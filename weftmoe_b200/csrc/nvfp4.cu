@@ -97,6 +97,26 @@ __global__ void nvfp4_pack_scales_kernel(const unsigned char* __restrict__ sf, i
 
 }  // namespace
 
+namespace wm {
+int nvfp4_quantize_rows(const void* x, int rows, int cols, float layer_scale, void* data, void* scales,
+                        int chunked, cudaStream_t stream) {
+  const long long total = static_cast<long long>(rows) * (cols / 16);
+  if (total == 0) return 0;
+  if (chunked) {
+    const size_t bytes = static_cast<size_t>((rows + 127) / 128) * (cols / 64) * 512;
+    WM_CUDA(cudaMemsetAsync(scales, 0, bytes, stream));
+  }
+  const int grid = static_cast<int>((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
+  nvfp4_quantize_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, cols,
+                                                  static_cast<float>(6.0 * static_cast<double>(layer_scale)),
+                                                  layer_scale, static_cast<uint2*>(data),
+                                                  static_cast<unsigned char*>(scales), chunked);
+  WM_CUDA(cudaGetLastError());
+  count_launch();
+  return 0;
+}
+}  // namespace wm
+
 extern "C" int wm_nvfp4_quantize(const void* x, int32_t rows, int32_t cols, float layer_scale, void* data,
                                  void* scales, int32_t chunked, void* stream_) {
   if (rows < 0 || cols < 0 || cols % 16 || (chunked && cols % 64) || !(layer_scale > 0.0f) ||
@@ -110,21 +130,8 @@ extern "C" int wm_nvfp4_quantize(const void* x, int32_t rows, int32_t cols, floa
     set_error("wm_nvfp4_quantize: null or misaligned tensor");
     return WM_ERR_INVALID;
   }
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  const long long total = static_cast<long long>(rows) * (cols / 16);
-  if (chunked) {
-    // rows of the last 128-row tile that do not exist must read as zero scales
-    const size_t bytes = static_cast<size_t>((rows + 127) / 128) * (cols / 64) * 512;
-    WM_CUDA(cudaMemsetAsync(scales, 0, bytes, stream));
-  }
-  const int grid = static_cast<int>((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
-  nvfp4_quantize_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, cols,
-                                                  static_cast<float>(6.0 * static_cast<double>(layer_scale)),
-                                                  layer_scale, static_cast<uint2*>(data),
-                                                  static_cast<unsigned char*>(scales), chunked);
-  WM_CUDA(cudaGetLastError());
-  count_launch();
-  return WM_OK;
+  return nvfp4_quantize_rows(x, rows, cols, layer_scale, data, scales, chunked,
+                             static_cast<cudaStream_t>(stream_));
 }
 
 // Diagnostic: out[m,n] = alpha * (A[m,k] * B[n,k]^T) with NVFP4 operands; scales row-major bytes.

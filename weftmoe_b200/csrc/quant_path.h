@@ -1,0 +1,43 @@
+// Host interface of the quantised forward path (quant_path.cu) and the types it shares with the
+// block-scaled GEMM kernel (gemm_bs.cuh).
+#pragma once
+#include <stdint.h>
+
+#include "kernels.h"
+#include "route.h"
+
+namespace wm {
+
+enum BlockScaledKind { kKindFp8 = 0, kKindNvfp4 = 1 };
+
+// Where the 512-byte scale-factor chunks of an operand live: chunk (group, tile, k stage, c) is at
+// base + group*group_stride + tile*tile_stride + kstage*kstage_stride + c*chunk_stride (bytes).
+struct SfLayout {
+  const uint8_t* base;
+  long long group_stride, tile_stride, kstage_stride, chunk_stride;
+};
+
+struct PeerBytes { const uint8_t* p[kMaxWorld]; };
+
+// fp8.cu / nvfp4.cu / fp8_gemm.cu
+int fp8_quantize_rows(const void* x, long long rows, int cols, void* q, float* scales, int sms,
+                      cudaStream_t stream);
+int nvfp4_quantize_rows(const void* x, int rows, int cols, float layer_scale, void* data, void* scales,
+                        int chunked, cudaStream_t stream);
+int pack_fp8_scales(const float* scales, int rows, int kblocks, int block_rows, void* out,
+                    cudaStream_t stream);
+
+// quant_path.cu
+int gather_q_rows(const OwnerRows& o, int rank, int e_local, int cap, int top_k, int kind, int hidden,
+                  const PeerBytes& stage, size_t sf_offset, const int* meta_origin, const float* meta_prob,
+                  uint8_t* rows_out, uint32_t* sfa_out, int* origin_out, float* prob_out, int ctas,
+                  cudaStream_t stream);
+int swiglu_quantize(DeviceRange rows, const __nv_bfloat16* ab, const float* prob, int inter, int kind,
+                    float layer_scale, uint8_t* uq, uint32_t* sfa_out, int sms, cudaStream_t stream);
+// out[rows, n] = alpha * A[rows, k] * B[e][n, k]^T with quantised operands; `push` != nullptr sends the
+// rows to the source ranks' mailboxes instead of storing them.
+int launch_block_scaled(int kind, const Schedule& s, const void* a, const SfLayout& sfa, const void* b,
+                        const SfLayout& sfb, __nv_bfloat16* out, const PushTarget* push, int n, int k,
+                        float alpha, int* status, int sms, cudaStream_t stream);
+
+}  // namespace wm

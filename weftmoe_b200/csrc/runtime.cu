@@ -18,6 +18,7 @@
 
 #include "../../include/weftmoe_b200.h"
 #include "kernels.h"
+#include "quant_path.h"
 #include "route.h"
 
 using namespace wm;
@@ -64,7 +65,7 @@ struct ScratchLayout {
   size_t status, sorted_slot, sorted_expert, slot_pos, local_offset, dst_rank, dst_row, dst_prow,
       chunk_hist, local_count, expert_total, expert_before, expert_base, expert_pbase, padded_start,
       tile_group, num_tiles, padded_rows, pair_tiles, num_pairs, split, origin, prob, xrows, u, recv, du,
-      dab, total;
+      dab, abq, sfa_x, sfa_u, total;
 };
 // Training cache carved out of the caller's tape buffer.
 struct TapeLayout {
@@ -146,6 +147,12 @@ ScratchLayout scratch_layout(const wm_config& c, int row_cap) {
   s.prob = k.take(sizeof(float) * row_cap);
   s.xrows = k.take(2ull * row_cap * c.hidden);
   s.u = k.take(2ull * row_cap * c.intermediate);
+  if (c.reserved != 0) {  // quantised precisions: BF16 gate/up rows and scale-factor chunks
+    const size_t tiles = row_cap / 128;
+    s.abq = k.take(4ull * row_cap * c.intermediate);
+    s.sfa_x = k.take(tiles * (c.hidden / 64) * 512);
+    s.sfa_u = k.take(tiles * (c.intermediate / 64) * 512);
+  }
   if (c.training) {
     s.recv = k.take(2ull * row_cap * c.hidden);
     s.du = k.take(2ull * row_cap * c.intermediate);
@@ -193,6 +200,10 @@ int check_config(const wm_config& c) {
       c.max_rows < 0) {
     set_error("Unsupported expert shape or token capacity (E=%d K=%d H=%d I=%d T=%d rows=%d)",
               c.experts, c.top_k, c.hidden, c.intermediate, c.max_tokens, c.max_rows);
+    return WM_ERR_INVALID;
+  }
+  if (c.reserved < 0 || c.reserved > 2 || (c.reserved == 2 && c.intermediate % 256)) {
+    set_error("precision must be 0 (BF16), 1 (blockwise FP8) or 2 (NVFP4; needs intermediate %% 256 == 0)");
     return WM_ERR_INVALID;
   }
   const long long origin_span = 1ll * c.world * (c.max_tokens > 0 ? c.max_tokens : 1) * c.top_k;
@@ -723,6 +734,159 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
     return rc;
   return unpermute_dgates(at<float>(rt->arena, rt->al.dgate_box), sorted_slot, sorted_expert, tokens,
                           c.top_k, dgates, stream);
+}
+
+// =============================================================================== quantised forward
+extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t* routes,
+                                    const float* gates, const wm_quant_weights* weights, int32_t tokens,
+                                    void* y, void* stream_) {
+  if (int rc = check_ready(rt, "wm_forward_quantized")) return rc;
+  const wm_config& c = rt->cfg;
+  const int kind = c.reserved == 1 ? kKindFp8 : kKindNvfp4;
+  if (c.reserved == 0) {
+    set_error("wm_forward_quantized: the runtime was created for BF16");
+    return WM_ERR_STATE;
+  }
+  if (tokens < 0 || tokens > c.max_tokens) {
+    set_error("Activation shape exceeds prepared capacity (%d tokens, capacity %d)", tokens, c.max_tokens);
+    return WM_ERR_CAPACITY;
+  }
+  if (!weights || !weights->w1 || !weights->w1_sf || !weights->w2 || !weights->w2_sf ||
+      (tokens > 0 && (!x || !routes || !gates || !y)) || !aligned16(x) || !aligned16(y) ||
+      !aligned16(weights->w1) || !aligned16(weights->w2) || !aligned16(weights->w1_sf) ||
+      !aligned16(weights->w2_sf)) {
+    set_error("wm_forward_quantized: null or misaligned tensor (16-byte alignment required)");
+    return WM_ERR_INVALID;
+  }
+  if (kind == kKindNvfp4 && !(weights->x_scale > 0 && weights->w1_scale > 0 && weights->u_scale > 0 &&
+                              weights->w2_scale > 0)) {
+    set_error("NVFP4 tensor scales must be finite and positive");
+    return WM_ERR_INVALID;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int gen = ++rt->generation;
+  const int world = c.world;
+  const int H = c.hidden, I = c.intermediate;
+  uint8_t* S = rt->scratch;
+  int* status = at<int>(S, rt->sl.status);
+  RouteLocal local{at<int>(S, rt->sl.sorted_slot), at<int>(S, rt->sl.sorted_expert), at<int>(S, rt->sl.slot_pos)};
+  PlanTables tables{};
+  tables.expert_total = at<int>(S, rt->sl.expert_total);
+  tables.expert_before = at<int>(S, rt->sl.expert_before);
+  tables.expert_base = at<int>(S, rt->sl.expert_base);
+  tables.expert_pbase = at<int>(S, rt->sl.expert_pbase);
+  tables.padded_start = at<int>(S, rt->sl.padded_start);
+  tables.tile_group = at<int>(S, rt->sl.tile_group);
+  tables.num_tiles = at<int>(S, rt->sl.num_tiles);
+  tables.padded_rows = at<int>(S, rt->sl.padded_rows);
+  tables.pair_tiles = at<int>(S, rt->sl.pair_tiles);
+  tables.num_pairs = at<int>(S, rt->sl.num_pairs);
+  tables.split = at<int>(S, rt->sl.split);
+  int* origin = at<int>(S, rt->sl.origin);
+  float* prob = at<float>(S, rt->sl.prob);
+  uint8_t* xq = at<uint8_t>(S, rt->sl.xrows);
+  uint8_t* uq = at<uint8_t>(S, rt->sl.u);
+  auto* abq = at<__nv_bfloat16>(S, rt->sl.abq);
+  auto* sfa_x = at<uint32_t>(S, rt->sl.sfa_x);
+  auto* sfa_u = at<uint32_t>(S, rt->sl.sfa_u);
+
+  RouteShape shape{c.experts, c.top_k, world, c.rank, c.max_tokens};
+  PeerInts counts{}, meta_origin{};
+  PeerFloats meta_prob{};
+  PeerBytes stage{};
+  PushTarget push{};
+  for (int r = 0; r < world; ++r) {
+    counts.p[r] = at<int>(rt->peer[r], rt->al.counts);
+    meta_origin.p[r] = at<int>(rt->peer[r], rt->al.meta_origin);
+    meta_prob.p[r] = at<float>(rt->peer[r], rt->al.meta_prob);
+    stage.p[r] = rt->peer[r] + rt->al.stage;
+    push.mailbox[r] = at<__nv_bfloat16>(rt->peer[r], rt->al.mailbox);
+  }
+  push.origin = origin;
+  push.cap = c.max_tokens;
+  push.top_k = c.top_k;
+
+  // 1. quantise this rank's tokens into the staging buffer: data rows, then the scale rows.
+  const size_t row_bytes = kind == kKindFp8 ? H : H / 2;
+  const size_t sf_offset = align_up(static_cast<size_t>(c.max_tokens) * row_bytes);
+  if (world > 1)
+    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, stream)) return rc;
+  uint8_t* my_stage = rt->arena + rt->al.stage;
+  if (tokens > 0) {
+    if (kind == kKindFp8) {
+      if (int rc = fp8_quantize_rows(x, tokens, H, my_stage, reinterpret_cast<float*>(my_stage + sf_offset),
+                                     rt->sms, stream))
+        return rc;
+    } else {
+      if (int rc = nvfp4_quantize_rows(x, tokens, H, weights->x_scale, my_stage, my_stage + sf_offset, 0, stream))
+        return rc;
+    }
+  }
+  // 2. route plan (as wm_forward).
+  if (int rc = route_local(shape, routes, tokens, local, at<int>(S, rt->sl.chunk_hist),
+                           at<int>(S, rt->sl.local_count), counts, stream))
+    return rc;
+  if (world > 1)
+    if (int rc = signal_peers(flag_group(rt, kCounts), world, c.rank, gen, stream)) return rc;
+  if (int rc = route_global(shape, at<int>(rt->arena, rt->al.counts), my_flags(rt, kCounts),
+                            world > 1 ? gen : 0, rt->row_cap, tables, status, stream))
+    return rc;
+  RouteRows rows{at<int>(S, rt->sl.local_offset), at<int>(S, rt->sl.dst_rank), at<int>(S, rt->sl.dst_row),
+                 at<int>(S, rt->sl.dst_prow)};
+  if (int rc = route_rows(shape, routes, gates, tokens, local, at<int>(S, rt->sl.chunk_hist), tables, rows,
+                          meta_origin, meta_prob, stream))
+    return rc;
+  if (world > 1) {
+    if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
+  }
+  // 3. owner side: pull quantised rows + scale factors, FC1, SwiGLU + re-quantisation, FC2 -> mailboxes.
+  OwnerRows owner{tables.padded_start, tables.tile_group, split_range(tables.split, 2, kWhole),
+                  tables.expert_total};
+  if (int rc = gather_q_rows(owner, c.rank, rt->e_local, c.max_tokens, c.top_k, kind, H, stage, sf_offset,
+                             at<int>(rt->arena, rt->al.meta_origin), at<float>(rt->arena, rt->al.meta_prob),
+                             xq, sfa_x, origin, prob, rt->sms * 8, stream))
+    return rc;
+  if (world > 1)
+    if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
+  Schedule sched{tables.split, tables.tile_group, tables.padded_start, rt->e_local, rt->row_cap,
+                 tables.pair_tiles, false, kWhole};
+  const long long chunk = 512;
+  const int kx = kind == kKindFp8 ? H / 128 : H / 64;   // scale-factor chunks per row tile along K
+  const int ku = kind == kKindFp8 ? I / 128 : I / 64;
+  const long long stage_chunks = kind == kKindFp8 ? 1 : 4;
+  const SfLayout sfa1{reinterpret_cast<const uint8_t*>(sfa_x), 0, kx * chunk, stage_chunks * chunk, chunk};
+  const SfLayout sfb1{static_cast<const uint8_t*>(weights->w1_sf), (2ll * I / 128) * kx * chunk, kx * chunk,
+                      stage_chunks * chunk, chunk};
+  const SfLayout sfa2{reinterpret_cast<const uint8_t*>(sfa_u), 0, ku * chunk, stage_chunks * chunk, chunk};
+  const SfLayout sfb2{static_cast<const uint8_t*>(weights->w2_sf), (1ll * H / 128) * ku * chunk, ku * chunk,
+                      stage_chunks * chunk, chunk};
+  const float alpha1 = kind == kKindFp8 ? 1.0f : weights->x_scale * weights->w1_scale;
+  const float alpha2 = kind == kKindFp8 ? 1.0f : weights->u_scale * weights->w2_scale;
+  if (int rc = launch_block_scaled(kind, sched, xq, sfa1, weights->w1, sfb1, abq, nullptr, 2 * I, H, alpha1,
+                                   status, rt->sms, stream))
+    return rc;
+  if (int rc = swiglu_quantize(split_range(tables.split, 2, kWhole), abq, prob, I, kind,
+                               kind == kKindFp8 ? 1.0f : weights->u_scale, uq, sfa_u, rt->sms, stream))
+    return rc;
+  if (int rc = launch_block_scaled(kind, sched, uq, sfa2, weights->w2, sfb2, nullptr, &push, H, I, alpha2,
+                                   status, rt->sms, stream))
+    return rc;
+  if (world > 1) {
+    if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
+  }
+  return combine_rows(at<__nv_bfloat16>(rt->arena, rt->al.mailbox), local.sorted_expert, tokens,
+                      c.max_tokens, c.top_k, c.hidden, static_cast<__nv_bfloat16*>(y), stream);
+}
+
+extern "C" int wm_fp8_pack_weight_scales(const float* scales, int32_t rows, int32_t kblocks, void* out,
+                                         void* stream) {
+  if (rows < 0 || rows % 128 || kblocks < 0 || (static_cast<long long>(rows) * kblocks > 0 && (!scales || !out))) {
+    set_error("wm_fp8_pack_weight_scales: rows must be a multiple of 128");
+    return WM_ERR_INVALID;
+  }
+  return pack_fp8_scales(scales, rows, kblocks, 128, out, static_cast<cudaStream_t>(stream));
 }
 
 // =============================================================================== stand-alone plan

@@ -94,8 +94,10 @@ class Tape:
 class NativeRuntime:
     """Owner of one `wm_runtime` handle; serialised on the supplied CUDA stream."""
 
+    PRECISIONS = {"bf16": 0, "fp8": 1, "nvfp4": 2}
+
     def __init__(self, collectives, experts, top_k, hidden, intermediate, max_tokens, max_rows,
-                 stream, training, max_saved):
+                 stream, training, max_saved, precision="bf16"):
         self.lib = _lib.load()
         self.col = collectives
         # A legacy default stream cannot join a caller's CUDA Graph capture
@@ -110,7 +112,9 @@ class NativeRuntime:
         config = _lib.WmConfig(rank=collectives.rank, world=collectives.world, experts=experts,
                                top_k=top_k, hidden=hidden, intermediate=intermediate,
                                max_tokens=max_tokens, max_rows=max_rows, training=int(training),
-                               reserved=0)
+                               reserved=self.PRECISIONS[precision])
+        self.precision = precision
+        self.scales = None  # NVFP4Scales, set by TensorRuntime for precision "nvfp4"
         handle = ctypes.c_void_p()
         # Agree on the outcome of local preparation before any rank touches a peer mapping.
         error = None
@@ -177,6 +181,61 @@ class NativeRuntime:
         self.tapes.add(tape)
         return tape
 
+    # ------------------------------------------------------------------ quantised inference
+    def _run_quantized(self, x, routes, gates, packed):
+        """packed: (w1 data, w1 scale chunks, w2 data, w2 scale chunks, x_scale, w1_scale, u_scale, w2_scale)."""
+        self._require()
+        caller = torch.cuda.current_stream()
+        if caller.device != self.stream.device or x.device != self.stream.device:
+            raise ValueError("Workspace and tensors must share the current device")
+        if caller != self.stream:
+            self.stream.wait_stream(caller)
+        with torch.cuda.stream(self.stream):
+            y = torch.empty_like(x)
+            w1, w1_sf, w2, w2_sf, sx, s1, su, s2 = packed
+            weights = _lib.WmQuantWeights(w1=w1.data_ptr(), w1_sf=w1_sf.data_ptr(), w2=w2.data_ptr(),
+                                          w2_sf=w2_sf.data_ptr(), x_scale=sx, w1_scale=s1, u_scale=su, w2_scale=s2)
+            _lib.check(self.lib.wm_forward_quantized(self.handle, _lib.ptr(x), _lib.ptr(routes), _lib.ptr(gates),
+                                                     ctypes.byref(weights), x.shape[0], _lib.ptr(y),
+                                                     self.stream.cuda_stream))
+            if caller != self.stream:
+                for tensor in (x, routes, gates, w1, w1_sf, w2, w2_sf):
+                    tensor.record_stream(self.stream)
+                y.record_stream(caller)
+        if caller != self.stream:
+            caller.wait_stream(self.stream)
+        return y
+
+    def _fp8_packed(self, weights):
+        """UE8M0 scale-factor chunks of prepared FP8 weights (packed once per weight version)."""
+        cached = getattr(weights, "_wm_chunks", None)
+        if cached is None:
+            chunks = []
+            for w in (weights.w1, weights.w2):
+                e, n, k = w.shape
+                out = torch.empty(e * n // 128, k // 128, 128, dtype=torch.int32, device=w.data.device)
+                _lib.check(self.lib.wm_fp8_pack_weight_scales(_lib.ptr(w.scales), e * n, k // 128, _lib.ptr(out),
+                                                              torch.cuda.current_stream().cuda_stream))
+                chunks.append(out)
+            cached = tuple(chunks)
+            object.__setattr__(weights, "_wm_chunks", cached)
+        return (weights.w1.data, cached[0], weights.w2.data, cached[1], 1.0, 1.0, 1.0, 1.0)
+
+    def forward_fp8(self, x, routes, gates, weights, synchronize, retain_backward_state, fp32_wgrad):
+        if retain_backward_state and self.training:
+            raise ValueError("Blockwise-FP8 backward is not built yet: call forward_fp8 with "
+                             "retain_backward_state=False or use the BF16 runtime for training")
+        y = self._run_quantized(x, routes, gates, self._fp8_packed(weights))
+        if synchronize:
+            self._poll()
+        return Tape(y)
+
+    def inference(self, x, routes, gates, weights, x_scale, intermediate_scale):
+        """NVFP4 inference with prepared weights (reference: NVFP4Runtime.inference, weftmoe/nvfp4.py:252-278)."""
+        (w1, w1_sf), (w2, w2_sf) = weights.fc1, weights.fc2
+        return self._run_quantized(x, routes, gates, (w1, w1_sf, w2, w2_sf, x_scale, weights.tensor_scales[0],
+                                                      intermediate_scale, weights.tensor_scales[1]))
+
     # ------------------------------------------------------------------ training
     def forward_async(self, x, routes, gates, w1, w2, retain_backward_state=True):
         if self.training and retain_backward_state:
@@ -212,7 +271,9 @@ class NativeRuntime:
         return result
 
     # ------------------------------------------------------------------ inference
-    def graph_forward(self, layer, x, routes, gates, w1, w2, caller_stream):
+    def graph_forward(self, layer, x, routes, gates, w1, w2, caller_stream, fp8_weights=None):
+        if fp8_weights is not None:
+            return self._run_quantized(x, routes, gates, self._fp8_packed(fp8_weights))
         return self._run(x, routes, gates, w1, w2)
 
     def eager_inference_async(self, x, routes, gates, w1, w2, caller_stream, layer=None):
@@ -338,8 +399,19 @@ class TensorRuntime:
             raise ValueError("nvfp4_scales requires NVFP4 precision")
         if self.nodes != 1:
             raise ValueError("This build serves one NVLink node: EP ranks must share a host")
-        if self.precision not in ("bf16",) or fp8_workspace or input_layout != "dp":
-            raise ValueError("Blackwell requires DP-sharded BF16 or NVFP4")
+        if self.precision not in ("bf16", "fp8", "nvfp4") or input_layout != "dp":
+            raise ValueError("Unsupported runtime precision")
+        if fp8_workspace and self.precision != "fp8":
+            raise ValueError("Unsupported runtime precision")
+        if self.precision != "bf16" and training:
+            raise ValueError("Quantised (FP8 / NVFP4) runtimes serve inference only in this build; "
+                             "train with the BF16 runtime")
+        if self.precision == "nvfp4":
+            from .nvfp4 import NVFP4Scales, _validate_scales
+            if intermediate % 256:
+                raise ValueError("NVFP4 requires intermediate divisible by 256")
+            self.nvfp4_scales = NVFP4Scales() if nvfp4_scales is None else NVFP4Scales(*nvfp4_scales)
+            _validate_scales(self.nvfp4_scales)
         if hidden > 4096 and hidden % 512:
             raise ValueError("Blackwell combine requires hidden divisible by 512 when hidden > 4096")
         if (max_tokens < 0 or hidden < 256 or hidden % 256 or not 128 <= intermediate <= 4096
@@ -348,16 +420,20 @@ class TensorRuntime:
                 or self.world not in (1, 2, 4, 8)):
             raise ValueError("Unsupported Blackwell expert shape or token capacity")
         factory = _native_factory or NativeRuntime
+        extra = () if self.precision == "bf16" else (self.precision,)
         self.native = factory(col, experts, top_k, hidden, intermediate, max_tokens, max_rows,
-                              self.stream, training, max_saved if training else 1)
+                              self.stream, training, max_saved if training else 1, *extra)
+        if self.precision == "nvfp4":
+            self.native.scales = self.nvfp4_scales
         self.stream = getattr(self.native, "stream", self.stream)
         self.compilation = None
 
     def _check(self, x, routes, gates, w1, w2):
         if self.native is None:
             raise RuntimeError("WeftMoE runtime is closed")
-        if self.fp8_workspace:
-            raise ValueError("Compact FP8 workspace requires forward_fp8 or moe(..., fp8_weights=...)")
+        if self.precision != "bf16":
+            raise ValueError("Compact FP8 workspace requires forward_fp8 or moe(..., fp8_weights=...)"
+                             if self.precision == "fp8" else "NVFP4 runtimes take inference_nvfp4")
         if self.training and torch.cuda.current_stream() != self.stream:
             raise RuntimeError("Runtime must be invoked on its preparation stream")
         if x.ndim != 2 or x.shape[1] != self.hidden or x.shape[0] > self.max_tokens:
@@ -410,9 +486,73 @@ class TensorRuntime:
         self._check_dy(dy)
         return self.native.backward_async(tape, dy)
 
+    def _check_quantized(self, x, routes, gates):
+        if self.native is None:
+            raise RuntimeError("WeftMoE runtime is closed")
+        if (not isinstance(x, torch.Tensor) or x.dtype != torch.bfloat16 or x.ndim != 2
+                or x.shape[1] != self.hidden or x.shape[0] > self.max_tokens or not x.is_cuda
+                or not x.is_contiguous() or x.device != self.stream.device):
+            raise ValueError("Source shape/device/layout does not match runtime")
+        for value, dtype in ((routes, torch.int32), (gates, torch.float32)):
+            if (value.shape != (x.shape[0], self.top_k) or value.dtype != dtype or not value.is_cuda
+                    or value.device != x.device or not value.is_contiguous()):
+                raise ValueError(f"Expected contiguous CUDA {dtype} of shape {(x.shape[0], self.top_k)}")
+
+    def _check_fp8_weights(self, weights, device):
+        from .fp8 import PreparedFP8Weights
+        if not isinstance(weights, PreparedFP8Weights):
+            raise TypeError("weights must be PreparedFP8Weights")
+        if (weights.w1.shape != (self.experts // self.world, 2 * self.intermediate, self.hidden)
+                or weights.w2.shape != (self.experts // self.world, self.hidden, self.intermediate)
+                or weights.w1.data.device != device):
+            raise ValueError("Prepared FP8 weights do not match runtime shape/device")
+
     def forward_fp8(self, x, routes, gates, weights, *, synchronize=True,
                     retain_backward_state=True, weight_grad_dtype=torch.float32):
-        raise ValueError("Blackwell requires DP-sharded BF16 or NVFP4")
+        """Forward with BF16 input quantised online (1x128) and prepared FP8 weights.
+
+        Prepare weights with weftmoe_b200.fp8.prepare_fp8_weights before this call.  Backward for FP8
+        tapes is not built yet: pass retain_backward_state=False (prequantised FP8Tensor inputs are
+        not accepted either)."""
+        if weight_grad_dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("weight_grad_dtype must be torch.bfloat16 or torch.float32")
+        if self.precision != "fp8":
+            raise ValueError("Prepare an FP8 runtime first (precision='fp8' or fp8_workspace=True)")
+        self._check_quantized(x, routes, gates)
+        self._check_fp8_weights(weights, x.device)
+        weights.wait(training=False)
+        return self.native.forward_fp8(x, routes, gates, weights, synchronize, retain_backward_state,
+                                       weight_grad_dtype == torch.float32)
+
+    def inference_fp8(self, layer, x, routes, gates, weights):
+        """Replayable FP8 inference with stable input addresses (reference: weftmoe/runtime.py:387-415)."""
+        if self.training or self.precision != "fp8":
+            raise ValueError("inference_fp8 requires an FP8 runtime with training=False")
+        self._check_quantized(x, routes, gates)
+        self._check_fp8_weights(weights, x.device)
+        if torch.cuda.is_current_stream_capturing():
+            weights._validate_version()
+        else:
+            weights.wait(training=False)
+        return self.native.graph_forward(layer, x, routes, gates, weights.w1.data, weights.w2.data,
+                                         torch.cuda.current_stream().cuda_stream, weights)
+
+    def inference_nvfp4(self, layer, x, routes, gates, weights, *, x_scale=None, intermediate_scale=None):
+        """Run prepared NVFP4 experts with online block-16 activation quantization."""
+        from .nvfp4 import NVFP4Weights, _validate_scales
+        if self.precision != "nvfp4" or self.training:
+            raise ValueError("Prepare an NVFP4 inference runtime first")
+        self._check_quantized(x, routes, gates)
+        if not isinstance(weights, NVFP4Weights):
+            raise TypeError("Expected prepared NVFP4 expert weights")
+        e = self.experts // self.world
+        if (weights.fc1[0].shape != (e, 2 * self.intermediate, self.hidden // 2)
+                or weights.fc2[0].shape != (e, self.hidden, self.intermediate // 2)):
+            raise ValueError("NVFP4 weights do not match the prepared experts")
+        x_scale = self.nvfp4_scales.x if x_scale is None else x_scale
+        intermediate_scale = self.nvfp4_scales.intermediate if intermediate_scale is None else intermediate_scale
+        _validate_scales((x_scale, intermediate_scale))
+        return self.native.inference(x, routes, gates, weights, x_scale, intermediate_scale)
 
     def drain(self):
         """Finish the pending training call before inspecting or releasing leases."""
