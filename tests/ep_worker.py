@@ -90,6 +90,40 @@ def main():
         ep1.close()
         if rank == 0:
             print(f"EP{world} {scenario}: oracle parity, bitwise repeat and EP1 == EP{world} bits passed", flush=True)
+    # ---- quantised inference (NVFP4 and blockwise FP8) over the EP group: EPn bits == EP1 bits
+    from weftmoe_b200.fp8 import prepare_fp8_weights
+    from weftmoe_b200.nvfp4 import prepare_nvfp4_weights
+    counts = [29 + 5 * r for r in range(world)]
+    g = torch.Generator().manual_seed(77)
+    w1 = (torch.randn(E, 2 * I, H, generator=g) * 0.023).bfloat16()
+    w2 = (torch.randn(E, H, I, generator=g) * 0.023).bfloat16()
+    xs = [(torch.randn(t, H, generator=g) * 0.16).bfloat16() for t in counts]
+    rs = [torch.rand(t, E, generator=g).topk(K).indices.int() for t in counts]
+    gs = [torch.rand(t, K, generator=g) for t in counts]
+    for precision in ("nvfp4", "fp8"):
+        outs = []
+        for group, n, sl in ((dist.group.WORLD, max(counts), slice(rank * e_local, (rank + 1) * e_local)),
+                             (SingleRankGroup(), sum(counts), slice(0, E))):
+            rt = TensorRuntime(group=group, experts=E, top_k=K, hidden=H, intermediate=I, max_tokens=max(n, 1),
+                               max_rows=sum(counts) * K, training=False, precision=precision)
+            lw1, lw2 = w1[sl].contiguous().cuda(), w2[sl].contiguous().cuda()
+            single = isinstance(group, SingleRankGroup)
+            x = (torch.cat(xs) if single else xs[rank]).cuda()
+            r = (torch.cat(rs) if single else rs[rank]).cuda()
+            gt = (torch.cat(gs) if single else gs[rank]).cuda()
+            if precision == "nvfp4":
+                y = rt.inference_nvfp4(0, x, r, gt, prepare_nvfp4_weights(lw1, lw2))
+            else:
+                y = rt.inference_fp8(0, x, r, gt, prepare_fp8_weights(lw1, lw2, training=False))
+            outs.append(y.clone())
+            rt.close()
+        begin = sum(counts[:rank])
+        assert torch.equal(bits(outs[1][begin:begin + counts[rank]]), bits(outs[0])), (precision, "EP1 != EPn bits")
+        ref = O.quantized_layer(torch.cat(xs), torch.cat(rs), torch.cat(gs), w1, w2, kind=precision)
+        err = rel_l2(outs[0], ref[begin:begin + counts[rank]])
+        assert err < 5e-3, (precision, err)
+    if rank == 0:
+        print(f"EP{world} quantised inference (nvfp4, fp8): oracle parity and EP1 == EP{world} bits passed", flush=True)
     # ---- received rows beyond max_rows: a collective, reported error, runtime stays usable
     small = TensorRuntime(group=dist.group.WORLD, experts=E, top_k=K, hidden=H, intermediate=I,
                           max_tokens=512, max_rows=128, training=False)
