@@ -116,7 +116,17 @@ typedef struct wm_quant_weights {
   float x_scale, w1_scale, u_scale, w2_scale; /* NVFP4 layer scales; ignored for FP8 */
 } wm_quant_weights;
 WM_API int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t* routes, const float* gates,
-                                const wm_quant_weights* weights, int32_t tokens, void* y, void* stream);
+                                const wm_quant_weights* weights, int32_t tokens, void* y, void* tape,
+                                void* stream);
+/* Blockwise-FP8 backward (reference: forward_fp8 + backward, weftmoe/runtime.py:303-367; dataflow
+ * docs/usage.md:216-252).  `tape` (tape_bytes, same size as the BF16 tape) was filled by
+ * wm_forward_quantized on an FP8 runtime created with training = 1; `transposed` holds the prepared
+ * W1^T [E_local][H][2I] and W2^T [E_local][I][H] bytes with their packed scale chunks.  dY is quantised
+ * 1 x 128 at the source; dU and dX run in FP8; dW1/dW2 are BF16 contractions of the dequantised saved X
+ * and dY rows (a stated simplification: no column-wise re-quantisation), returned as BF16. */
+WM_API int wm_backward_quantized(wm_runtime* rt, const void* tape, const void* dy,
+                                 const wm_quant_weights* transposed, int32_t tokens, void* dx,
+                                 float* dgates, void* dw1, void* dw2, void* stream);
 /* scales [rows/128][kblocks] FP32 (128 x 128 blocks of a [rows][K] weight, experts stacked along rows)
  * -> UE8M0 chunks [rows/128][kblocks][512 bytes]. */
 WM_API int wm_fp8_pack_weight_scales(const float* scales, int32_t rows, int32_t kblocks, void* out,

@@ -95,3 +95,43 @@ def test_quantised_runtime_contract_errors():
     with pytest.raises(TypeError):
         rt.inference_fp8(0, g["x"], g["routes"], g["gates"], (g["w1"], g["w2"]))
     rt.close()
+
+
+@pytest.mark.parametrize("cfg", [dict(experts=16, top_k=4, hidden=512, intermediate=256, tokens=200),
+                                 dict(experts=8, top_k=2, hidden=768, intermediate=384, tokens=130)])
+def test_fp8_training_forward_backward_meets_the_reference_acceptance(cfg):
+    """FP8 acceptance of the reference (benchmarks/training_reference.py:61-67, benchmarks/fp8_validation.py):
+    global diff < 5e-3 against the BF16 result for output and dX, per expert for dW1/dW2; dprob finite."""
+    from weftmoe_b200 import moe
+    d, g = inputs(cfg, 21, 1.0, 0.02)
+    rt = TensorRuntime(group=SingleRankGroup(), experts=cfg["experts"], top_k=cfg["top_k"], hidden=cfg["hidden"],
+                       intermediate=cfg["intermediate"], max_tokens=cfg["tokens"],
+                       max_rows=cfg["tokens"] * cfg["top_k"], training=True, precision="fp8", max_saved=2)
+    weights = prepare_fp8_weights(g["w1"], g["w2"], training=True)
+    ref = O.moe_layer(d["x"], d["routes"], d["gates"], d["w1"], d["w2"], d["dy"], precision="bf16")
+    results = []
+    for _ in range(2):
+        tape = rt.forward_fp8(g["x"], g["routes"], g["gates"], weights, weight_grad_dtype=torch.bfloat16)
+        results.append((tape.output, *rt.backward(tape, g["dy"])))
+    for a, b in zip(*results):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))            # repeatable bit for bit
+    y, dx, dg, dw1, dw2 = results[0]
+    assert global_diff(y, ref[0]) < 5e-3 and global_diff(dx, ref[1]) < 5e-3
+    assert torch.isfinite(dg).all() and rel_l2(dg, ref[2]) < 0.1
+    live = [e for e in range(cfg["experts"]) if (d["routes"] == e).any()]
+    for e in live:
+        assert global_diff(dw1[e], ref[3][e]) < 5e-3, (e, global_diff(dw1[e], ref[3][e]))
+        assert global_diff(dw2[e], ref[4][e]) < 5e-3, (e, global_diff(dw2[e], ref[4][e]))
+    # the no-tape forward gives the same bits as the saving forward
+    assert torch.equal(rt.forward_fp8(g["x"], g["routes"], g["gates"], weights, retain_backward_state=False).output
+                       .view(torch.int16), y.view(torch.int16))
+    # autograd entry point with FP32 weight gradients for FP32 parameters
+    x = g["x"].clone().requires_grad_()
+    w1, w2 = g["w1"].float().requires_grad_(), g["w2"].float().requires_grad_()
+    gates = g["gates"].clone().requires_grad_()
+    prepared = prepare_fp8_weights(w1, w2)
+    out = moe(rt, x, g["routes"], gates, w1, w2, fp8_weights=prepared)
+    out.backward(g["dy"])
+    assert w1.grad.dtype == torch.float32 and global_diff(x.grad, ref[1]) < 5e-3
+    assert global_diff(w2.grad[live[0]], ref[4][live[0]]) < 5e-3
+    rt.close()

@@ -52,7 +52,9 @@ SIGNATURES = {
     "wm_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p,
                             c_void_p, c_void_p, c_void_p, c_void_p]),
     "wm_forward_quantized": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(WmQuantWeights), c_int32,
-                                     c_void_p, c_void_p]),
+                                     c_void_p, c_void_p, c_void_p]),
+    "wm_backward_quantized": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(WmQuantWeights), c_int32, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_void_p]),
     "wm_fp8_pack_weight_scales": (c_int, [c_void_p, c_int32, c_int32, c_void_p, c_void_p]),
     "wm_status_poll": (c_int, [c_void_p, POINTER(c_int32), c_void_p]),
     "wm_launch_count": (ctypes.c_longlong, []),

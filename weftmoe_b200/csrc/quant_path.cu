@@ -61,11 +61,13 @@ __device__ __forceinline__ int chunk_word(int r) { return (r & 31) * 4 + ((r & 1
 // ------------------------------------------------------------------ owner-side pull
 // One warp per padded row: copy the quantised row from its source rank's staging buffer and write
 // its scale words into the chunked layout; padding rows get zero data and neutral scales.
+// by_origin != 0 (backward): `meta_origin` is the saved origin array (-1 on padding rows) and nothing is
+// written to origin_out / prob_out.
 __global__ void gather_q_kernel(OwnerRows o, int rank, int e_local, int cap, int top_k, int kind, int hidden,
                                 PeerBytes stage, size_t sf_offset, const int* __restrict__ meta_origin,
                                 const float* __restrict__ meta_prob, uint8_t* __restrict__ rows_out,
                                 uint32_t* __restrict__ sfa_out, int* __restrict__ origin_out,
-                                float* __restrict__ prob_out) {
+                                float* __restrict__ prob_out, int by_origin) {
   const int rows = *o.rows.end;
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -73,8 +75,13 @@ __global__ void gather_q_kernel(OwnerRows o, int rank, int e_local, int cap, int
   const int sf_words = kind == kKindFp8 ? hidden / 128 : hidden / 64;
   const int vecs = row_bytes / 16;
   for (int r = *o.rows.begin + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += warps) {
-    const int l = o.tile_group[r >> 7];
-    const bool live = r - o.padded_start[l] < o.expert_total[rank * e_local + l];
+    bool live;
+    if (by_origin) {
+      live = meta_origin[r] >= 0;
+    } else {
+      const int l = o.tile_group[r >> 7];
+      live = r - o.padded_start[l] < o.expert_total[rank * e_local + l];
+    }
     uint4* dst = reinterpret_cast<uint4*>(rows_out + static_cast<size_t>(r) * row_bytes);
     uint32_t* sf_dst = sfa_out + static_cast<size_t>(r >> 7) * sf_words * 128 + chunk_word(r);
     if (live) {
@@ -94,14 +101,14 @@ __global__ void gather_q_kernel(OwnerRows o, int rank, int e_local, int cap, int
         }
         sf_dst[static_cast<size_t>(j) * 128] = word;
       }
-      if (lane == 0) {
+      if (lane == 0 && !by_origin) {
         origin_out[r] = org;
         prob_out[r] = meta_prob[r];
       }
     } else {
       for (int c = lane; c < vecs; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
       for (int j = lane; j < sf_words; j += 32) sf_dst[static_cast<size_t>(j) * 128] = kind == kKindFp8 ? 0x7f7f7f7fu : 0u;
-      if (lane == 0) {
+      if (lane == 0 && !by_origin) {
         origin_out[r] = -1;
         prob_out[r] = 0.0f;
       }
@@ -177,6 +184,79 @@ __global__ void swiglu_quantize_kernel(DeviceRange range, const __nv_bfloat16* _
   }
 }
 
+// ------------------------------------------------------------------ FP8 helpers of the backward pass
+// BF16 rows -> E4M3 bytes + UE8M0 scale words in the chunked layout (1 x 128 blocks): sixteen lanes per
+// block, eight values per lane, over a device-side row range.
+__global__ void fp8_quantize_rows_chunked_kernel(DeviceRange range, const __nv_bfloat16* __restrict__ x,
+                                                 int cols, uint8_t* __restrict__ q,
+                                                 uint32_t* __restrict__ sfa_out) {
+  const int row0 = *range.begin, rows = *range.end;
+  const int kblocks = cols / 128;
+  const long long blocks = static_cast<long long>(rows - row0) * kblocks;
+  const long long half_warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 4;
+  const int sub = threadIdx.x & 15;
+  const unsigned mask = 0xffffu << (threadIdx.x & 16);
+  for (long long b = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4; b < blocks; b += half_warps) {
+    const int r = row0 + static_cast<int>(b / kblocks), kb = static_cast<int>(b % kblocks);
+    const uint4 raw = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * cols + kb * 128)[sub];
+    const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float v[8], m = 0.0f;
+    bool bad = false;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[2 * j] = __uint_as_float(w[j] << 16);
+      v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+      m = fmaxf(m, fmaxf(fabsf(v[2 * j]), fabsf(v[2 * j + 1])));
+      bad |= !isfinite(v[2 * j]) || !isfinite(v[2 * j + 1]);
+    }
+#pragma unroll
+    for (int d = 8; d; d >>= 1) {
+      m = fmaxf(m, __shfl_xor_sync(mask, m, d, 16));
+      bad |= __shfl_xor_sync(mask, static_cast<int>(bad), d, 16) != 0;
+    }
+    const float scale = fp8_block_scale(m, bad);
+    const float inv = scale != scale ? scale : __uint_as_float(0x7f000000u - __float_as_uint(scale));
+    uint2 out;
+    out.x = pack4_e4m3(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+    out.y = pack4_e4m3(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+    reinterpret_cast<uint2*>(q + static_cast<size_t>(r) * cols + kb * 128)[sub] = out;
+    if (sub == 0)
+      sfa_out[(static_cast<size_t>(r >> 7) * kblocks + kb) * 128 + chunk_word(r)] =
+          ((__float_as_uint(scale) >> 23) & 0xffu) * 0x01010101u;
+  }
+}
+
+// E4M3 rows + chunked UE8M0 scales -> BF16 rows (exact: the scale is a power of two).
+__global__ void fp8_dequantize_rows_kernel(DeviceRange range, const uint8_t* __restrict__ q,
+                                           const uint32_t* __restrict__ sfa, int cols,
+                                           __nv_bfloat16* __restrict__ out) {
+  const int row0 = *range.begin, rows = *range.end;
+  const int kblocks = cols / 128;
+  const long long blocks = static_cast<long long>(rows - row0) * kblocks;
+  const long long half_warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 4;
+  const int sub = threadIdx.x & 15;
+  for (long long b = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4; b < blocks; b += half_warps) {
+    const int r = row0 + static_cast<int>(b / kblocks), kb = static_cast<int>(b % kblocks);
+    const uint2 raw = reinterpret_cast<const uint2*>(q + static_cast<size_t>(r) * cols + kb * 128)[sub];
+    const unsigned e8 = sfa[(static_cast<size_t>(r >> 7) * kblocks + kb) * 128 + chunk_word(r)] & 0xffu;
+    const float scale = e8 == 0xffu ? __int_as_float(0x7fc00000) : __uint_as_float(e8 << 23);
+    const unsigned words[2] = {raw.x, raw.y};
+    unsigned o[4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      float f[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>((words[j] >> (8 * i)) & 0xffu), __NV_E4M3);
+        f[i] = __half2float(__half(h)) * scale;
+      }
+      o[2 * j] = pack_bf16x2(f[0], f[1]);
+      o[2 * j + 1] = pack_bf16x2(f[2], f[3]);
+    }
+    reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * cols + kb * 128)[sub] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 template <int KIND>
 int launch_bs_grouped(const Schedule& s, const void* a, const SfLayout& sfa, const void* b, const SfLayout& sfb,
                       __nv_bfloat16* out, const PushTarget* push, int n, int k, float alpha, int* status,
@@ -214,10 +294,11 @@ int launch_bs_grouped(const Schedule& s, const void* a, const SfLayout& sfa, con
 
 int gather_q_rows(const OwnerRows& o, int rank, int e_local, int cap, int top_k, int kind, int hidden,
                   const PeerBytes& stage, size_t sf_offset, const int* meta_origin, const float* meta_prob,
-                  uint8_t* rows_out, uint32_t* sfa_out, int* origin_out, float* prob_out, int ctas,
-                  cudaStream_t stream) {
+                  uint8_t* rows_out, uint32_t* sfa_out, int* origin_out, float* prob_out, int by_origin,
+                  int ctas, cudaStream_t stream) {
   gather_q_kernel<<<ctas, 256, 0, stream>>>(o, rank, e_local, cap, top_k, kind, hidden, stage, sf_offset,
-                                            meta_origin, meta_prob, rows_out, sfa_out, origin_out, prob_out);
+                                            meta_origin, meta_prob, rows_out, sfa_out, origin_out, prob_out,
+                                            by_origin);
   WM_CUDA(cudaGetLastError());
   count_launch();
   return 0;
@@ -228,6 +309,22 @@ int swiglu_quantize(DeviceRange rows, const __nv_bfloat16* ab, const float* prob
   swiglu_quantize_kernel<<<sms * 8, 256, 0, stream>>>(rows, ab, prob, inter, kind,
                                                       static_cast<float>(6.0 * static_cast<double>(layer_scale)),
                                                       layer_scale, uq, sfa_out);
+  WM_CUDA(cudaGetLastError());
+  count_launch();
+  return 0;
+}
+
+int fp8_quantize_rows_chunked(DeviceRange rows, const __nv_bfloat16* x, int cols, uint8_t* q,
+                              uint32_t* sfa_out, int sms, cudaStream_t stream) {
+  fp8_quantize_rows_chunked_kernel<<<sms * 16, 256, 0, stream>>>(rows, x, cols, q, sfa_out);
+  WM_CUDA(cudaGetLastError());
+  count_launch();
+  return 0;
+}
+
+int fp8_dequantize_rows(DeviceRange rows, const uint8_t* q, const uint32_t* sfa, int cols,
+                        __nv_bfloat16* out, int sms, cudaStream_t stream) {
+  fp8_dequantize_rows_kernel<<<sms * 16, 256, 0, stream>>>(rows, q, sfa, cols, out);
   WM_CUDA(cudaGetLastError());
   count_launch();
   return 0;

@@ -30,8 +30,13 @@ int pack_fp8_scales(const float* scales, int rows, int kblocks, int block_rows, 
 // quant_path.cu
 int gather_q_rows(const OwnerRows& o, int rank, int e_local, int cap, int top_k, int kind, int hidden,
                   const PeerBytes& stage, size_t sf_offset, const int* meta_origin, const float* meta_prob,
-                  uint8_t* rows_out, uint32_t* sfa_out, int* origin_out, float* prob_out, int ctas,
-                  cudaStream_t stream);
+                  uint8_t* rows_out, uint32_t* sfa_out, int* origin_out, float* prob_out, int by_origin,
+                  int ctas, cudaStream_t stream);
+// FP8 backward helpers over a device-side row range: BF16 rows -> E4M3 + chunked UE8M0 scales, and back.
+int fp8_quantize_rows_chunked(DeviceRange rows, const __nv_bfloat16* x, int cols, uint8_t* q,
+                              uint32_t* sfa_out, int sms, cudaStream_t stream);
+int fp8_dequantize_rows(DeviceRange rows, const uint8_t* q, const uint32_t* sfa, int cols,
+                        __nv_bfloat16* out, int sms, cudaStream_t stream);
 int swiglu_quantize(DeviceRange rows, const __nv_bfloat16* ab, const float* prob, int inter, int kind,
                     float layer_scale, uint8_t* uq, uint32_t* sfa_out, int sms, cudaStream_t stream);
 // out[rows, n] = alpha * A[rows, k] * B[e][n, k]^T with quantised operands; `push` != nullptr sends the

@@ -739,7 +739,7 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
 // =============================================================================== quantised forward
 extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t* routes,
                                     const float* gates, const wm_quant_weights* weights, int32_t tokens,
-                                    void* y, void* stream_) {
+                                    void* y, void* tape, void* stream_) {
   if (int rc = check_ready(rt, "wm_forward_quantized")) return rc;
   const wm_config& c = rt->cfg;
   const int kind = c.reserved == 1 ? kKindFp8 : kKindNvfp4;
@@ -763,31 +763,42 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
     set_error("NVFP4 tensor scales must be finite and positive");
     return WM_ERR_INVALID;
   }
+  if (tape && (!c.training || kind != kKindFp8 || !aligned16(tape))) {
+    set_error("a training cache needs an FP8 runtime created with training=1 (NVFP4 backward is not built)");
+    return WM_ERR_STATE;
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int gen = ++rt->generation;
   const int world = c.world;
   const int H = c.hidden, I = c.intermediate;
   uint8_t* S = rt->scratch;
+  uint8_t* T = static_cast<uint8_t*>(tape);
   int* status = at<int>(S, rt->sl.status);
-  RouteLocal local{at<int>(S, rt->sl.sorted_slot), at<int>(S, rt->sl.sorted_expert), at<int>(S, rt->sl.slot_pos)};
+  // With a tape, everything the backward pass needs is written into it (same layout as the BF16 tape;
+  // the row section holds the E4M3 rows followed by their scale chunks).
+  auto pick = [&](size_t tape_off, size_t scratch_off) { return tape ? T + tape_off : S + scratch_off; };
+  RouteLocal local{reinterpret_cast<int*>(pick(rt->tl.sorted_slot, rt->sl.sorted_slot)),
+                   reinterpret_cast<int*>(pick(rt->tl.sorted_expert, rt->sl.sorted_expert)),
+                   at<int>(S, rt->sl.slot_pos)};
   PlanTables tables{};
   tables.expert_total = at<int>(S, rt->sl.expert_total);
   tables.expert_before = at<int>(S, rt->sl.expert_before);
   tables.expert_base = at<int>(S, rt->sl.expert_base);
   tables.expert_pbase = at<int>(S, rt->sl.expert_pbase);
-  tables.padded_start = at<int>(S, rt->sl.padded_start);
-  tables.tile_group = at<int>(S, rt->sl.tile_group);
-  tables.num_tiles = at<int>(S, rt->sl.num_tiles);
-  tables.padded_rows = at<int>(S, rt->sl.padded_rows);
-  tables.pair_tiles = at<int>(S, rt->sl.pair_tiles);
-  tables.num_pairs = at<int>(S, rt->sl.num_pairs);
-  tables.split = at<int>(S, rt->sl.split);
-  int* origin = at<int>(S, rt->sl.origin);
-  float* prob = at<float>(S, rt->sl.prob);
-  uint8_t* xq = at<uint8_t>(S, rt->sl.xrows);
+  tables.padded_start = reinterpret_cast<int*>(pick(rt->tl.padded_start, rt->sl.padded_start));
+  tables.tile_group = reinterpret_cast<int*>(pick(rt->tl.tile_group, rt->sl.tile_group));
+  tables.num_tiles = reinterpret_cast<int*>(pick(rt->tl.num_tiles, rt->sl.num_tiles));
+  tables.padded_rows = reinterpret_cast<int*>(pick(rt->tl.padded_rows, rt->sl.padded_rows));
+  tables.pair_tiles = reinterpret_cast<int*>(pick(rt->tl.pair_tiles, rt->sl.pair_tiles));
+  tables.num_pairs = reinterpret_cast<int*>(pick(rt->tl.num_pairs, rt->sl.num_pairs));
+  tables.split = reinterpret_cast<int*>(pick(rt->tl.split, rt->sl.split));
+  int* origin = reinterpret_cast<int*>(pick(rt->tl.origin, rt->sl.origin));
+  float* prob = reinterpret_cast<float*>(pick(rt->tl.prob, rt->sl.prob));
+  uint8_t* xq = pick(rt->tl.xrows, rt->sl.xrows);
   uint8_t* uq = at<uint8_t>(S, rt->sl.u);
-  auto* abq = at<__nv_bfloat16>(S, rt->sl.abq);
-  auto* sfa_x = at<uint32_t>(S, rt->sl.sfa_x);
+  auto* abq = reinterpret_cast<__nv_bfloat16*>(pick(rt->tl.ab, rt->sl.abq));
+  auto* sfa_x = tape ? reinterpret_cast<uint32_t*>(T + rt->tl.xrows + align_up(static_cast<size_t>(rt->row_cap) * H))
+                     : at<uint32_t>(S, rt->sl.sfa_x);
   auto* sfa_u = at<uint32_t>(S, rt->sl.sfa_u);
 
   RouteShape shape{c.experts, c.top_k, world, c.rank, c.max_tokens};
@@ -845,7 +856,7 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
                   tables.expert_total};
   if (int rc = gather_q_rows(owner, c.rank, rt->e_local, c.max_tokens, c.top_k, kind, H, stage, sf_offset,
                              at<int>(rt->arena, rt->al.meta_origin), at<float>(rt->arena, rt->al.meta_prob),
-                             xq, sfa_x, origin, prob, rt->sms * 8, stream))
+                             xq, sfa_x, origin, prob, 0, rt->sms * 8, stream))
     return rc;
   if (world > 1)
     if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
@@ -878,6 +889,141 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
   }
   return combine_rows(at<__nv_bfloat16>(rt->arena, rt->al.mailbox), local.sorted_expert, tokens,
                       c.max_tokens, c.top_k, c.hidden, static_cast<__nv_bfloat16*>(y), stream);
+}
+
+// =============================================================================== FP8 backward
+// Mixed precision (stated in the header): both dgrad contractions run in blockwise FP8 against the
+// prepared transposed weights, exactly like the forward GEMMs; the two weight-gradient contractions run
+// in BF16 on the dequantised saved X and the dequantised dY rows (one E4M3 rounding each, no second
+// column-wise re-quantisation as in the reference, docs/usage.md:122-125).
+extern "C" int wm_backward_quantized(wm_runtime* rt, const void* tape, const void* dy,
+                                     const wm_quant_weights* transposed, int32_t tokens, void* dx,
+                                     float* dgates, void* dw1, void* dw2, void* stream_) {
+  if (int rc = check_ready(rt, "wm_backward_quantized")) return rc;
+  const wm_config& c = rt->cfg;
+  if (!c.training || c.reserved != 1) {
+    set_error("Backward requires an FP8 runtime prepared with training=True");
+    return WM_ERR_STATE;
+  }
+  if (tokens < 0 || tokens > c.max_tokens) {
+    set_error("Backward token count %d exceeds capacity %d", tokens, c.max_tokens);
+    return WM_ERR_CAPACITY;
+  }
+  if (!tape || !transposed || !transposed->w1 || !transposed->w1_sf || !transposed->w2 || !transposed->w2_sf ||
+      !dw1 || !dw2 || (tokens > 0 && (!dy || !dx || !dgates)) || !aligned16(tape) || !aligned16(dy) ||
+      !aligned16(dx) || !aligned16(dw1) || !aligned16(dw2)) {
+    set_error("wm_backward_quantized: null or misaligned tensor (16-byte alignment required)");
+    return WM_ERR_INVALID;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int gen = ++rt->generation;
+  const int world = c.world;
+  const int H = c.hidden, I = c.intermediate;
+  uint8_t* S = rt->scratch;
+  const uint8_t* T = static_cast<const uint8_t*>(tape);
+  auto tp = [&](size_t off) { return const_cast<uint8_t*>(T) + off; };
+  int* status = at<int>(S, rt->sl.status);
+  const int* sorted_slot = reinterpret_cast<const int*>(tp(rt->tl.sorted_slot));
+  const int* sorted_expert = reinterpret_cast<const int*>(tp(rt->tl.sorted_expert));
+  const int* padded_start = reinterpret_cast<const int*>(tp(rt->tl.padded_start));
+  const int* tile_group = reinterpret_cast<const int*>(tp(rt->tl.tile_group));
+  const int* pair_tiles = reinterpret_cast<const int*>(tp(rt->tl.pair_tiles));
+  const int* split = reinterpret_cast<const int*>(tp(rt->tl.split));
+  const int* origin = reinterpret_cast<const int*>(tp(rt->tl.origin));
+  const float* prob = reinterpret_cast<const float*>(tp(rt->tl.prob));
+  const uint8_t* xq = tp(rt->tl.xrows);
+  const auto* sfa_x = reinterpret_cast<const uint32_t*>(tp(rt->tl.xrows) + align_up(static_cast<size_t>(rt->row_cap) * H));
+  const auto* ab = reinterpret_cast<const __nv_bfloat16*>(tp(rt->tl.ab));
+  // scratch: dyq rows reuse the `u`-sized + `abq` buffers is too small for H-wide rows; the BF16 row
+  // buffers are: xrows (dequantised X), recv (dequantised dY); quantised rows: abq region (dY, dAB).
+  auto* x_bf16 = at<__nv_bfloat16>(S, rt->sl.xrows);
+  auto* dy_bf16 = at<__nv_bfloat16>(S, rt->sl.recv);
+  auto* u = at<__nv_bfloat16>(S, rt->sl.u);
+  auto* du = at<__nv_bfloat16>(S, rt->sl.du);
+  auto* dab = at<__nv_bfloat16>(S, rt->sl.dab);
+  uint8_t* qrows = at<uint8_t>(S, rt->sl.abq);          // 4*row_cap*I bytes >= row_cap*max(H, 2I)? checked below
+  auto* sfa_q = at<uint32_t>(S, rt->sl.sfa_x);
+  if (static_cast<size_t>(H) > 4ull * I) {
+    set_error("FP8 backward needs hidden <= 4 * intermediate (scratch sizing)");
+    return WM_ERR_INVALID;
+  }
+
+  PeerBytes stage{};
+  PeerFloats dgate_box{};
+  PushTarget push{};
+  for (int r = 0; r < world; ++r) {
+    stage.p[r] = rt->peer[r] + rt->al.stage;
+    dgate_box.p[r] = at<float>(rt->peer[r], rt->al.dgate_box);
+    push.mailbox[r] = at<__nv_bfloat16>(rt->peer[r], rt->al.mailbox);
+  }
+  push.origin = origin;
+  push.cap = c.max_tokens;
+  push.top_k = c.top_k;
+
+  // 1. quantise dY (1 x 128) into the staging buffer, as X was in the forward pass.
+  const size_t sf_offset = align_up(static_cast<size_t>(c.max_tokens) * H);
+  if (world > 1)
+    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, stream)) return rc;
+  uint8_t* my_stage = rt->arena + rt->al.stage;
+  if (tokens > 0)
+    if (int rc = fp8_quantize_rows(dy, tokens, H, my_stage, reinterpret_cast<float*>(my_stage + sf_offset),
+                                   rt->sms, stream))
+      return rc;
+  if (world > 1) {
+    if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
+  }
+  // 2. owner side: pull the quantised dY rows by the saved origins.
+  const DeviceRange all_rows = split_range(split, 2, kWhole);
+  OwnerRows owner{padded_start, tile_group, all_rows, nullptr};
+  if (int rc = gather_q_rows(owner, c.rank, rt->e_local, c.max_tokens, c.top_k, kKindFp8, H, stage, sf_offset,
+                             origin, nullptr, qrows, sfa_q, nullptr, nullptr, 1, rt->sms * 8, stream))
+    return rc;
+  if (world > 1)
+    if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
+  const bool many_rows = 1ll * tokens * c.top_k * world >= 1024ll * c.experts;
+  Schedule sched{split, tile_group, padded_start, rt->e_local, rt->row_cap, pair_tiles, many_rows, kWhole};
+  const long long chunk = 512;
+  const int kh = H / 128, ki2 = 2 * I / 128;
+  // 3. dU = dYq * W2 (as dYq [rows,H] x w2_t [I,H]^T); BF16 copy of dY for the weight gradient.
+  const SfLayout sfa_dy{reinterpret_cast<const uint8_t*>(sfa_q), 0, kh * chunk, chunk, chunk};
+  const SfLayout sfb_w2t{static_cast<const uint8_t*>(transposed->w2_sf), (1ll * I / 128) * kh * chunk, kh * chunk,
+                         chunk, chunk};
+  if (int rc = launch_block_scaled(kKindFp8, sched, qrows, sfa_dy, transposed->w2, sfb_w2t, du, nullptr, I, H,
+                                   1.0f, status, rt->sms, stream))
+    return rc;
+  if (int rc = fp8_dequantize_rows(all_rows, qrows, sfa_q, H, dy_bf16, rt->sms, stream)) return rc;
+  // 4. SwiGLU backward on the saved BF16 gate/up rows: U, dAB, dprob -> sources.
+  if (int rc = swiglu_backward(all_rows, ab, du, prob, origin, I, c.max_tokens, c.top_k, u, dab, dgate_box,
+                               rt->sms, stream))
+    return rc;
+  // 5. dX = q(dAB) * W1 (as dABq [rows,2I] x w1_t [H,2I]^T) -> sources' mailboxes.
+  auto* sfa_d = at<uint32_t>(S, rt->sl.sfa_u);  // sized for 2I/128 chunks per row tile
+  if (int rc = fp8_quantize_rows_chunked(all_rows, dab, 2 * I, qrows, sfa_d, rt->sms, stream)) return rc;
+  const SfLayout sfa_dab{reinterpret_cast<const uint8_t*>(sfa_d), 0, ki2 * chunk, chunk, chunk};
+  const SfLayout sfb_w1t{static_cast<const uint8_t*>(transposed->w1_sf), (1ll * H / 128) * ki2 * chunk,
+                         ki2 * chunk, chunk, chunk};
+  if (int rc = launch_block_scaled(kKindFp8, sched, qrows, sfa_dab, transposed->w1, sfb_w1t, nullptr, &push, H,
+                                   2 * I, 1.0f, status, rt->sms, stream))
+    return rc;
+  if (world > 1)
+    if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
+  // 6. weight gradients in BF16 on the dequantised saved X and dY rows (fixed row order).
+  if (int rc = fp8_dequantize_rows(all_rows, xq, sfa_x, H, x_bf16, rt->sms, stream)) return rc;
+  if (int rc = launch_kgrouped_tn(sched, dab, x_bf16, static_cast<__nv_bfloat16*>(dw1), 2 * I, H, status,
+                                  rt->sms, stream))
+    return rc;
+  if (int rc = launch_kgrouped_tn(sched, dy_bf16, u, static_cast<__nv_bfloat16*>(dw2), H, I, status, rt->sms,
+                                  stream))
+    return rc;
+  // 7. source side: ordered combine of dX, dprob back to the original slots.
+  if (world > 1)
+    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
+  if (int rc = combine_rows(at<__nv_bfloat16>(rt->arena, rt->al.mailbox), sorted_expert, tokens, c.max_tokens,
+                            c.top_k, c.hidden, static_cast<__nv_bfloat16*>(dx), stream))
+    return rc;
+  return unpermute_dgates(at<float>(rt->arena, rt->al.dgate_box), sorted_slot, sorted_expert, tokens, c.top_k,
+                          dgates, stream);
 }
 
 extern "C" int wm_fp8_pack_weight_scales(const float* scales, int32_t rows, int32_t kblocks, void* out,

@@ -182,7 +182,7 @@ class NativeRuntime:
         return tape
 
     # ------------------------------------------------------------------ quantised inference
-    def _run_quantized(self, x, routes, gates, packed):
+    def _run_quantized(self, x, routes, gates, packed, save=False):
         """packed: (w1 data, w1 scale chunks, w2 data, w2 scale chunks, x_scale, w1_scale, u_scale, w2_scale)."""
         self._require()
         caller = torch.cuda.current_stream()
@@ -192,19 +192,24 @@ class NativeRuntime:
             self.stream.wait_stream(caller)
         with torch.cuda.stream(self.stream):
             y = torch.empty_like(x)
+            blob = None
+            if save:
+                if len(self.tapes) >= self.max_saved:
+                    raise RuntimeError("Blackwell training tape capacity exhausted")
+                blob = torch.empty(self.sizes.tape_bytes, dtype=torch.uint8, device=x.device)
             w1, w1_sf, w2, w2_sf, sx, s1, su, s2 = packed
             weights = _lib.WmQuantWeights(w1=w1.data_ptr(), w1_sf=w1_sf.data_ptr(), w2=w2.data_ptr(),
                                           w2_sf=w2_sf.data_ptr(), x_scale=sx, w1_scale=s1, u_scale=su, w2_scale=s2)
             _lib.check(self.lib.wm_forward_quantized(self.handle, _lib.ptr(x), _lib.ptr(routes), _lib.ptr(gates),
                                                      ctypes.byref(weights), x.shape[0], _lib.ptr(y),
-                                                     self.stream.cuda_stream))
+                                                     _lib.ptr(blob), self.stream.cuda_stream))
             if caller != self.stream:
                 for tensor in (x, routes, gates, w1, w1_sf, w2, w2_sf):
                     tensor.record_stream(self.stream)
                 y.record_stream(caller)
         if caller != self.stream:
             caller.wait_stream(self.stream)
-        return y
+        return (y, blob) if save else y
 
     def _fp8_packed(self, weights):
         """UE8M0 scale-factor chunks of prepared FP8 weights (packed once per weight version)."""
@@ -221,14 +226,54 @@ class NativeRuntime:
             object.__setattr__(weights, "_wm_chunks", cached)
         return (weights.w1.data, cached[0], weights.w2.data, cached[1], 1.0, 1.0, 1.0, 1.0)
 
+    def _fp8_packed_transposed(self, weights):
+        """The same for W1^T / W2^T (backward operands)."""
+        cached = getattr(weights, "_wm_chunks_t", None)
+        if cached is None:
+            chunks = []
+            for w in (weights.w1_t, weights.w2_t):
+                e, n, k = w.shape
+                out = torch.empty(e * n // 128, k // 128, 128, dtype=torch.int32, device=w.data.device)
+                _lib.check(self.lib.wm_fp8_pack_weight_scales(_lib.ptr(w.scales), e * n, k // 128, _lib.ptr(out),
+                                                              torch.cuda.current_stream().cuda_stream))
+                chunks.append(out)
+            cached = tuple(chunks)
+            object.__setattr__(weights, "_wm_chunks_t", cached)
+        return weights.w1_t.data, cached[0], weights.w2_t.data, cached[1]
+
     def forward_fp8(self, x, routes, gates, weights, synchronize, retain_backward_state, fp32_wgrad):
         if retain_backward_state and self.training:
-            raise ValueError("Blockwise-FP8 backward is not built yet: call forward_fp8 with "
-                             "retain_backward_state=False or use the BF16 runtime for training")
-        y = self._run_quantized(x, routes, gates, self._fp8_packed(weights))
+            y, blob = self._run_quantized(x, routes, gates, self._fp8_packed(weights), save=True)
+            tape = Tape(y, (blob, weights, fp32_wgrad, x.shape[0], self.sizes.row_capacity * self.shape[2]))
+            self.tapes.add(tape)
+        else:
+            tape = Tape(self._run_quantized(x, routes, gates, self._fp8_packed(weights)))
         if synchronize:
             self._poll()
-        return Tape(y)
+        return tape
+
+    def _backward_fp8(self, tape, dy):
+        blob, weights, fp32_wgrad, tokens, _ = tape.state
+        if dy.dtype != torch.bfloat16 or dy.shape != tape.output.shape or dy.device != blob.device:
+            raise ValueError("Backward requires BF16 dY matching the forward output")
+        weights._validate_version(training=True)
+        w1t, w1t_sf, w2t, w2t_sf = self._fp8_packed_transposed(weights)
+        e, k = self.local_experts, self.shape[1]
+        _, _, hidden, inter = self.shape
+        dx = torch.empty_like(dy)
+        dgates = torch.empty((tokens, k), dtype=torch.float32, device=dy.device)
+        dw1 = torch.empty((e, 2 * inter, hidden), dtype=torch.bfloat16, device=dy.device)
+        dw2 = torch.empty((e, hidden, inter), dtype=torch.bfloat16, device=dy.device)
+        packed = _lib.WmQuantWeights(w1=w1t.data_ptr(), w1_sf=w1t_sf.data_ptr(), w2=w2t.data_ptr(),
+                                     w2_sf=w2t_sf.data_ptr(), x_scale=1.0, w1_scale=1.0, u_scale=1.0, w2_scale=1.0)
+        _lib.check(self.lib.wm_backward_quantized(self.handle, _lib.ptr(blob), _lib.ptr(dy), ctypes.byref(packed),
+                                                  tokens, _lib.ptr(dx), _lib.ptr(dgates), _lib.ptr(dw1),
+                                                  _lib.ptr(dw2), self.stream.cuda_stream))
+        tape.state = None
+        self.tapes.discard(tape)
+        if fp32_wgrad:
+            dw1, dw2 = dw1.float(), dw2.float()
+        return dx, dgates, dw1, dw2
 
     def inference(self, x, routes, gates, weights, x_scale, intermediate_scale):
         """NVFP4 inference with prepared weights (reference: NVFP4Runtime.inference, weftmoe/nvfp4.py:252-278)."""
@@ -251,6 +296,8 @@ class NativeRuntime:
         self._require()
         if tape not in self.tapes or tape.state is None:
             raise RuntimeError("Backward requires a live training tape from this runtime")
+        if self.precision == "fp8":
+            return self._backward_fp8(tape, dy)
         blob, w1, w2, tokens, _ = tape.state
         if dy.dtype != torch.bfloat16 or dy.shape != tape.output.shape or dy.device != blob.device:
             raise ValueError("Backward requires BF16 dY matching the forward output")
@@ -403,9 +450,8 @@ class TensorRuntime:
             raise ValueError("Unsupported runtime precision")
         if fp8_workspace and self.precision != "fp8":
             raise ValueError("Unsupported runtime precision")
-        if self.precision != "bf16" and training:
-            raise ValueError("Quantised (FP8 / NVFP4) runtimes serve inference only in this build; "
-                             "train with the BF16 runtime")
+        if self.precision == "nvfp4" and training:
+            raise ValueError("NVFP4 runtimes serve inference only in this build; train with BF16 or FP8")
         if self.precision == "nvfp4":
             from .nvfp4 import NVFP4Scales, _validate_scales
             if intermediate % 256:
@@ -509,18 +555,20 @@ class TensorRuntime:
 
     def forward_fp8(self, x, routes, gates, weights, *, synchronize=True,
                     retain_backward_state=True, weight_grad_dtype=torch.float32):
-        """Forward with BF16 input quantised online (1x128) and prepared FP8 weights.
+        """PF forward with BF16 input quantised online (1x128) and prepared FP8 weights.
 
-        Prepare weights with weftmoe_b200.fp8.prepare_fp8_weights before this call.  Backward for FP8
-        tapes is not built yet: pass retain_backward_state=False (prequantised FP8Tensor inputs are
-        not accepted either)."""
+        Prepare weights with weftmoe_b200.fp8.prepare_fp8_weights before this call (training=True when
+        a backward pass will follow).  Backward runs dU and dX in FP8 and the two weight gradients in
+        BF16 on the dequantised saved rows.  Prequantised FP8Tensor inputs are not accepted yet."""
         if weight_grad_dtype not in (torch.bfloat16, torch.float32):
             raise ValueError("weight_grad_dtype must be torch.bfloat16 or torch.float32")
         if self.precision != "fp8":
             raise ValueError("Prepare an FP8 runtime first (precision='fp8' or fp8_workspace=True)")
+        if self.training and torch.cuda.current_stream() != self.stream:
+            raise RuntimeError("Runtime must be invoked on its preparation stream")
         self._check_quantized(x, routes, gates)
         self._check_fp8_weights(weights, x.device)
-        weights.wait(training=False)
+        weights.wait(training=self.training and retain_backward_state)
         return self.native.forward_fp8(x, routes, gates, weights, synchronize, retain_backward_state,
                                        weight_grad_dtype == torch.float32)
 
@@ -612,10 +660,34 @@ class _MoE(torch.autograd.Function):
         return None, dx, None, dg, dw1, dw2
 
 
+class _MoEFP8(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, runtime, x, routes, gates, w1, w2, weights):
+        if (w1.shape != weights.w1.shape or w2.shape != weights.w2.shape
+                or w1.dtype not in (torch.bfloat16, torch.float32)
+                or w2.dtype not in (torch.bfloat16, torch.float32)
+                or w1.device != x.device or w2.device != x.device):
+            raise ValueError("FP8 autograd requires matching BF16/FP32 parameter tensors")
+        ctx.runtime = runtime
+        ctx.save_for_backward(w1, w2)
+        weights.validate_parameters(w1, w2)
+        grad_dtype = torch.bfloat16 if w1.dtype == w2.dtype == torch.bfloat16 else torch.float32
+        ctx.tape = runtime.forward_fp8(x, routes, gates, weights, weight_grad_dtype=grad_dtype)
+        return ctx.tape.output
+
+    @staticmethod
+    def backward(ctx, dy):
+        w1, w2 = ctx.saved_tensors  # detect optimizer updates before backward
+        dx, dg, dw1, dw2 = ctx.runtime.backward(ctx.tape, dy)
+        ctx.tape = None
+        ctx.runtime = None
+        return None, dx, None, dg, dw1.to(w1.dtype), dw2.to(w2.dtype), None
+
+
 def moe(runtime, x, routes, gates, w1, w2, *, fp8_weights=None):
     """Apply the fused operation, preserving router and expert autograd edges."""
     if torch.is_grad_enabled() and not runtime.training:
         raise ValueError("Autograd requires a runtime prepared with training=True")
     if fp8_weights is not None:
-        raise ValueError("Blackwell requires DP-sharded BF16 or NVFP4")
+        return _MoEFP8.apply(runtime, x, routes, gates, w1, w2, fp8_weights)
     return _MoE.apply(runtime, x, routes, gates, w1, w2)
