@@ -1,6 +1,9 @@
 // Diagnostic C entry point: run one grouped GEMM variant on caller-provided device buffers.
 // It plays the role of the reference's diagnostic fp8_gemm op (src/python/fp8.hpp:61-174):
 // a way to check a single contraction against a dense oracle without running the layer.
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <vector>
 
 #include "../../include/weftmoe_b200.h"
@@ -55,6 +58,10 @@ extern "C" int wm_debug_grouped_gemm(int kind, const void* a, const void* b, voi
   auto B = static_cast<const __nv_bfloat16*>(b);
   auto O = static_cast<__nv_bfloat16*>(out);
   int rc = 0;
+  // WM_DEBUG_GEMM_REPEAT=n launches the same GEMM n times (for timing runs of this diagnostic entry).
+  const char* repeat_env = std::getenv("WM_DEBUG_GEMM_REPEAT");
+  const int repeat = repeat_env ? std::max(1, std::atoi(repeat_env)) : 1;
+  for (int it = 0; it < repeat && rc == 0; ++it)
   switch (kind) {
     case 0: rc = launch_mgrouped_nt(s, A, B, O, nullptr, n, k_or_m, status_dev, sms, stream); break;
     case 1: rc = launch_mgrouped_nn(s, A, B, O, nullptr, n, k_or_m, status_dev, sms, stream); break;

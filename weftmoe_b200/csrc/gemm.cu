@@ -4,8 +4,11 @@
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
+#include <vector>
+#include <algorithm>
 
 #include <cstdlib>
+#include <cstring>
 
 #include "gemm.cuh"
 #include "gemm2.cuh"
@@ -136,6 +139,55 @@ static int launch(bool pair, const CUtensorMap& ta, const CUtensorMap& tb, const
   return launch_single<BLOCK_N, A_MN, B_MN, GATE_UP, K_GROUPED>(ta, tb, args, epi, sms, stream);
 }
 
+// Device timeline (diagnostics; the idea of the reference's src/cuda/profiling/device_timeline.cuh).
+// WM_DEBUG_TIMELINE=<names> makes the named one-CTA launchers (fc1, fc2, du, dx, nt, wgrad, or
+// "all") hand the kernel a stamp buffer and print it to stderr after the launch.  Printing
+// synchronises the device, so this is for investigation runs only.
+static unsigned long long* g_timeline = nullptr;
+
+static void dump_timeline(const char* what) {
+  cudaDeviceSynchronize();
+  std::vector<unsigned long long> t(kTimelineWords);
+  cudaMemcpy(t.data(), g_timeline, t.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+  cudaMemset(g_timeline, 0, t.size() * sizeof(unsigned long long));
+  unsigned long long first = ~0ull, last_start = 0, first_end = ~0ull, last_end = 0;
+  for (int c = 0; c < 1024; ++c) {
+    const unsigned long long b = t[kTimelineTileWords + 2 * c], e = t[kTimelineTileWords + 2 * c + 1];
+    if (!b) continue;
+    first = std::min(first, b); last_start = std::max(last_start, b);
+    first_end = std::min(first_end, e); last_end = std::max(last_end, e);
+  }
+  fprintf(stderr, "[%s] CTA starts within %lld ns; first CTA done at %lld ns, last at %lld ns\n", what,
+          (long long)(last_start - first), (long long)(first_end - first), (long long)(last_end - first));
+  const unsigned long long t0 = t[0];
+  fprintf(stderr, "tile | producer: start decoded first_stage last_stage | mma: start got_tmem first_full "
+                  "last_full | epilogue: acc_ready done_w3 done_w4 done_w5 (ns, CTA 0)\n");
+  for (int i = 0; i < 24 && t[i * kTimelineTileStamps]; ++i) {
+    fprintf(stderr, "%3d |", i);
+    for (int j = 0; j < kTimelineTileStamps; ++j)
+      fprintf(stderr, " %7lld%s", (long long)(t[i * kTimelineTileStamps + j] - t0), (j == 3 || j == 7) ? " |" : "");
+    fprintf(stderr, "\n");
+  }
+}
+
+struct TimelineScope {
+  const char* name;
+  bool on = false;
+  TimelineScope(const char* launcher, GemmArgs& a) : name(launcher) {
+    const char* want = std::getenv("WM_DEBUG_TIMELINE");
+    if (!want || !(std::strstr(want, launcher) || std::strstr(want, "all"))) return;
+    if (!g_timeline) {
+      if (cudaMalloc(&g_timeline, kTimelineWords * sizeof(unsigned long long)) != cudaSuccess) return;
+      cudaMemset(g_timeline, 0, kTimelineWords * sizeof(unsigned long long));
+    }
+    a.timeline = g_timeline;
+    on = true;
+  }
+  ~TimelineScope() {
+    if (on) dump_timeline(name);
+  }
+};
+
 static GemmArgs base_args(const Schedule& s, int* status) {
   GemmArgs a{};
   const DeviceRange tiles = split_range(s.split, 0, s.half);
@@ -161,6 +213,7 @@ int launch_fc1(const Schedule& s, const __nv_bfloat16* x, const __nv_bfloat16* w
   a.b_group_rows = 2 * inter;
   a.gate_up_half = inter;
   EpilogueSwiglu epi{u, ab, row_prob, inter};
+  TimelineScope timeline("fc1", a);
   return launch<256, false, false, true, false>(use_pairs(s, false), ta, tb, a, s, epi, sms, stream);
 }
 
@@ -188,6 +241,7 @@ static int launch_mgrouped(const Schedule& s, const __nv_bfloat16* a_ptr, const 
   a.n_tiles = n / bn;
   a.k_total = k;
   a.b_group_rows = B_MN ? k : n;
+  TimelineScope timeline(B_MN ? (push ? "dx" : "du") : (push ? "fc2" : "nt"), a);
   if (push) {
     if (bn == 256) {
       EpiloguePush<256> epi{};
@@ -234,6 +288,7 @@ int launch_kgrouped_tn(const Schedule& s, const __nv_bfloat16* a_ptr, const __nv
   GemmArgs a = base_args(s, status);
   a.m_tiles_per_group = m / 128;
   a.n_tiles = n / bn;
+  TimelineScope timeline("wgrad", a);
   if (bn == 256) {
     EpilogueStore<256> epi{out, (long long)m * n, n};
     return launch<256, true, true, false, true>(pair, ta, tb, a, s, epi, sms, stream);

@@ -43,7 +43,16 @@ struct GemmArgs {
   int b_group_rows;            // rows one expert occupies in B's 2-D tensor map
   int gate_up_half;            // gate/up pair: I (row offset of the "up" half inside one expert)
   int* status;                 // device status word (0 = ok)
+  // Optional device timeline (diagnostics, reference idea: src/cuda/profiling/device_timeline.cuh):
+  // CTA 0 stamps %globaltimer at a few points of every tile: [tile][role 0 producer / 1 MMA][4].
+  unsigned long long* timeline;
 };
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 template <int BLOCK_N>
 struct GemmSmem {
@@ -126,6 +135,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    if (args.timeline) args.timeline[kTimelineTileWords + 2 * blockIdx.x] = global_timer_ns();
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar + s, 1);
       mbar_init(empty_bar + s, 1);
@@ -162,12 +172,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      int local_tile = 0;
+      for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local_tile) {
+        const bool stamp = args.timeline != nullptr && blockIdx.x == 0 && local_tile < 64;
+        unsigned long long* tl = args.timeline + local_tile * kTimelineTileStamps;
+        if (stamp) tl[0] = global_timer_ns();
         const TileCoord t = decode_tile<K_GROUPED>(args, tile);
+        if (stamp) tl[1] = global_timer_ns();
         for (int kb = 0; kb < t.num_kb; ++kb) {
           ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, args.status,
                          kStatusTimeoutSmemEmpty);
           if (!ok) break;
+          if (stamp && kb == 0) tl[2] = global_timer_ns();
+          if (stamp && kb == t.num_kb - 1) tl[3] = global_timer_ns();
           uint8_t* sa = smem + stage * S::kStageBytes;
           uint8_t* sb = sa + S::kABytes;
           mbar_expect_tx(full_bar + stage, S::kStageBytes);
@@ -214,16 +231,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      int local_tile = 0;
+      for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local_tile) {
+        const bool stamp = args.timeline != nullptr && blockIdx.x == 0 && local_tile < 64;
+        unsigned long long* tl = args.timeline + local_tile * kTimelineTileStamps + 4;
+        if (stamp) tl[0] = global_timer_ns();
         const TileCoord t = decode_tile<K_GROUPED>(args, tile);
         ok = mbar_wait(tmem_empty + acc, acc_phase ^ 1, abort_flag, args.status,
                        kStatusTimeoutTmemEmpty);
         if (!ok) break;
+        if (stamp) tl[1] = global_timer_ns();
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
         for (int kb = 0; kb < t.num_kb; ++kb) {
           ok = mbar_wait(full_bar + stage, phase, abort_flag, args.status, kStatusTimeoutSmemFull);
           if (!ok) break;
+          if (stamp && kb == 0) tl[2] = global_timer_ns();
+          if (stamp && kb == t.num_kb - 1) tl[3] = global_timer_ns();
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
           const uint32_t sb = sa + S::kABytes;
@@ -247,15 +271,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+    int local_tile = 0;
+    for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local_tile) {
+      const bool stamp = args.timeline != nullptr && blockIdx.x == 0 && local_tile < 64 && lane == 0;
+      unsigned long long* tl = args.timeline + local_tile * kTimelineTileStamps + 8 + (warp - 2);
       const TileCoord t = decode_tile<K_GROUPED>(args, tile);
       ok = mbar_wait(tmem_full + acc, acc_phase, abort_flag, args.status, kStatusTimeoutTmemFull);
       if (!ok) break;
+      if (stamp && warp == 2) tl[0] = global_timer_ns();
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
       epilogue(taddr, t, q, lane, t.num_kb == 0, staging + (warp - 2) * (32 * 256));
       tc_fence_before();
       __syncwarp();
+      if (stamp && warp > 2) tl[0] = global_timer_ns();
       if (lane == 0) mbar_arrive(tmem_empty + acc);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
@@ -267,6 +296,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0 && args.timeline)
+    args.timeline[kTimelineTileWords + 2 * blockIdx.x + 1] = global_timer_ns();
 }
 
 }  // namespace wm

@@ -21,6 +21,7 @@ void count_launch(int n = 1);
 long long launch_count();
 // Kernel choice override for tests and A/B runs: -1 automatic, 0 one-CTA kernel, 1 CTA-pair kernel.
 void force_gemm_pairs(int mode);
+
 #define WM_CUDA(expr)                                                                 \
   do {                                                                                \
     cudaError_t e_ = (expr);                                                          \

@@ -15,5 +15,11 @@ enum : int {
   kStatusRowOverflow = 121,       // received rows exceed the prepared capacity
 };
 
+// Diagnostic timeline buffer of the one-CTA grouped GEMM: 64 tiles x 12 stamps of CTA 0 (4 of the
+// TMA producer, 4 of the MMA issuer, then the epilogue: accumulator ready, and the time at which
+// epilogue warps 3, 4 and 5 finished the tile), then the (start, end) time of every CTA.
+constexpr int kTimelineTileStamps = 12;
+constexpr int kTimelineTileWords = 64 * kTimelineTileStamps;
+constexpr int kTimelineWords = kTimelineTileWords + 2 * 1024;
 
 }  // namespace wm
