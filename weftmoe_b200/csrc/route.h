@@ -70,6 +70,13 @@ int route_rows(const RouteShape& s, const int* routes, const float* gates, int t
                const RouteLocal& local, const int* chunk_base, PlanTables t, RouteRows out,
                const PeerInts& meta_origin, const PeerFloats& meta_prob, cudaStream_t stream);
 
+// Source side, world > 1: a token routed to several experts of ONE owner rank crosses NVLink once.
+// For every route, meta_primary[owner][row] = the owner row of the token's first route (lowest
+// combine position) to that owner; rows whose value is their own index are pulled, the others are
+// copied from that row inside the owner.
+int route_primary(const RouteShape& s, int tokens, const RouteLocal& local, const RouteRows& rows,
+                  const PeerInts& meta_primary, cudaStream_t stream);
+
 // ------------------------------------------------------------------ transport (transport.cu)
 struct OwnerRows {
   const int* padded_start;  // [e_local + 1]
@@ -89,14 +96,20 @@ int signal_peers(const PeerInts& flag_group, int world, int slot, int generation
 // must stay free for the GEMM's CTA; NVLink needs far fewer loads in flight than HBM).
 // Owner side, forward: pull every live row's activation from its source rank's staging buffer,
 // copy origin/prob words from the meta mailbox to local arrays, zero the padding rows.
+// meta_primary (nullable = every row is pulled) names the row a duplicate is copied from;
+// primary_out (nullable) keeps it for the backward pass.  Call copy_duplicate_rows afterwards.
 int gather_rows(const OwnerRows& o, int rank, int e_local, int cap, int top_k, int hidden,
                 const PeerConstRows& stage, const int* meta_origin, const float* meta_prob,
-                __nv_bfloat16* rows_out, int* origin_out, float* prob_out, int ctas,
-                cudaStream_t stream);
-// Owner side, backward: pull dY rows by the saved origins.
-int gather_by_origin(DeviceRange rows, const int* origin, int cap, int top_k, int hidden,
-                     const PeerConstRows& stage, __nv_bfloat16* rows_out, int ctas,
+                const int* meta_primary, __nv_bfloat16* rows_out, int* origin_out, float* prob_out,
+                int* primary_out, int ctas, cudaStream_t stream);
+// Owner side, backward: pull dY rows by the saved origins (only rows with primary[r] == r when
+// `primary` is given).
+int gather_by_origin(DeviceRange rows, const int* origin, const int* primary, int cap, int top_k,
+                     int hidden, const PeerConstRows& stage, __nv_bfloat16* rows_out, int ctas,
                      cudaStream_t stream);
+// Owner side: rows_out[r] = rows_out[primary[r]] for the rows of the range with primary[r] != r.
+int copy_duplicate_rows(DeviceRange rows, const int* primary, int hidden, __nv_bfloat16* rows_out,
+                        int ctas, cudaStream_t stream);
 // Source side: out[t] = bf16( sum over combine positions j with a live route of mailbox[j][t] ).
 int combine_rows(const __nv_bfloat16* mailbox, const int* sorted_expert, int tokens, int cap,
                  int top_k, int hidden, __nv_bfloat16* out, cudaStream_t stream);

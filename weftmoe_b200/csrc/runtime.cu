@@ -12,6 +12,8 @@
 //   CONTRIB[o]  owner o finished writing its results into my mailbox
 // A source overwrites its staging buffer only after PULLED >= g-1 from every owner; an owner
 // writes a mailbox only after READY >= g, which the source sends after its previous combine.
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -31,14 +33,18 @@ enum FlagGroup { kCounts = 0, kReady = 1, kPulled = 2, kContrib = 3, kFlagGroups
 enum Stage {
   kStagePlan = 0, kStageGather, kStageFc1, kStageFc2, kStageCombine,
   kStageGatherDy, kStageDu, kStageSwigluBwd, kStageDx, kStageDw1, kStageDw2, kStageCombineDx,
-  // second halves (world > 1 only; the copies of the second half run on the side stream, untimed)
-  kStageFc1B, kStageFc2B, kStageDuB, kStageSwigluBwdB, kStageDxB,
+  // second halves (world > 1 only; the second half's rows are pulled on the side stream)
+  kStageFc1B, kStageFc2B, kStageDuB, kStageSwigluBwdB, kStageDxB, kStageGatherB, kStageGatherDyB,
+  // waits and staging copies around the kernels (they absorb the skew between ranks)
+  kStageStageIn, kStageSyncReady, kStageSyncContrib, kStageStageInBwd, kStageSyncReadyBwd, kStageSyncContribBwd,
   kStageCount
 };
 const char* const kStageNames[kStageCount] = {
     "route_plan", "gather_rows", "fc1_swiglu", "fc2_push", "combine",
     "gather_dy", "dgrad_du", "swiglu_backward", "dgrad_dx_push", "wgrad_dw1", "wgrad_dw2",
-    "combine_dx", "fc1_swiglu_b", "fc2_push_b", "dgrad_du_b", "swiglu_backward_b", "dgrad_dx_push_b"};
+    "combine_dx", "fc1_swiglu_b", "fc2_push_b", "dgrad_du_b", "swiglu_backward_b", "dgrad_dx_push_b",
+    "gather_rows_b", "gather_dy_b", "stage_in", "sync_ready", "sync_contrib", "stage_in_bwd", "sync_ready_bwd",
+    "sync_contrib_bwd"};
 constexpr int kTimingRing = 32;
 struct TimingSlot {
   cudaEvent_t start[kStageCount] = {};
@@ -59,18 +65,18 @@ struct Carver {
 };
 
 struct ArenaLayout {
-  size_t flags, counts, stage, meta_origin, meta_prob, mailbox, dgate_box, total;
+  size_t flags, counts, stage, meta_origin, meta_prob, meta_primary, mailbox, dgate_box, total;
 };
 struct ScratchLayout {
   size_t status, sorted_slot, sorted_expert, slot_pos, local_offset, dst_rank, dst_row, dst_prow,
       chunk_hist, local_count, expert_total, expert_before, expert_base, expert_pbase, padded_start,
       tile_group, num_tiles, padded_rows, pair_tiles, num_pairs, split, origin, prob, xrows, u, recv, du,
-      dab, abq, sfa_x, sfa_u, total;
+      dab, abq, sfa_x, sfa_u, primary, total;
 };
 // Training cache carved out of the caller's tape buffer.
 struct TapeLayout {
   size_t sorted_slot, sorted_expert, padded_start, tile_group, num_tiles, padded_rows, pair_tiles,
-      num_pairs, split, origin, prob, xrows, ab, total;
+      num_pairs, split, origin, prob, primary, xrows, ab, total;
 };
 
 }  // namespace
@@ -92,6 +98,7 @@ struct wm_runtime {
   // Optional per-stage device timing (CUDA events on the caller's stream).
   bool timing = false;
   int timing_slot = 0;
+  cudaEvent_t ev_trace_origin = nullptr;  // recorded at the first timed call
   std::vector<TimingSlot> slots;
   double stage_ms[kStageCount] = {};
   long long stage_calls[kStageCount] = {};
@@ -110,6 +117,7 @@ ArenaLayout arena_layout(const wm_config& c, int row_cap) {
   a.stage = k.take(2ull * c.max_tokens * c.hidden);
   a.meta_origin = k.take(sizeof(int) * row_cap);
   a.meta_prob = k.take(sizeof(float) * row_cap);
+  a.meta_primary = k.take(sizeof(int) * row_cap);
   a.mailbox = k.take(2ull * c.top_k * c.max_tokens * c.hidden);
   a.dgate_box = k.take(sizeof(float) * c.max_tokens * c.top_k);
   a.total = align_up(k.cursor, 1 << 16);  // 64 KiB multiple keeps large-page peer mappings
@@ -145,6 +153,7 @@ ScratchLayout scratch_layout(const wm_config& c, int row_cap) {
   s.split = k.take(sizeof(int) * 8);
   s.origin = k.take(sizeof(int) * row_cap);
   s.prob = k.take(sizeof(float) * row_cap);
+  s.primary = k.take(sizeof(int) * row_cap);
   s.xrows = k.take(2ull * row_cap * c.hidden);
   s.u = k.take(2ull * row_cap * c.intermediate);
   if (c.reserved != 0) {  // quantised precisions: BF16 gate/up rows and scale-factor chunks
@@ -178,6 +187,7 @@ TapeLayout tape_layout(const wm_config& c, int row_cap) {
   t.split = k.take(sizeof(int) * 8);
   t.origin = k.take(sizeof(int) * row_cap);
   t.prob = k.take(sizeof(float) * row_cap);
+  t.primary = k.take(sizeof(int) * row_cap);
   t.xrows = k.take(2ull * row_cap * c.hidden);
   t.ab = k.take(4ull * row_cap * c.intermediate);
   t.total = k.cursor;
@@ -249,6 +259,8 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 // Fold the finished measurements of one ring slot into the totals (waits for its events).
 void harvest(wm_runtime* rt, TimingSlot& slot) {
+  // WM_DEBUG_STEP_TRACE=1: print each stage's start and end relative to the first timed call.
+  static const bool trace = std::getenv("WM_DEBUG_STEP_TRACE") != nullptr;
   for (int k = 0; k < kStageCount; ++k) {
     if (!slot.used[k]) continue;
     float ms = 0.0f;
@@ -256,12 +268,19 @@ void harvest(wm_runtime* rt, TimingSlot& slot) {
         cudaEventElapsedTime(&ms, slot.start[k], slot.stop[k]) == cudaSuccess) {
       rt->stage_ms[k] += ms;
       rt->stage_calls[k] += 1;
+      float at = 0.0f;
+      if (trace && rt->ev_trace_origin &&
+          cudaEventElapsedTime(&at, rt->ev_trace_origin, slot.start[k]) == cudaSuccess)
+        fprintf(stderr, "[trace rank %d] %-20s %9.1f %9.1f us\n", rt->cfg.rank, kStageNames[k], at * 1e3,
+                (at + ms) * 1e3);
     }
     slot.used[k] = false;
   }
 }
-TimingSlot* begin_timing(wm_runtime* rt) {
+TimingSlot* begin_timing(wm_runtime* rt, cudaStream_t stream) {
   if (!rt->timing) return nullptr;
+  if (!rt->ev_trace_origin && cudaEventCreate(&rt->ev_trace_origin) == cudaSuccess)
+    cudaEventRecord(rt->ev_trace_origin, stream);
   TimingSlot& slot = rt->slots[rt->timing_slot];
   rt->timing_slot = (rt->timing_slot + 1) % kTimingRing;
   harvest(rt, slot);
@@ -416,6 +435,7 @@ extern "C" int wm_runtime_destroy(wm_runtime* rt) {
   if (rt->side) cudaStreamDestroy(rt->side);
   if (rt->ev_first_pulled) cudaEventDestroy(rt->ev_first_pulled);
   if (rt->ev_second_pulled) cudaEventDestroy(rt->ev_second_pulled);
+  if (rt->ev_trace_origin) cudaEventDestroy(rt->ev_trace_origin);
   if (rt->arena) cudaFree(rt->arena);
   if (rt->scratch) cudaFree(rt->scratch);
   rt->arena = rt->scratch = nullptr;
@@ -485,12 +505,14 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
   tables.split = tape ? at<int>(T, rt->tl.split) : at<int>(S, rt->sl.split);
   int* origin = tape ? at<int>(T, rt->tl.origin) : at<int>(S, rt->sl.origin);
   float* prob = tape ? at<float>(T, rt->tl.prob) : at<float>(S, rt->sl.prob);
+  // world > 1: row a duplicate of a token is copied from (the token crosses NVLink once per owner).
+  int* primary = world == 1 ? nullptr : (tape ? at<int>(T, rt->tl.primary) : at<int>(S, rt->sl.primary));
   auto* xrows = tape ? at<__nv_bfloat16>(T, rt->tl.xrows) : at<__nv_bfloat16>(S, rt->sl.xrows);
   auto* ab = tape ? at<__nv_bfloat16>(T, rt->tl.ab) : nullptr;
   auto* u = at<__nv_bfloat16>(S, rt->sl.u);
 
   RouteShape shape{c.experts, c.top_k, world, c.rank, c.max_tokens};
-  PeerInts counts{}, meta_origin{};
+  PeerInts counts{}, meta_origin{}, meta_primary{};
   PeerFloats meta_prob{};
   PeerConstRows stage{};
   PushTarget push{};
@@ -498,6 +520,7 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
     counts.p[r] = at<int>(rt->peer[r], rt->al.counts);
     meta_origin.p[r] = at<int>(rt->peer[r], rt->al.meta_origin);
     meta_prob.p[r] = at<float>(rt->peer[r], rt->al.meta_prob);
+    meta_primary.p[r] = at<int>(rt->peer[r], rt->al.meta_primary);
     stage.p[r] = at<__nv_bfloat16>(rt->peer[r], rt->al.stage);
     push.mailbox[r] = at<__nv_bfloat16>(rt->peer[r], rt->al.mailbox);
   }
@@ -506,16 +529,18 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
   push.top_k = c.top_k;
 
   // 1. staging buffer free?  then stage x and plan locally; counts go to every rank.
-  if (world > 1)
-    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, stream)) return rc;
-  if (world == 1)
+  TimingSlot* timing = begin_timing(rt, stream);
+  if (world == 1) {
     stage.p[0] = static_cast<const __nv_bfloat16*>(x);  // no peers: owners read x itself
-  else if (tokens > 0)
-    WM_CUDA(cudaMemcpyAsync(rt->arena + rt->al.stage, x, 2ull * tokens * c.hidden,
-                            cudaMemcpyDeviceToDevice, stream));
+  } else {
+    StageScope scope(timing, kStageStageIn, stream);
+    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, stream)) return rc;
+    if (tokens > 0)
+      WM_CUDA(cudaMemcpyAsync(rt->arena + rt->al.stage, x, 2ull * tokens * c.hidden,
+                              cudaMemcpyDeviceToDevice, stream));
+  }
   // 1b/2. local plan, count exchange, global plan (waits for all count rows), destination rows,
   //       origin/prob words to the owners.  At world > 1 the stage time includes the wait.
-  TimingSlot* timing = begin_timing(rt);
   {
     StageScope scope(timing, kStagePlan, stream);
     if (int rc = route_local(shape, routes, tokens, local, at<int>(S, rt->sl.chunk_hist),
@@ -531,8 +556,11 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
     if (int rc = route_rows(shape, routes, gates, tokens, local, at<int>(S, rt->sl.chunk_hist),
                             tables, rows, meta_origin, meta_prob, stream))
       return rc;
+    if (world > 1)
+      if (int rc = route_primary(shape, tokens, local, rows, meta_primary, stream)) return rc;
   }
   if (world > 1) {
+    StageScope scope(timing, kStageSyncReady, stream);
     if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
     if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
   }
@@ -544,10 +572,15 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
     return OwnerRows{tables.padded_start, tables.tile_group, split_range(tables.split, 2, half),
                      tables.expert_total};
   };
-  auto pull = [&](int half, cudaStream_t st) {
-    return gather_rows(owner_rows(half), c.rank, rt->e_local, c.max_tokens, c.top_k, c.hidden, stage,
-                       at<int>(rt->arena, rt->al.meta_origin), at<float>(rt->arena, rt->al.meta_prob),
-                       xrows, origin, prob, halves ? rt->sms * 2 : rt->sms * 8, st);
+  auto pull = [&](int half, cudaStream_t st) -> int {
+    const int ctas = st == rt->side ? rt->sms * 2 : rt->sms * 8;  // the side stream copies beside a GEMM
+    if (int rc = gather_rows(owner_rows(half), c.rank, rt->e_local, c.max_tokens, c.top_k, c.hidden, stage,
+                             at<int>(rt->arena, rt->al.meta_origin), at<float>(rt->arena, rt->al.meta_prob),
+                             primary ? at<int>(rt->arena, rt->al.meta_primary) : nullptr, xrows, origin,
+                             prob, primary, ctas, st))
+      return rc;
+    return primary ? copy_duplicate_rows(split_range(tables.split, 2, half), primary, c.hidden, xrows, ctas, st)
+                   : 0;
   };
   auto compute = [&](int half, int stage_fc1, int stage_fc2) -> int {
     Schedule sched{tables.split, tables.tile_group, tables.padded_start, rt->e_local, rt->row_cap,
@@ -575,7 +608,10 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
     }
     WM_CUDA(cudaEventRecord(rt->ev_first_pulled, stream));
     WM_CUDA(cudaStreamWaitEvent(rt->side, rt->ev_first_pulled, 0));
-    if (int rc = pull(kSecondHalf, rt->side)) return rc;
+    {
+      StageScope scope(timing, kStageGatherB, rt->side);
+      if (int rc = pull(kSecondHalf, rt->side)) return rc;
+    }
     WM_CUDA(cudaEventRecord(rt->ev_second_pulled, rt->side));
     if (int rc = compute(kFirstHalf, kStageFc1, kStageFc2)) return rc;
     WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_second_pulled, 0));
@@ -583,6 +619,7 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
     if (int rc = compute(kSecondHalf, kStageFc1B, kStageFc2B)) return rc;
   }
   if (world > 1) {
+    StageScope scope(timing, kStageSyncContrib, stream);
     if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
     if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
   }
@@ -645,28 +682,35 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
   push.top_k = c.top_k;
 
   // 1. stage dY where the owners can read it.
-  if (world > 1)
-    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, stream)) return rc;
-  if (world == 1)
+  TimingSlot* timing = begin_timing(rt, stream);
+  if (world == 1) {
     stage.p[0] = static_cast<const __nv_bfloat16*>(dy);  // no peers: owners read dY itself
-  else if (tokens > 0)
-    WM_CUDA(cudaMemcpyAsync(rt->arena + rt->al.stage, dy, 2ull * tokens * c.hidden,
-                            cudaMemcpyDeviceToDevice, stream));
-  if (world > 1) {
+  } else {
+    {
+      StageScope scope(timing, kStageStageInBwd, stream);
+      if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, stream)) return rc;
+      if (tokens > 0)
+        WM_CUDA(cudaMemcpyAsync(rt->arena + rt->al.stage, dy, 2ull * tokens * c.hidden,
+                                cudaMemcpyDeviceToDevice, stream));
+    }
+    StageScope scope(timing, kStageSyncReadyBwd, stream);
     if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
     if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
   }
   // 2./3. owner side: pull dY rows in the saved row order; dU = dY * W2; SwiGLU backward (U, dAB,
   //       dprob -> sources); dX = dAB * W1 -> sources.  world > 1: two halves, the second half's
   //       pull runs on the side stream beside the first half's compute and pushes.
-  TimingSlot* timing = begin_timing(rt);
   // Rows per local expert if routing were uniform: tokens * K * world / E.
   const bool many_rows = 1ll * tokens * c.top_k * world >= 1024ll * c.experts;
   const int* split = reinterpret_cast<const int*>(tp(rt->tl.split));
   const bool halves = world > 1;
-  auto pull = [&](int half, cudaStream_t st) {
-    return gather_by_origin(split_range(split, 2, half), origin, c.max_tokens, c.top_k, c.hidden, stage,
-                            recv, halves ? rt->sms * 2 : rt->sms * 8, st);
+  const int* primary = world == 1 ? nullptr : reinterpret_cast<const int*>(tp(rt->tl.primary));
+  auto pull = [&](int half, cudaStream_t st) -> int {
+    const int ctas = st == rt->side ? rt->sms * 2 : rt->sms * 8;  // the side stream copies beside a GEMM
+    if (int rc = gather_by_origin(split_range(split, 2, half), origin, primary, c.max_tokens, c.top_k,
+                                  c.hidden, stage, recv, ctas, st))
+      return rc;
+    return primary ? copy_duplicate_rows(split_range(split, 2, half), primary, c.hidden, recv, ctas, st) : 0;
   };
   auto schedule = [&](int half) {
     return Schedule{split, tile_group, padded_start, rt->e_local, rt->row_cap, pair_tiles, many_rows, half};
@@ -702,7 +746,10 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
     }
     WM_CUDA(cudaEventRecord(rt->ev_first_pulled, stream));
     WM_CUDA(cudaStreamWaitEvent(rt->side, rt->ev_first_pulled, 0));
-    if (int rc = pull(kSecondHalf, rt->side)) return rc;
+    {
+      StageScope scope(timing, kStageGatherDyB, rt->side);
+      if (int rc = pull(kSecondHalf, rt->side)) return rc;
+    }
     WM_CUDA(cudaEventRecord(rt->ev_second_pulled, rt->side));
     if (int rc = compute(kFirstHalf, kStageDu, kStageSwigluBwd, kStageDx)) return rc;
     WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_second_pulled, 0));
@@ -726,8 +773,10 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
       return rc;
   }
   // 5. source side: ordered combine of dX, dprob back to the original slots.
-  if (world > 1)
+  if (world > 1) {
+    StageScope scope(timing, kStageSyncContribBwd, stream);
     if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
+  }
   StageScope scope(timing, kStageCombineDx, stream);
   if (int rc = combine_rows(at<__nv_bfloat16>(rt->arena, rt->al.mailbox), sorted_expert, tokens,
                             c.max_tokens, c.top_k, c.hidden, static_cast<__nv_bfloat16*>(dx), stream))

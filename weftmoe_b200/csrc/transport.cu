@@ -60,8 +60,10 @@ __global__ void gather_rows_kernel(OwnerRows o, int rank, int e_local, int cap, 
                                    int hidden, PeerConstRows stage,
                                    const int* __restrict__ meta_origin,
                                    const float* __restrict__ meta_prob,
+                                   const int* __restrict__ meta_primary,
                                    __nv_bfloat16* __restrict__ rows_out,
-                                   int* __restrict__ origin_out, float* __restrict__ prob_out) {
+                                   int* __restrict__ origin_out, float* __restrict__ prob_out,
+                                   int* __restrict__ primary_out) {
   const int rows = *o.rows.end;
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -73,26 +75,32 @@ __global__ void gather_rows_kernel(OwnerRows o, int rank, int e_local, int cap, 
     uint4* dst = reinterpret_cast<uint4*>(rows_out + static_cast<size_t>(r) * hidden);
     if (live) {
       const int org = meta_origin[r];
-      const int src = org / (cap * top_k);
-      const int token = (org - src * cap * top_k) / top_k;
-      copy_row(reinterpret_cast<const uint4*>(stage.p[src] + static_cast<size_t>(token) * hidden),
-               dst, vecs, lane);
+      const int first = meta_primary ? meta_primary[r] : r;
+      if (first == r) {  // duplicates of a token inside this rank are copied locally afterwards
+        const int src = org / (cap * top_k);
+        const int token = (org - src * cap * top_k) / top_k;
+        copy_row(reinterpret_cast<const uint4*>(stage.p[src] + static_cast<size_t>(token) * hidden),
+                 dst, vecs, lane);
+      }
       if (lane == 0) {
         origin_out[r] = org;
         prob_out[r] = meta_prob[r];
+        if (primary_out) primary_out[r] = first;
       }
     } else {
       zero_row(dst, vecs, lane);
       if (lane == 0) {
         origin_out[r] = -1;
         prob_out[r] = 0.0f;
+        if (primary_out) primary_out[r] = r;
       }
     }
   }
 }
 
 __global__ void gather_by_origin_kernel(DeviceRange range, const int* __restrict__ origin,
-                                        int cap, int top_k, int hidden, PeerConstRows stage,
+                                        const int* __restrict__ primary, int cap, int top_k,
+                                        int hidden, PeerConstRows stage,
                                         __nv_bfloat16* __restrict__ rows_out) {
   const int rows = *range.end;
   const int lane = threadIdx.x & 31;
@@ -102,6 +110,7 @@ __global__ void gather_by_origin_kernel(DeviceRange range, const int* __restrict
     const int org = origin[r];
     uint4* dst = reinterpret_cast<uint4*>(rows_out + static_cast<size_t>(r) * hidden);
     if (org >= 0) {
+      if (primary != nullptr && primary[r] != r) continue;  // copied locally afterwards
       const int src = org / (cap * top_k);
       const int token = (org - src * cap * top_k) / top_k;
       copy_row(reinterpret_cast<const uint4*>(stage.p[src] + static_cast<size_t>(token) * hidden),
@@ -112,22 +121,43 @@ __global__ void gather_by_origin_kernel(DeviceRange range, const int* __restrict
   }
 }
 
+__global__ void copy_duplicate_rows_kernel(DeviceRange range, const int* __restrict__ primary,
+                                           int hidden, __nv_bfloat16* __restrict__ rows_out) {
+  const int rows = *range.end;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int vecs = hidden / 8;
+  for (int r = *range.begin + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += warps) {
+    const int first = primary[r];
+    if (first == r || first < 0) continue;
+    copy_row(reinterpret_cast<const uint4*>(rows_out + static_cast<size_t>(first) * hidden),
+             reinterpret_cast<uint4*>(rows_out + static_cast<size_t>(r) * hidden), vecs, lane);
+  }
+}
+
 int gather_rows(const OwnerRows& o, int rank, int e_local, int cap, int top_k, int hidden,
                 const PeerConstRows& stage, const int* meta_origin, const float* meta_prob,
-                __nv_bfloat16* rows_out, int* origin_out, float* prob_out, int ctas,
-                cudaStream_t stream) {
+                const int* meta_primary, __nv_bfloat16* rows_out, int* origin_out, float* prob_out,
+                int* primary_out, int ctas, cudaStream_t stream) {
   gather_rows_kernel<<<ctas, 256, 0, stream>>>(o, rank, e_local, cap, top_k, hidden, stage,
-                                                  meta_origin, meta_prob, rows_out, origin_out,
-                                                  prob_out);
+                                                  meta_origin, meta_prob, meta_primary, rows_out,
+                                                  origin_out, prob_out, primary_out);
   count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
 }
-int gather_by_origin(DeviceRange rows, const int* origin, int cap, int top_k, int hidden,
-                     const PeerConstRows& stage, __nv_bfloat16* rows_out, int ctas,
+int gather_by_origin(DeviceRange rows, const int* origin, const int* primary, int cap, int top_k,
+                     int hidden, const PeerConstRows& stage, __nv_bfloat16* rows_out, int ctas,
                      cudaStream_t stream) {
-  gather_by_origin_kernel<<<ctas, 256, 0, stream>>>(rows, origin, cap, top_k, hidden, stage,
+  gather_by_origin_kernel<<<ctas, 256, 0, stream>>>(rows, origin, primary, cap, top_k, hidden, stage,
                                                    rows_out);
+  count_launch();
+  WM_CUDA(cudaGetLastError());
+  return 0;
+}
+int copy_duplicate_rows(DeviceRange rows, const int* primary, int hidden, __nv_bfloat16* rows_out,
+                        int ctas, cudaStream_t stream) {
+  copy_duplicate_rows_kernel<<<ctas, 256, 0, stream>>>(rows, primary, hidden, rows_out);
   count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
