@@ -151,15 +151,19 @@ static void dump_timeline(const char* what) {
   cudaMemcpy(t.data(), g_timeline, t.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
   cudaMemset(g_timeline, 0, t.size() * sizeof(unsigned long long));
   unsigned long long first = ~0ull, last_start = 0, first_end = ~0ull, last_end = 0;
+  int slowest = 0, fastest = 0;
   for (int c = 0; c < 1024; ++c) {
     const unsigned long long b = t[kTimelineTileWords + 2 * c], e = t[kTimelineTileWords + 2 * c + 1];
     if (!b) continue;
     first = std::min(first, b); last_start = std::max(last_start, b);
-    first_end = std::min(first_end, e); last_end = std::max(last_end, e);
+    if (e < first_end) { first_end = e; fastest = c; }
+    if (e > last_end) { last_end = e; slowest = c; }
   }
-  fprintf(stderr, "[%s] CTA starts within %lld ns; first CTA done at %lld ns, last at %lld ns\n", what,
-          (long long)(last_start - first), (long long)(first_end - first), (long long)(last_end - first));
+  fprintf(stderr, "[%s] CTA starts within %lld ns; first CTA (%d) done at %lld ns, last (%d) at %lld ns\n", what,
+          (long long)(last_start - first), fastest, (long long)(first_end - first), slowest,
+          (long long)(last_end - first));
   const unsigned long long t0 = t[0];
+  fprintf(stderr, "stamps of the CTA chosen with WM_DEBUG_TIMELINE_CTA (default 0)\n");
   fprintf(stderr, "tile | producer: start decoded first_stage last_stage | mma: start got_tmem first_full "
                   "last_full | epilogue: acc_ready done_w3 done_w4 done_w5 (ns, CTA 0)\n");
   for (int i = 0; i < 24 && t[i * kTimelineTileStamps]; ++i) {
@@ -181,6 +185,7 @@ struct TimelineScope {
       cudaMemset(g_timeline, 0, kTimelineWords * sizeof(unsigned long long));
     }
     a.timeline = g_timeline;
+    if (const char* cta = std::getenv("WM_DEBUG_TIMELINE_CTA")) a.timeline_cta = std::atoi(cta);
     on = true;
   }
   ~TimelineScope() {

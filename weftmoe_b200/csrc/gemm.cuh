@@ -46,6 +46,7 @@ struct GemmArgs {
   // Optional device timeline (diagnostics, reference idea: src/cuda/profiling/device_timeline.cuh):
   // CTA 0 stamps %globaltimer at a few points of every tile: [tile][role 0 producer / 1 MMA][4].
   unsigned long long* timeline;
+  int timeline_cta;            // the CTA whose per-tile stamps are kept
 };
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -174,7 +175,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       bool ok = true;
       int local_tile = 0;
       for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local_tile) {
-        const bool stamp = args.timeline != nullptr && blockIdx.x == 0 && local_tile < 64;
+        const bool stamp = args.timeline != nullptr && blockIdx.x == args.timeline_cta && local_tile < 64;
         unsigned long long* tl = args.timeline + local_tile * kTimelineTileStamps;
         if (stamp) tl[0] = global_timer_ns();
         const TileCoord t = decode_tile<K_GROUPED>(args, tile);
@@ -233,7 +234,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       bool ok = true;
       int local_tile = 0;
       for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local_tile) {
-        const bool stamp = args.timeline != nullptr && blockIdx.x == 0 && local_tile < 64;
+        const bool stamp = args.timeline != nullptr && blockIdx.x == args.timeline_cta && local_tile < 64;
         unsigned long long* tl = args.timeline + local_tile * kTimelineTileStamps + 4;
         if (stamp) tl[0] = global_timer_ns();
         const TileCoord t = decode_tile<K_GROUPED>(args, tile);
@@ -273,7 +274,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     bool ok = true;
     int local_tile = 0;
     for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local_tile) {
-      const bool stamp = args.timeline != nullptr && blockIdx.x == 0 && local_tile < 64 && lane == 0;
+      const bool stamp = args.timeline != nullptr && blockIdx.x == args.timeline_cta && local_tile < 64 && lane == 0;
       unsigned long long* tl = args.timeline + local_tile * kTimelineTileStamps + 8 + (warp - 2);
       const TileCoord t = decode_tile<K_GROUPED>(args, tile);
       ok = mbar_wait(tmem_full + acc, acc_phase, abort_flag, args.status, kStatusTimeoutTmemFull);
