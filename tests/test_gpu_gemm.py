@@ -97,3 +97,35 @@ def test_row_bits_do_not_depend_on_position_or_neighbours():
     out3 = torch.empty(128, n, device=dev, dtype=torch.bfloat16)
     grouped_gemm(0, a[:128].contiguous(), b, out3, [128], n, k)
     assert torch.equal(out[:128].view(torch.int16), out3.view(torch.int16))
+
+
+def test_device_timeline_diagnostic_prints_the_stamps(kernel_choice):
+    """WM_DEBUG_TIMELINE=<launcher> makes the one-CTA kernel stamp %globaltimer per tile and the
+    launcher print them; the GEMM result is unaffected.  Run in a child process to read its stderr."""
+    if kernel_choice:
+        pytest.skip("the timeline covers the one-CTA kernel")
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import torch\n"
+        "from tests.gpu_util import grouped_gemm\n"
+        "from weftmoe_b200 import _lib\n"
+        "_lib.load().wm_debug_force_gemm_pairs(0)\n"
+        "a = torch.randn(256, 256, device='cuda').bfloat16()\n"
+        "b = torch.randn(1, 512, 256, device='cuda').bfloat16()\n"
+        "out = torch.empty(256, 512, device='cuda', dtype=torch.bfloat16)\n"
+        "grouped_gemm(0, a, b, out, [256], 512, 256)\n"
+        "ref = a.float() @ b[0].float().T\n"
+        "print('rel', ((out.float() - ref).norm() / ref.norm()).item())\n")
+    env = dict(os.environ, WM_DEBUG_TIMELINE="nt", WM_DEBUG_TIMELINE_CTA="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    run = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True,
+                         timeout=300)
+    assert run.returncode == 0, run.stderr
+    assert float(run.stdout.split("rel")[1]) < TOL
+    assert "[nt] CTA starts within" in run.stderr
+    rows = [l for l in run.stderr.splitlines() if l.strip().startswith("0 |")]
+    assert rows, run.stderr   # CTA 1 handled one tile (4 tiles over the grid) and stamped it
+    stamps = [int(v) for v in rows[0].replace("|", " ").split()[1:]]
+    assert len(stamps) == 12 and stamps[3] >= stamps[2] >= 0   # producer: last stage after first stage
