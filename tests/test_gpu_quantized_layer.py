@@ -135,3 +135,20 @@ def test_fp8_training_forward_backward_meets_the_reference_acceptance(cfg):
     assert w1.grad.dtype == torch.float32 and global_diff(x.grad, ref[1]) < 5e-3
     assert global_diff(w2.grad[live[0]], ref[4][live[0]]) < 5e-3
     rt.close()
+
+
+def test_fp8_weight_gradients_in_fp8_meet_the_same_acceptance():
+    """WM_FP8_WGRAD=1 switches the two weight-gradient contractions to the reference's recipe (operands
+    re-quantised 1 x 128 along the rows, blockwise-FP8 K-grouped GEMM; docs/usage.md:122-125).  The
+    library reads the switch once, so the acceptance test above is re-run in a child process."""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("WM_FP8_WGRAD") == "1":
+        pytest.skip("already running with FP8 weight gradients")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    run = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "tests/test_gpu_quantized_layer.py", "-k",
+                          "fp8_training_forward_backward"], cwd=root, env=dict(os.environ, WM_FP8_WGRAD="1"),
+                         capture_output=True, text=True, timeout=900)
+    assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-2000:]
+    assert "2 passed" in run.stdout

@@ -203,6 +203,7 @@ struct EpilogueStoreScaled {
   __nv_bfloat16* out;
   int ld;
   float alpha;
+  long long group_stride;  // elements between experts' outputs (K-grouped), 0 for M-grouped
 
   __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane, bool,
                                              uint8_t* stage) const {
@@ -215,7 +216,7 @@ struct EpilogueStoreScaled {
       stage_put32(stage, lane, c, w);
     }
     __syncwarp();
-    __nv_bfloat16* block = out + row0 * ld + t.n_tile * BLOCK_N;
+    __nv_bfloat16* block = out + group_stride * t.group + row0 * ld + t.n_tile * BLOCK_N;
     const int ldl = ld;
     stage_flush(stage, lane, [block, ldl](int r) { return block + static_cast<long long>(r) * ldl; });
     __syncwarp();

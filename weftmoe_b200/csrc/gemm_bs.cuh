@@ -45,7 +45,11 @@ struct BsArgs {
   SfLayout sfb;    // group = expert, tile = 128-row tile of that expert's B
 };
 
-template <int KIND, class Epilogue>
+// K_GROUPED (weight gradients): out[e] = A[:, rows_e]  x  B[:, rows_e]^T with both operands stored
+// K-major over the rank's padded rows (A [M, row_capacity], B [N, row_capacity]); expert e reduces over
+// its own row segment [row0_e, row0_e + rows_e), rows_e a multiple of 128.  An NVFP4 stage spans 256
+// rows: when only 128 remain, half of the stage's MMAs are issued.
+template <int KIND, bool K_GROUPED, class Epilogue>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const BsArgs bs, const Epilogue epilogue) {
@@ -89,9 +93,18 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  const int first_tile = __ldg(args.tile_begin) * args.n_tiles;
-  const int total_tiles = __ldg(args.tile_end) * args.n_tiles;
-  const int k_stages = (args.k_total + C::kElemsPerStage - 1) / C::kElemsPerStage;
+  int first_tile = 0, total_tiles;
+  if constexpr (K_GROUPED) {
+    total_tiles = args.groups * args.m_tiles_per_group * args.n_tiles;
+  } else {
+    first_tile = __ldg(args.tile_begin) * args.n_tiles;
+    total_tiles = __ldg(args.tile_end) * args.n_tiles;
+  }
+  // Stages and 64-element MMA groups of a tile's K loop, and the element its K range starts at.
+  constexpr int kElemsPerMma = C::kElemsPerStage / 4;
+  auto k_groups_of = [&](const TileCoord& t) {
+    return K_GROUPED ? t.num_kb * kBlockK / kElemsPerMma : (args.k_total + kElemsPerMma - 1) / kElemsPerMma;
+  };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -99,9 +112,16 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const TileCoord t = decode_tile<false>(args, tile);
-        const uint8_t* sfa = bs.sfa.base + t.m_tile * bs.sfa.tile_stride;
-        const uint8_t* sfb = bs.sfb.base + t.group * bs.sfb.group_stride + t.n_tile * bs.sfb.tile_stride;
+        const TileCoord t = decode_tile<K_GROUPED>(args, tile);
+        const int k_stages = (k_groups_of(t) + 3) / 4;
+        // K-grouped: the K range starts at the expert's first row; its scale chunks follow suit.
+        const int k0 = K_GROUPED ? t.row0 : 0;
+        const int k0_bytes = KIND == kKindFp8 ? k0 : k0 / 2;
+        const long long sf_k0 = static_cast<long long>(k0 / (C::kElemsPerStage / C::kSfChunks)) * 512;
+        const uint8_t* sfa = bs.sfa.base + t.m_tile * bs.sfa.tile_stride + (K_GROUPED ? sf_k0 : 0);
+        const uint8_t* sfb = bs.sfb.base + (K_GROUPED ? sf_k0 : t.group * bs.sfb.group_stride) +
+                             t.n_tile * bs.sfb.tile_stride;
+        const int b_row = K_GROUPED ? t.n_tile * C::kBlockN : t.group * args.b_group_rows + t.n_tile * C::kBlockN;
         for (int kb = 0; kb < k_stages; ++kb) {
           ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, args.status, kStatusTimeoutSmemEmpty);
           if (!ok) break;
@@ -110,9 +130,8 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           uint8_t* ssfa = sb + C::kBBytes;
           uint8_t* ssfb = ssfa + C::kSfBytes;
           mbar_expect_tx(full_bar + stage, C::kStageBytes);
-          tma_load_2d(sa, &tmap_a, full_bar + stage, kb * C::kRowBytes, t.m_tile * kBlockM);
-          tma_load_2d(sb, &tmap_b, full_bar + stage, kb * C::kRowBytes,
-                      t.group * args.b_group_rows + t.n_tile * C::kBlockN);
+          tma_load_2d(sa, &tmap_a, full_bar + stage, k0_bytes + kb * C::kRowBytes, t.m_tile * kBlockM);
+          tma_load_2d(sb, &tmap_b, full_bar + stage, k0_bytes + kb * C::kRowBytes, b_row);
 #pragma unroll
           for (int c = 0; c < C::kSfChunks; ++c) {
             bulk_load_1d(ssfa + c * 512, sfa + kb * bs.sfa.kstage_stride + c * bs.sfa.chunk_stride, 512,
@@ -132,6 +151,14 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        int k_groups = 0;
+        if constexpr (K_GROUPED) {
+          const TileCoord t = decode_tile<true>(args, tile);
+          k_groups = k_groups_of(t);
+        } else {
+          k_groups = (args.k_total + kElemsPerMma - 1) / kElemsPerMma;
+        }
+        const int k_stages = (k_groups + 3) / 4;
         ok = mbar_wait(tmem_empty + acc, acc_phase ^ 1, abort_flag, args.status, kStatusTimeoutTmemEmpty);
         if (!ok) break;
         tc_fence_after();
@@ -151,8 +178,10 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
           const uint64_t da = umma_desc_sw128(sa, 0, 1024);
           const uint64_t db = umma_desc_sw128(sb, 0, 1024);
+          const int mmas = K_GROUPED ? min(4, k_groups - 4 * kb) : 4;  // a half-filled last NVFP4 stage
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
+            if (K_GROUPED && k >= mmas) break;
             const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
             if constexpr (KIND == kKindFp8) {
               // one chunk per stage: byte k of each row's word is the scale of 32-element group k
@@ -180,7 +209,8 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const TileCoord t = decode_tile<false>(args, tile);
+      const TileCoord t = decode_tile<K_GROUPED>(args, tile);
+      const int k_stages = (k_groups_of(t) + 3) / 4;
       ok = mbar_wait(tmem_full + acc, acc_phase, abort_flag, args.status, kStatusTimeoutTmemFull);
       if (!ok) break;
       tc_fence_after();
@@ -243,10 +273,10 @@ struct EpilogueBounded {
 
 // Host launcher (needs kernels.h for WM_CUDA / count_launch; include it before this header).
 #ifdef WM_CUDA
-template <int KIND, class Epi>
+template <int KIND, bool K_GROUPED = false, class Epi>
 int launch_bs(const CUtensorMap& ta, const CUtensorMap& tb, const BsArgs& args, const Epi& epi, int sms,
               cudaStream_t stream) {
-  auto kernel = gemm_bs_kernel<KIND, Epi>;
+  auto kernel = gemm_bs_kernel<KIND, K_GROUPED, Epi>;
   constexpr int smem = BsConfig<KIND>::kTotal;
   static bool configured = false;
   if (!configured) {

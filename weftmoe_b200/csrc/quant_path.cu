@@ -286,8 +286,88 @@ int launch_bs_grouped(const Schedule& s, const void* a, const SfLayout& sfa, con
     epi.alpha = alpha;
     return launch_bs<KIND>(ta, tb, args, epi, sms, stream);
   }
-  EpilogueStoreScaled<128> epi{out, n, alpha};
+  EpilogueStoreScaled<128> epi{out, n, alpha, 0};
   return launch_bs<KIND>(ta, tb, args, epi, sms, stream);
+}
+
+// Weight gradient: out[e] [m, n] = alpha * A[:, rows_e] * B[:, rows_e]^T, operands stored K-major
+// over the padded rows (A [m, row_capacity], B [n, row_capacity] elements).
+template <int KIND>
+int launch_bs_kgrouped(const Schedule& s, const void* a, const SfLayout& sfa, const void* b, const SfLayout& sfb,
+                       __nv_bfloat16* out, int m, int n, float alpha, int* status, int sms, cudaStream_t stream) {
+  const int kbytes = KIND == kKindFp8 ? s.row_capacity : s.row_capacity / 2;
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap_2d(&ta, a, 1, kbytes, m, kbytes, 128, 128)) return rc;
+  if (int rc = make_tmap_2d(&tb, b, 1, kbytes, n, kbytes, 128, 128)) return rc;
+  BsArgs args{};
+  args.base.group_row_start = s.group_row_start;
+  args.base.groups = s.groups;
+  args.base.m_tiles_per_group = m / 128;
+  args.base.n_tiles = n / 128;
+  args.base.status = status;
+  args.sfa = sfa;
+  args.sfb = sfb;
+  EpilogueStoreScaled<128> epi{out, n, alpha, static_cast<long long>(m) * n};
+  return launch_bs<KIND, true>(ta, tb, args, epi, sms, stream);
+}
+
+// BF16 rows [rows, cols] -> E4M3 of the TRANSPOSE, qt [cols][row_capacity], quantised 1 x 128 along the
+// rows (the reduction axis of a weight gradient; reference: column re-quantisation, docs/usage.md:122-125),
+// with the UE8M0 scale words in the chunked layout of a K-major operand whose rows are the columns of x:
+// chunk (cols/128 tile, 128-row block).  One warp per (128-row block, 64 columns): two columns per lane,
+// first the column maxima, then sixteen rows at a time.
+__global__ void fp8_quantize_cols_chunked_kernel(DeviceRange range, const __nv_bfloat16* __restrict__ x,
+                                                 int cols, int row_capacity, uint8_t* __restrict__ qt,
+                                                 uint32_t* __restrict__ sf_out) {
+  const int row0 = *range.begin, rows = *range.end;
+  const int rblocks = (rows - row0) >> 7, cgroups = cols / 64, rblocks_total = row_capacity >> 7;
+  const long long units = static_cast<long long>(rblocks) * cgroups;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (long long unit = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; unit < units;
+       unit += warps) {
+    const int rb = static_cast<int>(unit / cgroups), cg = static_cast<int>(unit % cgroups);
+    const int r_first = row0 + rb * 128, c = cg * 64 + lane * 2;
+    const unsigned* src = reinterpret_cast<const unsigned*>(x + static_cast<size_t>(r_first) * cols + c);
+    const size_t pitch = static_cast<size_t>(cols) / 2;  // in 32-bit words
+    float m0 = 0.0f, m1 = 0.0f;
+    bool bad0 = false, bad1 = false;  // a non-finite value poisons only its own column's block
+#pragma unroll 8
+    for (int r = 0; r < 128; ++r) {
+      const unsigned w = src[r * pitch];
+      const float a = __uint_as_float(w << 16), b = __uint_as_float(w & 0xffff0000u);
+      m0 = fmaxf(m0, fabsf(a));
+      m1 = fmaxf(m1, fabsf(b));
+      bad0 |= !isfinite(a);
+      bad1 |= !isfinite(b);
+    }
+    const float s0 = fp8_block_scale(m0, bad0), s1 = fp8_block_scale(m1, bad1);
+    const float i0 = s0 != s0 ? s0 : __uint_as_float(0x7f000000u - __float_as_uint(s0));
+    const float i1 = s1 != s1 ? s1 : __uint_as_float(0x7f000000u - __float_as_uint(s1));
+    uint8_t* dst0 = qt + static_cast<size_t>(c) * row_capacity + r_first;
+    uint8_t* dst1 = dst0 + row_capacity;
+#pragma unroll 1
+    for (int g = 0; g < 8; ++g) {
+      float a[16], b[16];
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        const unsigned w = src[(g * 16 + r) * pitch];
+        a[r] = __uint_as_float(w << 16) * i0;
+        b[r] = __uint_as_float(w & 0xffff0000u) * i1;
+      }
+      uint4 oa, ob;
+      oa.x = pack4_e4m3(a[0], a[1], a[2], a[3]);   oa.y = pack4_e4m3(a[4], a[5], a[6], a[7]);
+      oa.z = pack4_e4m3(a[8], a[9], a[10], a[11]); oa.w = pack4_e4m3(a[12], a[13], a[14], a[15]);
+      ob.x = pack4_e4m3(b[0], b[1], b[2], b[3]);   ob.y = pack4_e4m3(b[4], b[5], b[6], b[7]);
+      ob.z = pack4_e4m3(b[8], b[9], b[10], b[11]); ob.w = pack4_e4m3(b[12], b[13], b[14], b[15]);
+      *reinterpret_cast<uint4*>(dst0 + g * 16) = oa;
+      *reinterpret_cast<uint4*>(dst1 + g * 16) = ob;
+    }
+    const int kb = (r_first >> 7);
+    uint32_t* chunk = sf_out + (static_cast<size_t>(c >> 7) * rblocks_total + kb) * 128;
+    chunk[chunk_word(c)] = ((__float_as_uint(s0) >> 23) & 0xffu) * 0x01010101u;
+    chunk[chunk_word(c + 1)] = ((__float_as_uint(s1) >> 23) & 0xffu) * 0x01010101u;
+  }
 }
 
 }  // namespace
@@ -328,6 +408,27 @@ int fp8_dequantize_rows(DeviceRange rows, const uint8_t* q, const uint32_t* sfa,
   WM_CUDA(cudaGetLastError());
   count_launch();
   return 0;
+}
+
+int fp8_quantize_cols_chunked(DeviceRange rows, const __nv_bfloat16* x, int cols, int row_capacity,
+                              uint8_t* qt, uint32_t* sf_out, int sms, cudaStream_t stream) {
+  fp8_quantize_cols_chunked_kernel<<<sms * 8, 256, 0, stream>>>(rows, x, cols, row_capacity, qt, sf_out);
+  WM_CUDA(cudaGetLastError());
+  count_launch();
+  return 0;
+}
+
+int launch_block_scaled_kgrouped(int kind, const Schedule& s, const void* a, const SfLayout& sfa, const void* b,
+                                 const SfLayout& sfb, __nv_bfloat16* out, int m, int n, float alpha,
+                                 int* status, int sms, cudaStream_t stream) {
+  if (m % 128 || n % 128 || s.row_capacity % (kind == kKindFp8 ? 128 : 256)) {
+    set_error("block-scaled weight gradient needs M %% 128 == 0, N %% 128 == 0 and a row capacity that is a "
+              "multiple of 128 (FP8) or 256 (NVFP4) (M=%d, N=%d, rows=%d)", m, n, s.row_capacity);
+    return 2;
+  }
+  return kind == kKindFp8
+             ? launch_bs_kgrouped<kKindFp8>(s, a, sfa, b, sfb, out, m, n, alpha, status, sms, stream)
+             : launch_bs_kgrouped<kKindNvfp4>(s, a, sfa, b, sfb, out, m, n, alpha, status, sms, stream);
 }
 
 int launch_block_scaled(int kind, const Schedule& s, const void* a, const SfLayout& sfa, const void* b,

@@ -37,6 +37,14 @@ int fp8_quantize_rows_chunked(DeviceRange rows, const __nv_bfloat16* x, int cols
                               uint32_t* sfa_out, int sms, cudaStream_t stream);
 int fp8_dequantize_rows(DeviceRange rows, const uint8_t* q, const uint32_t* sfa, int cols,
                         __nv_bfloat16* out, int sms, cudaStream_t stream);
+// BF16 rows -> E4M3 of the transpose [cols][row_capacity], 1 x 128 along the rows, chunked UE8M0 scales
+// (chunk = (cols / 128 tile, 128-row block)): the operand layout of a block-scaled weight gradient.
+int fp8_quantize_cols_chunked(DeviceRange rows, const __nv_bfloat16* x, int cols, int row_capacity,
+                              uint8_t* qt, uint32_t* sf_out, int sms, cudaStream_t stream);
+// out[e] [m, n] = alpha * A[:, rows of e] * B[:, rows of e]^T, operands K-major over the padded rows.
+int launch_block_scaled_kgrouped(int kind, const Schedule& s, const void* a, const SfLayout& sfa, const void* b,
+                                 const SfLayout& sfb, __nv_bfloat16* out, int m, int n, float alpha,
+                                 int* status, int sms, cudaStream_t stream);
 int swiglu_quantize(DeviceRange rows, const __nv_bfloat16* ab, const float* prob, int inter, int kind,
                     float layer_scale, uint8_t* uq, uint32_t* sfa_out, int sms, cudaStream_t stream);
 // out[rows, n] = alpha * A[rows, k] * B[e][n, k]^T with quantised operands; `push` != nullptr sends the

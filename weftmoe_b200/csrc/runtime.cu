@@ -71,7 +71,7 @@ struct ScratchLayout {
   size_t status, sorted_slot, sorted_expert, slot_pos, local_offset, dst_rank, dst_row, dst_prow,
       chunk_hist, local_count, expert_total, expert_before, expert_base, expert_pbase, padded_start,
       tile_group, num_tiles, padded_rows, pair_tiles, num_pairs, split, origin, prob, xrows, u, recv, du,
-      dab, abq, sfa_x, sfa_u, primary, total;
+      dab, abq, sfa_x, sfa_u, primary, wq_a, wq_b, wsf_a, wsf_b, total;
 };
 // Training cache carved out of the caller's tape buffer.
 struct TapeLayout {
@@ -166,6 +166,15 @@ ScratchLayout scratch_layout(const wm_config& c, int row_cap) {
     s.recv = k.take(2ull * row_cap * c.hidden);
     s.du = k.take(2ull * row_cap * c.intermediate);
     s.dab = k.take(4ull * row_cap * c.intermediate);
+  }
+  if (c.training && c.reserved == 1) {
+    // FP8 weight gradients: both operands of each contraction, re-quantised along the rows and stored
+    // transposed ([features][row_cap] bytes), plus their scale chunks (+4 chunks of slack).
+    const size_t wide = c.hidden > 2 * c.intermediate ? c.hidden : 2 * c.intermediate;
+    s.wq_a = k.take(static_cast<size_t>(row_cap) * wide);
+    s.wq_b = k.take(static_cast<size_t>(row_cap) * c.hidden);
+    s.wsf_a = k.take((wide / 128) * (row_cap / 128) * 512 + 4 * 512);
+    s.wsf_b = k.take((static_cast<size_t>(c.hidden) / 128) * (row_cap / 128) * 512 + 4 * 512);
   }
   s.total = k.cursor;
   return s;
@@ -1057,14 +1066,40 @@ extern "C" int wm_backward_quantized(wm_runtime* rt, const void* tape, const voi
     return rc;
   if (world > 1)
     if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
-  // 6. weight gradients in BF16 on the dequantised saved X and dY rows (fixed row order).
+  // 6. weight gradients (fixed row order).  Default: BF16 on the dequantised saved X and dY rows.
+  //    WM_FP8_WGRAD=1: the reference's recipe (docs/usage.md:122-125) - every operand re-quantised
+  //    1 x 128 along the rows and the contraction run in blockwise FP8.
   if (int rc = fp8_dequantize_rows(all_rows, xq, sfa_x, H, x_bf16, rt->sms, stream)) return rc;
-  if (int rc = launch_kgrouped_tn(sched, dab, x_bf16, static_cast<__nv_bfloat16*>(dw1), 2 * I, H, status,
-                                  rt->sms, stream))
-    return rc;
-  if (int rc = launch_kgrouped_tn(sched, dy_bf16, u, static_cast<__nv_bfloat16*>(dw2), H, I, status, rt->sms,
-                                  stream))
-    return rc;
+  static const bool fp8_wgrad = [] {
+    const char* v = std::getenv("WM_FP8_WGRAD");
+    return v && v[0] == '1';
+  }();
+  if (fp8_wgrad) {
+    uint8_t* qa = at<uint8_t>(S, rt->sl.wq_a);
+    uint8_t* qb = at<uint8_t>(S, rt->sl.wq_b);
+    auto* sa = at<uint32_t>(S, rt->sl.wsf_a);
+    auto* sb = at<uint32_t>(S, rt->sl.wsf_b);
+    const long long per_tile = static_cast<long long>(rt->row_cap / 128) * chunk;
+    const SfLayout la{reinterpret_cast<const uint8_t*>(sa), 0, per_tile, chunk, chunk};
+    const SfLayout lb{reinterpret_cast<const uint8_t*>(sb), 0, per_tile, chunk, chunk};
+    if (int rc = fp8_quantize_cols_chunked(all_rows, dab, 2 * I, rt->row_cap, qa, sa, rt->sms, stream)) return rc;
+    if (int rc = fp8_quantize_cols_chunked(all_rows, x_bf16, H, rt->row_cap, qb, sb, rt->sms, stream)) return rc;
+    if (int rc = launch_block_scaled_kgrouped(kKindFp8, sched, qa, la, qb, lb, static_cast<__nv_bfloat16*>(dw1),
+                                              2 * I, H, 1.0f, status, rt->sms, stream))
+      return rc;
+    if (int rc = fp8_quantize_cols_chunked(all_rows, dy_bf16, H, rt->row_cap, qa, sa, rt->sms, stream)) return rc;
+    if (int rc = fp8_quantize_cols_chunked(all_rows, u, I, rt->row_cap, qb, sb, rt->sms, stream)) return rc;
+    if (int rc = launch_block_scaled_kgrouped(kKindFp8, sched, qa, la, qb, lb, static_cast<__nv_bfloat16*>(dw2), H,
+                                              I, 1.0f, status, rt->sms, stream))
+      return rc;
+  } else {
+    if (int rc = launch_kgrouped_tn(sched, dab, x_bf16, static_cast<__nv_bfloat16*>(dw1), 2 * I, H, status,
+                                    rt->sms, stream))
+      return rc;
+    if (int rc = launch_kgrouped_tn(sched, dy_bf16, u, static_cast<__nv_bfloat16*>(dw2), H, I, status, rt->sms,
+                                    stream))
+      return rc;
+  }
   // 7. source side: ordered combine of dX, dprob back to the original slots.
   if (world > 1)
     if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
