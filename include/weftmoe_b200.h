@@ -114,11 +114,23 @@ typedef struct wm_quant_weights {
   const void* w2;
   const void* w2_sf;
   float x_scale, w1_scale, u_scale, w2_scale; /* NVFP4 layer scales; ignored for FP8 */
+  float dy_scale, dab_scale;                   /* NVFP4 backward only: layer scales of dY and d(gate,up) */
 } wm_quant_weights;
 WM_API int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t* routes, const float* gates,
                                 const wm_quant_weights* weights, int32_t tokens, void* y, void* tape,
                                 void* stream);
-/* Blockwise-FP8 backward (reference: forward_fp8 + backward, weftmoe/runtime.py:303-367; dataflow
+/* Backward of the quantised layer; `tape` was filled by wm_forward_quantized on a runtime created with
+ * training = 1 and the same precision.
+ *
+ * NVFP4 (reference: weftmoe/nvfp4_backward.py:59-112): `transposed` holds W1^T [E_local][H][2I/2] and
+ * W2^T [E_local][I][H/2] quantised along their new last axis with the same weight scales, plus all six
+ * layer scales.  dY rows are quantised along H (dy_scale) for dU = dY W2, dAB rows along 2I (dab_scale)
+ * for dX = dAB W1; for the weight gradients dAB, the saved X (dequantised NVFP4 rows), dY and the
+ * recomputed U are re-quantised block-16 ALONG THE ROWS (each contraction's reduction axis) with
+ * dab_scale, x_scale, dy_scale, u_scale, and contracted per expert.  SwiGLU backward runs in FP32 on the
+ * saved BF16 gate/up rows.  Outputs as in wm_backward.
+ *
+ * Blockwise FP8 (reference: forward_fp8 + backward, weftmoe/runtime.py:303-367; dataflow
  * docs/usage.md:216-252).  `tape` (tape_bytes, same size as the BF16 tape) was filled by
  * wm_forward_quantized on an FP8 runtime created with training = 1; `transposed` holds the prepared
  * W1^T [E_local][H][2I] and W2^T [E_local][I][H] bytes with their packed scale chunks.  dY is quantised

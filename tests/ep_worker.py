@@ -124,6 +124,27 @@ def main():
         assert err < 5e-3, (precision, err)
     if rank == 0:
         print(f"EP{world} quantised inference (nvfp4, fp8): oracle parity and EP1 == EP{world} bits passed", flush=True)
+    # ---- NVFP4 training over the EP group: output and all gradients, EPn bits == EP1 bits
+    dys = [(torch.randn(t, H, generator=g) * 0.2).bfloat16() for t in counts]
+    grads = []
+    for group, n, sl in ((dist.group.WORLD, max(counts), slice(rank * e_local, (rank + 1) * e_local)),
+                         (SingleRankGroup(), sum(counts), slice(0, E))):
+        rt = TensorRuntime(group=group, experts=E, top_k=K, hidden=H, intermediate=I, max_tokens=max(n, 1),
+                           max_rows=sum(counts) * K, training=True, precision="nvfp4", max_saved=1)
+        single = isinstance(group, SingleRankGroup)
+        pick = (lambda parts: torch.cat(parts).cuda()) if single else (lambda parts: parts[rank].cuda())
+        lw1, lw2 = w1[sl].contiguous().cuda(), w2[sl].contiguous().cuda()
+        tape = rt.forward_async(pick(xs), pick(rs), pick(gs), lw1, lw2)
+        grads.append((tape.output, *rt.backward(tape, pick(dys))))
+        rt.close()
+    begin = sum(counts[:rank])
+    mine = slice(begin, begin + counts[rank])
+    for name, part, whole in zip(("y", "dx", "dgates"), grads[0][:3], grads[1][:3]):
+        assert torch.equal(bits(whole[mine]), bits(part)), ("nvfp4 training", name, "EP1 != EPn bits")
+    for name, part, whole in zip(("dw1", "dw2"), grads[0][3:], grads[1][3:]):
+        assert torch.equal(bits(whole[rank * e_local:(rank + 1) * e_local]), bits(part)), ("nvfp4 training", name)
+    if rank == 0:
+        print(f"EP{world} NVFP4 training: EP1 == EP{world} bits for y, dx, dgates, dw1, dw2 passed", flush=True)
     # ---- received rows beyond max_rows: a collective, reported error, runtime stays usable
     small = TensorRuntime(group=dist.group.WORLD, experts=E, top_k=K, hidden=H, intermediate=I,
                           max_tokens=512, max_rows=128, training=False)

@@ -152,3 +152,37 @@ def test_fp8_weight_gradients_in_fp8_meet_the_same_acceptance():
                          capture_output=True, text=True, timeout=900)
     assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-2000:]
     assert "2 passed" in run.stdout
+
+
+@pytest.mark.parametrize("cfg", [dict(experts=16, top_k=4, hidden=512, intermediate=256, tokens=200),
+                                 dict(experts=8, top_k=2, hidden=1024, intermediate=512, tokens=77)])
+def test_nvfp4_training_forward_backward_against_reference_formula(cfg):
+    """NVFP4 training (reference: tests/torchrun_sm100_nvfp4_backward.py): output and every gradient against
+    independently rounded FP32 GEMMs; the reference accepts rel-L2 < 6e-4 per gradient on its own kernels,
+    here the bound leaves room for the few FP4 codes that flip when a BF16 intermediate differs by one
+    ulp between the FP32 tensor-core sum and the oracle's matmul."""
+    d, g = inputs(cfg, 31, 0.2, 0.025)           # the reference test's input scales
+    g["dy"] = (g["dy"] * 0.2).contiguous()
+    d["dy"] = g["dy"].cpu()
+    scales = NVFP4Scales()
+    rt = TensorRuntime(group=SingleRankGroup(), experts=cfg["experts"], top_k=cfg["top_k"], hidden=cfg["hidden"],
+                       intermediate=cfg["intermediate"], max_tokens=cfg["tokens"],
+                       max_rows=cfg["tokens"] * cfg["top_k"], training=True, precision="nvfp4", max_saved=2)
+    results = []
+    for _ in range(2):
+        tape = rt.forward_async(g["x"], g["routes"], g["gates"], g["w1"], g["w2"])
+        results.append((tape.output, *rt.backward(tape, g["dy"])))
+    for a, b in zip(*results):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))            # repeatable bit for bit
+    ref = O.nvfp4_training_layer(d["x"], d["routes"], d["gates"], d["w1"], d["w2"], d["dy"], scales=tuple(scales))
+    names = ("y", "dx", "dgates", "dw1", "dw2")
+    for name, actual, expected in zip(names, results[0], ref):
+        err = rel_l2(actual, expected)
+        assert err < 2e-3, (name, err)   # measured: 0 for y, dx, dw2; <= 6.1e-4 for dw1; 1.4e-7 for dgates
+    # the inference forward of an inference runtime gives the same output bits
+    inf = runtime(cfg, "nvfp4")
+    weights = prepare_nvfp4_weights(g["w1"], g["w2"], weight_scales=(scales.w1, scales.w2))
+    assert torch.equal(inf.inference_nvfp4(0, g["x"], g["routes"], g["gates"], weights).view(torch.int16),
+                       results[0][0].view(torch.int16))
+    inf.close()
+    rt.close()

@@ -81,3 +81,21 @@ def test_reference_verify_step_accepts_the_oracle():
 
     errors = ref.verify_step(Stub(), d["x"], d["routes"], d["gates"], d["w1"], d["w2"], d["dy"])
     assert all(e["relative_l2"] < 1e-5 for e in errors.values()), errors
+
+
+def test_nvfp4_training_oracle_is_consistent_with_the_forward_oracle_and_the_unquantised_layer():
+    """The NVFP4 training restatement (weftmoe/nvfp4_backward.py:59-112) gives the forward oracle's output
+    bit for bit, and its gradients stay within 4-bit distance of the unquantised layer's."""
+    cfg = dict(experts=4, top_k=2, hidden=128, intermediate=64, tokens=24)
+    d = O.make_inputs(cfg, seed=5, x_std=0.2, w_std=0.025)
+    d["routes"][0] = 1
+    d["routes"][1] = -1
+    dy = (d["dy"].float() * 0.2).to(torch.bfloat16)
+    scales = (1 / 32, 1 / 64, 1 / 512, 1 / 64, 1 / 32, 1 / 512)
+    y, dx, dg, dw1, dw2 = O.nvfp4_training_layer(d["x"], d["routes"], d["gates"], d["w1"], d["w2"], dy, scales=scales)
+    fwd = O.quantized_layer(d["x"], d["routes"], d["gates"], d["w1"], d["w2"], kind="nvfp4", scales=scales[:4])
+    assert torch.equal(y, fwd)
+    ref = O.moe_layer(d["x"], d["routes"], d["gates"], d["w1"], d["w2"], dy)
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    assert rel(dx, ref[1]) < 0.3 and rel(dw1, ref[3]) < 0.3 and rel(dw2, ref[4]) < 0.3 and rel(dg, ref[2]) < 0.3
+    assert (dx[1] == 0).all() and (dg[1] == 0).all()

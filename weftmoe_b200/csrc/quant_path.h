@@ -45,6 +45,10 @@ int fp8_quantize_cols_chunked(DeviceRange rows, const __nv_bfloat16* x, int cols
 int launch_block_scaled_kgrouped(int kind, const Schedule& s, const void* a, const SfLayout& sfa, const void* b,
                                  const SfLayout& sfb, __nv_bfloat16* out, int m, int n, float alpha,
                                  int* status, int sms, cudaStream_t stream);
+// NVFP4 backward helpers: a plain BF16 transpose, and packed rows + chunked scales back to BF16.
+int transpose_bf16(const __nv_bfloat16* x, int rows, int cols, __nv_bfloat16* xt, cudaStream_t stream);
+int nvfp4_dequantize_rows(const uint8_t* data, const uint8_t* sf_chunks, int rows, int cols, float layer_scale,
+                          __nv_bfloat16* out, int sms, cudaStream_t stream);
 int swiglu_quantize(DeviceRange rows, const __nv_bfloat16* ab, const float* prob, int inter, int kind,
                     float layer_scale, uint8_t* uq, uint32_t* sfa_out, int sms, cudaStream_t stream);
 // out[rows, n] = alpha * A[rows, k] * B[e][n, k]^T with quantised operands; `push` != nullptr sends the

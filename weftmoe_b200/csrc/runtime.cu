@@ -12,6 +12,7 @@
 //   CONTRIB[o]  owner o finished writing its results into my mailbox
 // A source overwrites its staging buffer only after PULLED >= g-1 from every owner; an owner
 // writes a mailbox only after READY >= g, which the source sends after its previous combine.
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -71,7 +72,7 @@ struct ScratchLayout {
   size_t status, sorted_slot, sorted_expert, slot_pos, local_offset, dst_rank, dst_row, dst_prow,
       chunk_hist, local_count, expert_total, expert_before, expert_base, expert_pbase, padded_start,
       tile_group, num_tiles, padded_rows, pair_tiles, num_pairs, split, origin, prob, xrows, u, recv, du,
-      dab, abq, sfa_x, sfa_u, primary, wq_a, wq_b, wsf_a, wsf_b, total;
+      dab, abq, sfa_x, sfa_u, primary, wq_a, wq_b, wsf_a, wsf_b, wt, total;
 };
 // Training cache carved out of the caller's tape buffer.
 struct TapeLayout {
@@ -160,7 +161,8 @@ ScratchLayout scratch_layout(const wm_config& c, int row_cap) {
     const size_t tiles = row_cap / 128;
     s.abq = k.take(4ull * row_cap * c.intermediate);
     s.sfa_x = k.take(tiles * (c.hidden / 64) * 512);
-    s.sfa_u = k.take(tiles * (c.intermediate / 64) * 512);
+    // U chunks in the forward pass; the backward pass keeps the chunks of dAB (2I wide) here
+    s.sfa_u = k.take(tiles * (c.intermediate / 64) * 512 * (c.training ? 2 : 1));
   }
   if (c.training) {
     s.recv = k.take(2ull * row_cap * c.hidden);
@@ -175,6 +177,16 @@ ScratchLayout scratch_layout(const wm_config& c, int row_cap) {
     s.wq_b = k.take(static_cast<size_t>(row_cap) * c.hidden);
     s.wsf_a = k.take((wide / 128) * (row_cap / 128) * 512 + 4 * 512);
     s.wsf_b = k.take((static_cast<size_t>(c.hidden) / 128) * (row_cap / 128) * 512 + 4 * 512);
+  }
+  if (c.training && c.reserved == 2) {
+    // NVFP4 weight gradients: a BF16 transpose of one operand at a time, then both operands of the
+    // contraction quantised block-16 along the rows ([features][row_cap / 2] bytes) with their chunks.
+    const size_t wide = c.hidden > 2 * c.intermediate ? c.hidden : 2 * c.intermediate;
+    s.wt = k.take(2ull * row_cap * wide);
+    s.wq_a = k.take(static_cast<size_t>(row_cap) / 2 * wide);
+    s.wq_b = k.take(static_cast<size_t>(row_cap) / 2 * wide);
+    s.wsf_a = k.take((wide / 128) * (row_cap / 64) * 512 + 4 * 512);
+    s.wsf_b = k.take((wide / 128) * (row_cap / 64) * 512 + 4 * 512);
   }
   s.total = k.cursor;
   return s;
@@ -821,8 +833,8 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
     set_error("NVFP4 tensor scales must be finite and positive");
     return WM_ERR_INVALID;
   }
-  if (tape && (!c.training || kind != kKindFp8 || !aligned16(tape))) {
-    set_error("a training cache needs an FP8 runtime created with training=1 (NVFP4 backward is not built)");
+  if (tape && (!c.training || !aligned16(tape))) {
+    set_error("a training cache needs a runtime created with training=1");
     return WM_ERR_STATE;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -949,6 +961,150 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
                       c.max_tokens, c.top_k, c.hidden, static_cast<__nv_bfloat16*>(y), stream);
 }
 
+// =============================================================================== NVFP4 backward
+// Reference: weftmoe/nvfp4_backward.py:59-112.  Every contraction reads operands quantised block-16 along
+// ITS reduction axis: dU and dX use row-quantised dY / dAB against the prepared W2^T / W1^T; the weight
+// gradients use dAB, X, dY, U transposed and quantised along the rows, contracted by the K-grouped mode
+// of the block-scaled kernel.  dY travels in BF16 (pulled by the saved origins like the BF16 backward).
+static int backward_nvfp4(wm_runtime* rt, const void* tape, const void* dy, const wm_quant_weights* w,
+                          int32_t tokens, void* dx, float* dgates, void* dw1, void* dw2, void* stream_) {
+  const wm_config& c = rt->cfg;
+  if (tokens < 0 || tokens > c.max_tokens) {
+    set_error("Backward token count %d exceeds capacity %d", tokens, c.max_tokens);
+    return WM_ERR_CAPACITY;
+  }
+  if (!tape || !w || !w->w1 || !w->w1_sf || !w->w2 || !w->w2_sf || !dw1 || !dw2 ||
+      (tokens > 0 && (!dy || !dx || !dgates)) || !aligned16(tape) || !aligned16(dy) || !aligned16(dx) ||
+      !aligned16(dw1) || !aligned16(dw2)) {
+    set_error("wm_backward_quantized: null or misaligned tensor (16-byte alignment required)");
+    return WM_ERR_INVALID;
+  }
+  const float scales[6] = {w->x_scale, w->w1_scale, w->u_scale, w->w2_scale, w->dy_scale, w->dab_scale};
+  for (float v : scales)
+    if (!(v > 0.0f) || !std::isfinite(v)) {
+      set_error("NVFP4 tensor scales must be finite and positive");
+      return WM_ERR_INVALID;
+    }
+  const int H = c.hidden, I = c.intermediate;
+  if (H > 8 * I) {
+    set_error("NVFP4 backward needs hidden <= 8 * intermediate (scratch sizing)");
+    return WM_ERR_INVALID;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int gen = ++rt->generation;
+  const int world = c.world;
+  uint8_t* S = rt->scratch;
+  const uint8_t* T = static_cast<const uint8_t*>(tape);
+  auto tp = [&](size_t off) { return const_cast<uint8_t*>(T) + off; };
+  int* status = at<int>(S, rt->sl.status);
+  const int* sorted_slot = reinterpret_cast<const int*>(tp(rt->tl.sorted_slot));
+  const int* sorted_expert = reinterpret_cast<const int*>(tp(rt->tl.sorted_expert));
+  const int* padded_start = reinterpret_cast<const int*>(tp(rt->tl.padded_start));
+  const int* tile_group = reinterpret_cast<const int*>(tp(rt->tl.tile_group));
+  const int* pair_tiles = reinterpret_cast<const int*>(tp(rt->tl.pair_tiles));
+  const int* split = reinterpret_cast<const int*>(tp(rt->tl.split));
+  const int* origin = reinterpret_cast<const int*>(tp(rt->tl.origin));
+  const float* prob = reinterpret_cast<const float*>(tp(rt->tl.prob));
+  const uint8_t* xq = tp(rt->tl.xrows);
+  const uint8_t* sf_x = tp(rt->tl.xrows) + align_up(static_cast<size_t>(rt->row_cap) * H);
+  const auto* ab = reinterpret_cast<const __nv_bfloat16*>(tp(rt->tl.ab));
+  auto* x_bf16 = at<__nv_bfloat16>(S, rt->sl.xrows);
+  auto* recv = at<__nv_bfloat16>(S, rt->sl.recv);
+  auto* u = at<__nv_bfloat16>(S, rt->sl.u);
+  auto* du = at<__nv_bfloat16>(S, rt->sl.du);
+  auto* dab = at<__nv_bfloat16>(S, rt->sl.dab);
+  uint8_t* qrows = at<uint8_t>(S, rt->sl.abq);       // row-quantised dY, then dAB (<= row_cap * 4I bytes)
+  uint8_t* sf_dy = at<uint8_t>(S, rt->sl.sfa_x);     // H / 64 chunks per row tile
+  uint8_t* sf_dab = at<uint8_t>(S, rt->sl.sfa_u);    // 2I / 64 chunks per row tile
+  auto* wt = at<__nv_bfloat16>(S, rt->sl.wt);
+  uint8_t* qa = at<uint8_t>(S, rt->sl.wq_a);
+  uint8_t* qb = at<uint8_t>(S, rt->sl.wq_b);
+  uint8_t* sa = at<uint8_t>(S, rt->sl.wsf_a);
+  uint8_t* sb = at<uint8_t>(S, rt->sl.wsf_b);
+  const int R = rt->row_cap;
+
+  PeerConstRows stage{};
+  PeerFloats dgate_box{};
+  PushTarget push{};
+  for (int r = 0; r < world; ++r) {
+    stage.p[r] = at<__nv_bfloat16>(rt->peer[r], rt->al.stage);
+    dgate_box.p[r] = at<float>(rt->peer[r], rt->al.dgate_box);
+    push.mailbox[r] = at<__nv_bfloat16>(rt->peer[r], rt->al.mailbox);
+  }
+  push.origin = origin;
+  push.cap = c.max_tokens;
+  push.top_k = c.top_k;
+
+  // 1. stage dY (BF16) and pull its rows in the saved row order.
+  if (world > 1)
+    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, stream)) return rc;
+  if (world == 1)
+    stage.p[0] = static_cast<const __nv_bfloat16*>(dy);
+  else if (tokens > 0)
+    WM_CUDA(cudaMemcpyAsync(rt->arena + rt->al.stage, dy, 2ull * tokens * H, cudaMemcpyDeviceToDevice, stream));
+  if (world > 1) {
+    if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
+  }
+  const DeviceRange all_rows = split_range(split, 2, kWhole);
+  if (int rc = gather_by_origin(all_rows, origin, nullptr, c.max_tokens, c.top_k, H, stage, recv, rt->sms * 8,
+                                stream))
+    return rc;
+  if (world > 1)
+    if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
+  Schedule sched{split, tile_group, padded_start, rt->e_local, R, pair_tiles, false, kWhole};
+  const long long chunk = 512;
+  const int kh = H / 64, ki2 = 2 * I / 64;
+  // 2. dU = q(dY) W2: dY rows quantised along H against W2^T [I][H].
+  if (int rc = nvfp4_quantize_rows(recv, R, H, w->dy_scale, qrows, sf_dy, 1, stream)) return rc;
+  const SfLayout sfa_dy{sf_dy, 0, kh * chunk, 4 * chunk, chunk};
+  const SfLayout sfb_w2t{static_cast<const uint8_t*>(w->w2_sf), (1ll * I / 128) * kh * chunk, kh * chunk, 4 * chunk,
+                         chunk};
+  if (int rc = launch_block_scaled(kKindNvfp4, sched, qrows, sfa_dy, w->w2, sfb_w2t, du, nullptr, I, H,
+                                   w->dy_scale * w->w2_scale, status, rt->sms, stream))
+    return rc;
+  // 3. SwiGLU backward in FP32 on the saved BF16 gate/up rows: U, dAB, dprob -> sources.
+  if (int rc = swiglu_backward(all_rows, ab, du, prob, origin, I, c.max_tokens, c.top_k, u, dab, dgate_box,
+                               rt->sms, stream))
+    return rc;
+  // 4. dX = q(dAB) W1 -> sources' mailboxes: dAB rows quantised along 2I against W1^T [H][2I].
+  if (int rc = nvfp4_quantize_rows(dab, R, 2 * I, w->dab_scale, qrows, sf_dab, 1, stream)) return rc;
+  const SfLayout sfa_dab{sf_dab, 0, ki2 * chunk, 4 * chunk, chunk};
+  const SfLayout sfb_w1t{static_cast<const uint8_t*>(w->w1_sf), (1ll * H / 128) * ki2 * chunk, ki2 * chunk,
+                         4 * chunk, chunk};
+  if (int rc = launch_block_scaled(kKindNvfp4, sched, qrows, sfa_dab, w->w1, sfb_w1t, nullptr, &push, H, 2 * I,
+                                   w->dab_scale * w->w1_scale, status, rt->sms, stream))
+    return rc;
+  if (world > 1)
+    if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
+  // 5. weight gradients: operands transposed, quantised along the rows, contracted per expert.
+  const long long per_tile = static_cast<long long>(R / 64) * chunk;
+  const SfLayout la{sa, 0, per_tile, 4 * chunk, chunk}, lb{sb, 0, per_tile, 4 * chunk, chunk};
+  auto along_rows = [&](const __nv_bfloat16* rows_in, int cols, float scale, uint8_t* q, uint8_t* sf) -> int {
+    if (int rc = transpose_bf16(rows_in, R, cols, wt, stream)) return rc;
+    return nvfp4_quantize_rows(wt, cols, R, scale, q, sf, 1, stream);
+  };
+  if (int rc = nvfp4_dequantize_rows(xq, sf_x, R, H, w->x_scale, x_bf16, rt->sms, stream)) return rc;
+  if (int rc = along_rows(dab, 2 * I, w->dab_scale, qa, sa)) return rc;
+  if (int rc = along_rows(x_bf16, H, w->x_scale, qb, sb)) return rc;
+  if (int rc = launch_block_scaled_kgrouped(kKindNvfp4, sched, qa, la, qb, lb, static_cast<__nv_bfloat16*>(dw1),
+                                            2 * I, H, w->dab_scale * w->x_scale, status, rt->sms, stream))
+    return rc;
+  if (int rc = along_rows(recv, H, w->dy_scale, qa, sa)) return rc;
+  if (int rc = along_rows(u, I, w->u_scale, qb, sb)) return rc;
+  if (int rc = launch_block_scaled_kgrouped(kKindNvfp4, sched, qa, la, qb, lb, static_cast<__nv_bfloat16*>(dw2), H, I,
+                                            w->dy_scale * w->u_scale, status, rt->sms, stream))
+    return rc;
+  // 6. source side: ordered combine of dX, dprob back to the original slots.
+  if (world > 1)
+    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
+  if (int rc = combine_rows(at<__nv_bfloat16>(rt->arena, rt->al.mailbox), sorted_expert, tokens, c.max_tokens,
+                            c.top_k, H, static_cast<__nv_bfloat16*>(dx), stream))
+    return rc;
+  return unpermute_dgates(at<float>(rt->arena, rt->al.dgate_box), sorted_slot, sorted_expert, tokens, c.top_k,
+                          dgates, stream);
+}
+
 // =============================================================================== FP8 backward
 // Mixed precision (stated in the header): both dgrad contractions run in blockwise FP8 against the
 // prepared transposed weights, exactly like the forward GEMMs; the two weight-gradient contractions run
@@ -959,10 +1115,11 @@ extern "C" int wm_backward_quantized(wm_runtime* rt, const void* tape, const voi
                                      float* dgates, void* dw1, void* dw2, void* stream_) {
   if (int rc = check_ready(rt, "wm_backward_quantized")) return rc;
   const wm_config& c = rt->cfg;
-  if (!c.training || c.reserved != 1) {
-    set_error("Backward requires an FP8 runtime prepared with training=True");
+  if (!c.training || c.reserved == 0) {
+    set_error("Backward requires an FP8 or NVFP4 runtime prepared with training=True");
     return WM_ERR_STATE;
   }
+  if (c.reserved == 2) return backward_nvfp4(rt, tape, dy, transposed, tokens, dx, dgates, dw1, dw2, stream_);
   if (tokens < 0 || tokens > c.max_tokens) {
     set_error("Backward token count %d exceeds capacity %d", tokens, c.max_tokens);
     return WM_ERR_CAPACITY;

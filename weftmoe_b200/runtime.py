@@ -283,9 +283,53 @@ class NativeRuntime:
 
     # ------------------------------------------------------------------ training
     def forward_async(self, x, routes, gates, w1, w2, retain_backward_state=True):
+        if self.precision == "nvfp4":
+            return self._forward_nvfp4(x, routes, gates, w1, w2, retain_backward_state)
         if self.training and retain_backward_state:
             return self._run(x, routes, gates, w1, w2, save=True)
         return Tape(self._run(x, routes, gates, w1, w2))
+
+    # NVFP4 training (reference: NVFP4Runtime.forward / weftmoe/nvfp4_backward.py): BF16 master weights are
+    # quantised block-16 along the reduction axis of each contraction, forward layout in the forward
+    # pass and transposed in the backward pass, with the runtime's layer scales.
+    def _forward_nvfp4(self, x, routes, gates, w1, w2, retain):
+        from .nvfp4 import prepare_nvfp4_weights
+        s = self.scales
+        q = prepare_nvfp4_weights(w1, w2, weight_scales=(s.w1, s.w2))
+        packed = (q.fc1[0], q.fc1[1], q.fc2[0], q.fc2[1], s.x, s.w1, s.intermediate, s.w2)
+        if self.training and retain:
+            y, blob = self._run_quantized(x, routes, gates, packed, save=True)
+            tape = Tape(y, (blob, w1, w2, x.shape[0], self.sizes.row_capacity * self.shape[2] // 2))
+            self.tapes.add(tape)
+            return tape
+        return Tape(self._run_quantized(x, routes, gates, packed))
+
+    def _backward_nvfp4(self, tape, dy):
+        from .nvfp4 import quantize_nvfp4
+        blob, w1, w2, tokens, _ = tape.state
+        if dy.dtype != torch.bfloat16 or dy.shape != tape.output.shape or dy.device != blob.device:
+            raise ValueError("Backward requires BF16 dY matching the forward output")
+        s = self.scales
+        e, k = self.local_experts, self.shape[1]
+        _, _, hidden, inter = self.shape
+        w1t = w1.transpose(1, 2).contiguous().view(e * hidden, 2 * inter)     # [E*H, 2I]: reduce over 2I
+        w2t = w2.transpose(1, 2).contiguous().view(e * inter, hidden)         # [E*I, H]:  reduce over H
+        w1t_q, w1t_sf = quantize_nvfp4(w1t, s.w1, chunked=True)
+        w2t_q, w2t_sf = quantize_nvfp4(w2t, s.w2, chunked=True)
+        dx = torch.empty_like(dy)
+        dgates = torch.empty((tokens, k), dtype=torch.float32, device=dy.device)
+        dw1, dw2 = torch.empty_like(w1), torch.empty_like(w2)
+        packed = _lib.WmQuantWeights(w1=w1t_q.data_ptr(), w1_sf=w1t_sf.data_ptr(), w2=w2t_q.data_ptr(),
+                                     w2_sf=w2t_sf.data_ptr(), x_scale=s.x, w1_scale=s.w1, u_scale=s.intermediate,
+                                     w2_scale=s.w2, dy_scale=s.dy, dab_scale=s.dgate_up)
+        _lib.check(self.lib.wm_backward_quantized(self.handle, _lib.ptr(blob), _lib.ptr(dy), ctypes.byref(packed),
+                                                  tokens, _lib.ptr(dx), _lib.ptr(dgates), _lib.ptr(dw1),
+                                                  _lib.ptr(dw2), self.stream.cuda_stream))
+        for t in (w1t_q, w1t_sf, w2t_q, w2t_sf):
+            t.record_stream(self.stream)
+        tape.state = None
+        self.tapes.discard(tape)
+        return dx, dgates, dw1, dw2
 
     def forward(self, x, routes, gates, w1, w2):
         tape = self.forward_async(x, routes, gates, w1, w2)
@@ -298,6 +342,8 @@ class NativeRuntime:
             raise RuntimeError("Backward requires a live training tape from this runtime")
         if self.precision == "fp8":
             return self._backward_fp8(tape, dy)
+        if self.precision == "nvfp4":
+            return self._backward_nvfp4(tape, dy)
         blob, w1, w2, tokens, _ = tape.state
         if dy.dtype != torch.bfloat16 or dy.shape != tape.output.shape or dy.device != blob.device:
             raise ValueError("Backward requires BF16 dY matching the forward output")
@@ -450,8 +496,6 @@ class TensorRuntime:
             raise ValueError("Unsupported runtime precision")
         if fp8_workspace and self.precision != "fp8":
             raise ValueError("Unsupported runtime precision")
-        if self.precision == "nvfp4" and training:
-            raise ValueError("NVFP4 runtimes serve inference only in this build; train with BF16 or FP8")
         if self.precision == "nvfp4":
             from .nvfp4 import NVFP4Scales, _validate_scales
             if intermediate % 256:
@@ -477,9 +521,10 @@ class TensorRuntime:
     def _check(self, x, routes, gates, w1, w2):
         if self.native is None:
             raise RuntimeError("WeftMoE runtime is closed")
-        if self.precision != "bf16":
-            raise ValueError("Compact FP8 workspace requires forward_fp8 or moe(..., fp8_weights=...)"
-                             if self.precision == "fp8" else "NVFP4 runtimes take inference_nvfp4")
+        if self.precision == "fp8":
+            raise ValueError("Compact FP8 workspace requires forward_fp8 or moe(..., fp8_weights=...)")
+        if self.precision == "nvfp4" and not self.training:
+            raise ValueError("NVFP4 inference runtimes take inference_nvfp4")
         if self.training and torch.cuda.current_stream() != self.stream:
             raise RuntimeError("Runtime must be invoked on its preparation stream")
         if x.ndim != 2 or x.shape[1] != self.hidden or x.shape[0] > self.max_tokens:
