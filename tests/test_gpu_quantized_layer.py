@@ -179,6 +179,13 @@ def test_nvfp4_training_forward_backward_against_reference_formula(cfg):
     for name, actual, expected in zip(names, results[0], ref):
         err = rel_l2(actual, expected)
         assert err < 2e-3, (name, err)   # measured: 0 for y, dx, dw2; <= 6.1e-4 for dw1; 1.4e-7 for dgates
+    # autograd entry point: same bits as the direct calls
+    from weftmoe_b200 import moe
+    x, gates = g["x"].clone().requires_grad_(), g["gates"].clone().requires_grad_()
+    w1, w2 = g["w1"].clone().requires_grad_(), g["w2"].clone().requires_grad_()
+    moe(rt, x, g["routes"], gates, w1, w2).backward(g["dy"])
+    for grad, expected in zip((x.grad, gates.grad, w1.grad, w2.grad), results[0][1:]):
+        assert torch.equal(grad.view(torch.uint8), expected.view(torch.uint8))
     # the inference forward of an inference runtime gives the same output bits
     inf = runtime(cfg, "nvfp4")
     weights = prepare_nvfp4_weights(g["w1"], g["w2"], weight_scales=(scales.w1, scales.w2))
