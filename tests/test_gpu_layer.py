@@ -221,3 +221,49 @@ def test_decode_under_cuda_graph_replays_and_matches_eager_bits():
     assert rel_l2(y, ref) < TOL_ROUNDED_ORACLE
     del graph
     rt.close()
+
+
+def test_full_size_layer_repeats_is_batch_invariant_and_matches_the_oracle_on_samples():
+    """BASELINE configs[1] at EP1 (E=256, K=8, H=2048, I=512, 8192 tokens), where the whole-layer oracle would
+    take minutes: (1) forward + backward twice give identical bits; (2) a token's output does not depend on
+    its batch: the first 1000 tokens alone reproduce their rows bit for bit; (3) sampled parity with the
+    oracle: y and dX of a few tokens (they depend only on that token's row and its experts' weights) and
+    dW1 / dW2 of two experts (they depend only on the rows routed to that expert)."""
+    cfg = dict(experts=256, top_k=8, hidden=2048, intermediate=512, tokens=8192)
+    d = O.make_inputs(cfg, seed=123, bias_std=0.5)
+    g = on_gpu(d)
+    rt = runtime(cfg, cfg["tokens"], max_saved=1)
+    runs = []
+    for _ in range(2):
+        tape = rt.forward_async(g["x"], g["routes"], g["gates"], g["w1"], g["w2"])
+        runs.append((tape.output, *rt.backward_async(tape, g["dy"])))
+    for a, b in zip(*runs):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    y, dx, dg, dw1, dw2 = runs[0]
+    prefix = rt.forward_async(g["x"][:1000].contiguous(), g["routes"][:1000].contiguous(),
+                              g["gates"][:1000].contiguous(), g["w1"], g["w2"], retain_backward_state=False)
+    assert torch.equal(bits(prefix.output), bits(y[:1000]))
+    rt.close()
+
+    def compact(tokens, routes):
+        """The oracle on a few tokens with only the experts they touch (ids renumbered)."""
+        used = routes[routes >= 0].unique()
+        remap = torch.full((cfg["experts"],), -1, dtype=torch.int32)
+        remap[used.long()] = torch.arange(len(used), dtype=torch.int32)
+        local = torch.where(routes >= 0, remap[routes.clamp_min(0).long()], routes)
+        out = O.moe_layer(d["x"][tokens], local, d["gates"][tokens], d["w1"][used.long()], d["w2"][used.long()],
+                          d["dy"][tokens])
+        return used, out
+
+    sample = torch.tensor([0, 1, 4097, 8191])
+    _, (ys, dxs, dgs, _, _) = compact(sample, d["routes"][sample])
+    assert rel_l2(y[sample], ys) < TOL_ROUNDED_ORACLE and rel_l2(dx[sample], dxs) < TOL_ROUNDED_ORACLE
+    assert rel_l2(dg[sample], dgs) < TOL_ROUNDED_ORACLE
+    counts = torch.bincount(d["routes"].flatten().long(), minlength=cfg["experts"])
+    for expert in (int(counts.argmax()), int(counts.argmin())):
+        tokens = (d["routes"] == expert).any(dim=1).nonzero().flatten()
+        only = torch.where(d["routes"][tokens] == expert, d["routes"][tokens], torch.full_like(d["routes"][tokens], -1))
+        used, (_, _, _, w1g, w2g) = compact(tokens, only)
+        assert used.tolist() == [expert]
+        assert rel_l2(dw1[expert], w1g[0]) < TOL_ROUNDED_ORACLE, expert
+        assert rel_l2(dw2[expert], w2g[0]) < TOL_ROUNDED_ORACLE, expert
