@@ -72,6 +72,49 @@ struct EpilogueStore {
   }
 };
 
+// Plain BF16 store through TMA: each warp packs its 32 rows into two 128-byte-swizzled boxes
+// (32 rows x 64 columns, 4 KB each) and one lane issues a bulk tensor store per box, so the warp
+// spends no instructions on reading the staging back and writing global memory.  `out` is described by
+// a 2-D tensor map over [all rows][ld] with box {64, 32}; K-grouped outputs stack the experts along
+// the rows (row = group * rows_per_group + m_tile * 128 + r).  A box is reused once the store issued
+// from it one half earlier has finished reading it.
+template <int BLOCK_N>
+struct EpilogueStoreTma {
+  alignas(64) CUtensorMap tmap;
+  int rows_per_group;  // K-grouped: M (rows of one expert's output); 0 for M-grouped
+
+  __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane,
+                                             bool zero, uint8_t* stage) const {
+    const int row0 = t.group * rows_per_group + t.m_tile * kBlockM + q * 32;
+    const int col0 = t.n_tile * BLOCK_N;
+#pragma unroll 1
+    for (int unit = 0; unit < BLOCK_N / 64; ++unit) {
+      uint8_t* box = stage + (unit & 1) * 4096;
+      if (lane == 0) bulk_wait_group_read<1>();  // the store issued from this box two units ago
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t w[16];
+        load_pack32(taddr + unit * 64 + c * 32, zero, w);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(box + lane * 128 + (((c * 4 + j) ^ (lane & 7)) << 4)) =
+              make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(&tmap, box, col0 + unit * 64, row0);
+        bulk_commit_group();
+      }
+    }
+  }
+  // Before the CTA exits: every store has finished reading shared memory.
+  __device__ __forceinline__ void finish(int lane) const {
+    if (lane == 0) bulk_wait_group_read<0>();
+  }
+};
+
 // FC1 epilogue (reference: src/cuda/blackwell/fused/impls/routed_bf16.cuh:874-1027):
 // accumulator columns [0,128) are gate, [128,256) are up for intermediate columns
 // n_tile*128 .. +127.  gate and up are rounded to BF16 first (that rounded pair is what the

@@ -193,6 +193,15 @@ struct TimelineScope {
   }
 };
 
+// WM_EPILOGUE_TMA=0 keeps the plain-store epilogue of dU / dW (comparison runs).
+static bool tma_epilogue() {
+  static const bool on = [] {
+    const char* v = std::getenv("WM_EPILOGUE_TMA");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
 static GemmArgs base_args(const Schedule& s, int* status) {
   GemmArgs a{};
   const DeviceRange tiles = split_range(s.split, 0, s.half);
@@ -259,6 +268,12 @@ static int launch_mgrouped(const Schedule& s, const __nv_bfloat16* a_ptr, const 
     epi.origin = push->origin; epi.cap = push->cap; epi.top_k = push->top_k; epi.ld = n;
     return launch<128, false, B_MN, false, false>(pair, ta, tb, a, s, epi, sms, stream);
   }
+  if (bn == 256 && tma_epilogue()) {
+    EpilogueStoreTma<256> epi{};
+    if (int rc = make_tmap_2d(&epi.tmap, out, 2, n, s.row_capacity, (uint64_t)n * 2, 64, 32)) return rc;
+    epi.rows_per_group = 0;
+    return launch<256, false, B_MN, false, false>(pair, ta, tb, a, s, epi, sms, stream);
+  }
   if (bn == 256) {
     EpilogueStore<256> epi{out, 0, n};
     return launch<256, false, B_MN, false, false>(pair, ta, tb, a, s, epi, sms, stream);
@@ -294,6 +309,12 @@ int launch_kgrouped_tn(const Schedule& s, const __nv_bfloat16* a_ptr, const __nv
   a.m_tiles_per_group = m / 128;
   a.n_tiles = n / bn;
   TimelineScope timeline("wgrad", a);
+  if (bn == 256 && tma_epilogue()) {
+    EpilogueStoreTma<256> epi{};
+    if (int rc = make_tmap_2d(&epi.tmap, out, 2, n, (uint64_t)s.groups * m, (uint64_t)n * 2, 64, 32)) return rc;
+    epi.rows_per_group = m;
+    return launch<256, true, true, false, true>(pair, ta, tb, a, s, epi, sms, stream);
+  }
   if (bn == 256) {
     EpilogueStore<256> epi{out, (long long)m * n, n};
     return launch<256, true, true, false, true>(pair, ta, tb, a, s, epi, sms, stream);

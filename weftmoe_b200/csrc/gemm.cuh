@@ -111,10 +111,18 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& a, int tile) {
 // out with each half-warp covering one whole 256-byte row segment: fully coalesced stores,
 // local or over NVLink.
 
+// Epilogues that keep asynchronous stores in flight define finish(lane); the others need nothing.
+template <class Epilogue>
+__device__ __forceinline__ auto epilogue_finish(const Epilogue& e, int lane, int) -> decltype(e.finish(lane)) {
+  e.finish(lane);
+}
+template <class Epilogue>
+__device__ __forceinline__ void epilogue_finish(const Epilogue&, int, long) {}
+
 template <int BLOCK_N, bool A_MN, bool B_MN, bool GATE_UP, bool K_GROUPED, class Epilogue>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            const GemmArgs args, const Epilogue epilogue) {
+            const GemmArgs args, const __grid_constant__ Epilogue epilogue) {
   using S = GemmSmem<BLOCK_N>;
   constexpr int kStages = S::kStages;
   constexpr uint32_t kTmemCols = 2 * BLOCK_N;  // two accumulator stages (256 or 512 columns)
@@ -289,6 +297,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       if (lane == 0) mbar_arrive(tmem_empty + acc);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    epilogue_finish(epilogue, lane, 0);
   }
 
   tc_fence_before();

@@ -81,7 +81,7 @@ __device__ __forceinline__ PairTile decode_pair(const Gemm2Args& a, int work, in
 template <int BLOCK_N, bool A_MN, bool B_MN, bool GATE_UP, bool K_GROUPED, class Epilogue>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-             const Gemm2Args args2, const Epilogue epilogue) {
+             const Gemm2Args args2, const __grid_constant__ Epilogue epilogue) {
   using S = Gemm2Smem<BLOCK_N>;
   constexpr int kStages = S::kStages;
   constexpr int kHalfN = BLOCK_N / 2;
@@ -247,6 +247,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty + acc), 0));
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    epilogue_finish(epilogue, lane, 0);
   }
 
   tc_fence_before();
