@@ -96,6 +96,11 @@ struct wm_runtime {
   // half is being computed (inbound NVLink beside compute and outbound pushes).
   cudaStream_t side = nullptr;
   cudaEvent_t ev_first_pulled = nullptr, ev_second_pulled = nullptr;
+  // Optional (WM_PUSH_SMS = n > 0, world > 1): the first half's push GEMM (FC2 / dX, bound by NVLink)
+  // runs on n SMs of a third stream beside the second half's compute-bound kernels on the other SMs.
+  cudaStream_t push_stream = nullptr;
+  cudaEvent_t ev_half_ready = nullptr, ev_half_pushed = nullptr;
+  int push_sms = 0;
   // Optional per-stage device timing (CUDA events on the caller's stream).
   bool timing = false;
   int timing_slot = 0;
@@ -377,6 +382,13 @@ extern "C" int wm_runtime_create(const wm_config* config, wm_runtime** out) {
     e = cudaStreamCreateWithFlags(&rt->side, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&rt->ev_first_pulled, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&rt->ev_second_pulled, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&rt->push_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&rt->ev_half_ready, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&rt->ev_half_pushed, cudaEventDisableTiming);
+    if (const char* v = std::getenv("WM_PUSH_SMS")) {
+      const int n = std::atoi(v);
+      if (n >= 8 && n <= rt->sms - 8) rt->push_sms = n & ~1;
+    }
     if (e != cudaSuccess) {
       set_error("side stream creation failed: %s", cudaGetErrorString(e));
       return fail(WM_ERR_CUDA);
@@ -456,6 +468,9 @@ extern "C" int wm_runtime_destroy(wm_runtime* rt) {
   if (rt->side) cudaStreamDestroy(rt->side);
   if (rt->ev_first_pulled) cudaEventDestroy(rt->ev_first_pulled);
   if (rt->ev_second_pulled) cudaEventDestroy(rt->ev_second_pulled);
+  if (rt->push_stream) cudaStreamDestroy(rt->push_stream);
+  if (rt->ev_half_ready) cudaEventDestroy(rt->ev_half_ready);
+  if (rt->ev_half_pushed) cudaEventDestroy(rt->ev_half_pushed);
   if (rt->ev_trace_origin) cudaEventDestroy(rt->ev_trace_origin);
   if (rt->arena) cudaFree(rt->arena);
   if (rt->scratch) cudaFree(rt->scratch);
@@ -603,18 +618,23 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
     return primary ? copy_duplicate_rows(split_range(tables.split, 2, half), primary, c.hidden, xrows, ctas, st)
                    : 0;
   };
+  auto schedule_of = [&](int half) {
+    return Schedule{tables.split, tables.tile_group, tables.padded_start, rt->e_local, rt->row_cap,
+                    tables.pair_tiles, false, half};
+  };
+  auto fc1 = [&](int half, int stage_id, int sms) -> int {
+    StageScope scope(timing, stage_id, stream);
+    return launch_fc1(schedule_of(half), xrows, static_cast<const __nv_bfloat16*>(w1), u, ab, prob, c.hidden,
+                      c.intermediate, status, sms, stream);
+  };
+  auto fc2 = [&](int half, int stage_id, int sms, cudaStream_t st) -> int {
+    StageScope scope(timing, stage_id, st);
+    return launch_mgrouped_nt(schedule_of(half), u, static_cast<const __nv_bfloat16*>(w2), nullptr, &push,
+                              c.hidden, c.intermediate, status, sms, st);
+  };
   auto compute = [&](int half, int stage_fc1, int stage_fc2) -> int {
-    Schedule sched{tables.split, tables.tile_group, tables.padded_start, rt->e_local, rt->row_cap,
-                   tables.pair_tiles, false, half};
-    {
-      StageScope scope(timing, stage_fc1, stream);
-      if (int rc = launch_fc1(sched, xrows, static_cast<const __nv_bfloat16*>(w1), u, ab, prob,
-                              c.hidden, c.intermediate, status, rt->sms, stream))
-        return rc;
-    }
-    StageScope scope(timing, stage_fc2, stream);
-    return launch_mgrouped_nt(sched, u, static_cast<const __nv_bfloat16*>(w2), nullptr, &push,
-                              c.hidden, c.intermediate, status, rt->sms, stream);
+    if (int rc = fc1(half, stage_fc1, rt->sms)) return rc;
+    return fc2(half, stage_fc2, rt->sms, stream);
   };
   if (!halves) {
     {
@@ -634,10 +654,24 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
       if (int rc = pull(kSecondHalf, rt->side)) return rc;
     }
     WM_CUDA(cudaEventRecord(rt->ev_second_pulled, rt->side));
-    if (int rc = compute(kFirstHalf, kStageFc1, kStageFc2)) return rc;
-    WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_second_pulled, 0));
-    if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
-    if (int rc = compute(kSecondHalf, kStageFc1B, kStageFc2B)) return rc;
+    if (rt->push_sms == 0) {
+      if (int rc = compute(kFirstHalf, kStageFc1, kStageFc2)) return rc;
+      WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_second_pulled, 0));
+      if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
+      if (int rc = compute(kSecondHalf, kStageFc1B, kStageFc2B)) return rc;
+    } else {
+      // FC2 of the first half pushes over NVLink from a few SMs while FC1 of the second half computes.
+      if (int rc = fc1(kFirstHalf, kStageFc1, rt->sms)) return rc;
+      WM_CUDA(cudaEventRecord(rt->ev_half_ready, stream));
+      WM_CUDA(cudaStreamWaitEvent(rt->push_stream, rt->ev_half_ready, 0));
+      if (int rc = fc2(kFirstHalf, kStageFc2, rt->push_sms, rt->push_stream)) return rc;
+      WM_CUDA(cudaEventRecord(rt->ev_half_pushed, rt->push_stream));
+      WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_second_pulled, 0));
+      if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
+      if (int rc = fc1(kSecondHalf, kStageFc1B, rt->sms - rt->push_sms)) return rc;
+      WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_half_pushed, 0));
+      if (int rc = fc2(kSecondHalf, kStageFc2B, rt->sms, stream)) return rc;
+    }
   }
   if (world > 1) {
     StageScope scope(timing, kStageSyncContrib, stream);
@@ -736,23 +770,25 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
   auto schedule = [&](int half) {
     return Schedule{split, tile_group, padded_start, rt->e_local, rt->row_cap, pair_tiles, many_rows, half};
   };
-  auto compute = [&](int half, int stage_du, int stage_sw, int stage_dx) -> int {
-    const Schedule sched = schedule(half);
+  auto du_and_swiglu = [&](int half, int stage_du, int stage_sw, int sms) -> int {
     {
       StageScope scope(timing, stage_du, stream);
-      if (int rc = launch_mgrouped_nn(sched, recv, static_cast<const __nv_bfloat16*>(w2), du, nullptr,
-                                      c.intermediate, c.hidden, status, rt->sms, stream))
+      if (int rc = launch_mgrouped_nn(schedule(half), recv, static_cast<const __nv_bfloat16*>(w2), du, nullptr,
+                                      c.intermediate, c.hidden, status, sms, stream))
         return rc;
     }
-    {
-      StageScope scope(timing, stage_sw, stream);
-      if (int rc = swiglu_backward(split_range(split, 2, half), ab, du, prob, origin, c.intermediate,
-                                   c.max_tokens, c.top_k, u, dab, dgate_box, rt->sms, stream))
-        return rc;
-    }
-    StageScope scope(timing, stage_dx, stream);
-    return launch_mgrouped_nn(sched, dab, static_cast<const __nv_bfloat16*>(w1), nullptr, &push,
-                              c.hidden, 2 * c.intermediate, status, rt->sms, stream);
+    StageScope scope(timing, stage_sw, stream);
+    return swiglu_backward(split_range(split, 2, half), ab, du, prob, origin, c.intermediate, c.max_tokens,
+                           c.top_k, u, dab, dgate_box, rt->sms, stream);
+  };
+  auto dx_push = [&](int half, int stage_dx, int sms, cudaStream_t st) -> int {
+    StageScope scope(timing, stage_dx, st);
+    return launch_mgrouped_nn(schedule(half), dab, static_cast<const __nv_bfloat16*>(w1), nullptr, &push,
+                              c.hidden, 2 * c.intermediate, status, sms, st);
+  };
+  auto compute = [&](int half, int stage_du, int stage_sw, int stage_dx) -> int {
+    if (int rc = du_and_swiglu(half, stage_du, stage_sw, rt->sms)) return rc;
+    return dx_push(half, stage_dx, rt->sms, stream);
   };
   if (!halves) {
     {
@@ -772,10 +808,24 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
       if (int rc = pull(kSecondHalf, rt->side)) return rc;
     }
     WM_CUDA(cudaEventRecord(rt->ev_second_pulled, rt->side));
-    if (int rc = compute(kFirstHalf, kStageDu, kStageSwigluBwd, kStageDx)) return rc;
-    WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_second_pulled, 0));
-    if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
-    if (int rc = compute(kSecondHalf, kStageDuB, kStageSwigluBwdB, kStageDxB)) return rc;
+    if (rt->push_sms == 0) {
+      if (int rc = compute(kFirstHalf, kStageDu, kStageSwigluBwd, kStageDx)) return rc;
+      WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_second_pulled, 0));
+      if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
+      if (int rc = compute(kSecondHalf, kStageDuB, kStageSwigluBwdB, kStageDxB)) return rc;
+    } else {
+      // dX of the first half pushes from a few SMs while dU and SwiGLU of the second half compute.
+      if (int rc = du_and_swiglu(kFirstHalf, kStageDu, kStageSwigluBwd, rt->sms)) return rc;
+      WM_CUDA(cudaEventRecord(rt->ev_half_ready, stream));
+      WM_CUDA(cudaStreamWaitEvent(rt->push_stream, rt->ev_half_ready, 0));
+      if (int rc = dx_push(kFirstHalf, kStageDx, rt->push_sms, rt->push_stream)) return rc;
+      WM_CUDA(cudaEventRecord(rt->ev_half_pushed, rt->push_stream));
+      WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_second_pulled, 0));
+      if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
+      if (int rc = du_and_swiglu(kSecondHalf, kStageDuB, kStageSwigluBwdB, rt->sms - rt->push_sms)) return rc;
+      WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_half_pushed, 0));
+      if (int rc = dx_push(kSecondHalf, kStageDxB, rt->sms, stream)) return rc;
+    }
   }
   const Schedule sched = schedule(kWhole);
   if (world > 1)
