@@ -1,9 +1,9 @@
 """Generate the golden fixtures in this folder by RUNNING THE REFERENCE's own code.
 
-Run in a container that has the reference checkout (default /root/reference) — the fixtures are
+Run in a container that has the reference checkout (path given with --reference) — the fixtures are
 committed because the GPU box has no reference.  Nothing here is imported by the product.
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference <checkout>]
 
 Outputs
   moe_small.pt        inputs + outputs of the reference's torch MoE layer

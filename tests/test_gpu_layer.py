@@ -32,7 +32,7 @@ def bits(t):
 
 
 @pytest.mark.parametrize("cfg", [
-    dict(experts=8, top_k=2, hidden=512, intermediate=512, tokens=256),      # BASELINE config 0 shape
+    dict(experts=8, top_k=2, hidden=512, intermediate=512, tokens=256),      # the CPU-runnable configuration's shape
     dict(experts=16, top_k=4, hidden=768, intermediate=384, tokens=301),     # 128-wide N tiles, ragged T
     dict(experts=32, top_k=8, hidden=2048, intermediate=512, tokens=96),     # mostly idle experts
     dict(experts=4, top_k=1, hidden=256, intermediate=128, tokens=5),
@@ -224,7 +224,7 @@ def test_decode_under_cuda_graph_replays_and_matches_eager_bits():
 
 
 def test_full_size_layer_repeats_is_batch_invariant_and_matches_the_oracle_on_samples():
-    """BASELINE configs[1] at EP1 (E=256, K=8, H=2048, I=512, 8192 tokens), where the whole-layer oracle would
+    """The headline training configuration at EP1 (E=256, K=8, H=2048, I=512, 8192 tokens), where the whole-layer oracle would
     take minutes: (1) forward + backward twice give identical bits; (2) a token's output does not depend on
     its batch: the first 1000 tokens alone reproduce their rows bit for bit; (3) sampled parity with the
     oracle: y and dX of a few tokens (they depend only on that token's row and its experts' weights) and

@@ -51,7 +51,7 @@ def test_nvfp4_forward_against_reference_formula(cfg):
 
 
 def test_nvfp4_calibrated_scales_for_unit_variance_inputs():
-    """BASELINE config 3 draws X ~ N(0,1): the default layer scales were chosen for x0.16 data, so the
+    """The NVFP4 inference configuration draws X ~ N(0,1): the default layer scales were chosen for x0.16 data, so the
     scales are calibrated (max |x| / (6 * 448) rule) and the same scales go to oracle and kernel."""
     cfg = dict(experts=8, top_k=2, hidden=512, intermediate=256, tokens=64)
     d, g = inputs(cfg, 11, 1.0, 0.02)

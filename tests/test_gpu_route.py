@@ -60,7 +60,7 @@ def test_empty_everywhere():
 
 @pytest.mark.parametrize("tokens", [8192, 20480])
 def test_full_size_properties(tokens):
-    """BASELINE shapes (E=256, K=8, 8 ranks): rows are a permutation, ordinals are stable."""
+    """Benchmark shapes (E=256, K=8, 8 ranks): rows are a permutation, ordinals are stable."""
     world, experts, top_k = 8, 256, 8
     g = torch.Generator().manual_seed(tokens)
     bias = torch.randn(experts, generator=g) * 0.5

@@ -54,7 +54,7 @@ def test_invalid_and_duplicate_routes():
 @pytest.mark.skipif(not (REFERENCE / "benchmarks/training_reference.py").is_file(),
                     reason="reference checkout not present")
 def test_reference_verify_step_accepts_the_oracle():
-    """BASELINE config 0 through the reference's verify_step (benchmarks/training_reference.py:15-79),
+    """The CPU-runnable FP32 configuration through the reference's verify_step (benchmarks/training_reference.py:15-79),
     gloo world 1, with a stub runtime that returns this oracle's tensors."""
     import torch.distributed as dist
     spec = importlib.util.spec_from_file_location("ref_training_reference", REFERENCE / "benchmarks/training_reference.py")
