@@ -11,6 +11,8 @@
 // All kernels are HBM/latency-bound integer work over T*K route words.
 #include "kernels.h"
 #include "ptx.cuh"
+#include <cstdlib>
+
 #include "route.h"
 
 namespace wm {
@@ -89,7 +91,7 @@ __global__ void chunk_scan_kernel(int* __restrict__ chunk_hist, int chunks, int 
 // rank as owner: padded row start per local expert, the 128-row tile -> expert map, tile count.
 __global__ void global_plan_kernel(const int* __restrict__ count_matrix, const int* flag_counts,
                                    int generation, int world, int rank, int experts,
-                                   int row_capacity, PlanTables t, int* status) {
+                                   int row_capacity, PlanTables t, int* status, int split_percent) {
   extern __shared__ int sh[];
   int* total = sh;               // [experts]
   int* padded = sh + experts;    // [experts]
@@ -159,10 +161,10 @@ __global__ void global_plan_kernel(const int* __restrict__ count_matrix, const i
     }
     *t.num_pairs = p;
     if (t.split != nullptr) {
-      // first expert boundary at or beyond half of the padded rows
+      // first expert boundary at or beyond split_percent of the padded rows (half by default)
       const int total_rows = *t.padded_rows;
       int rows = 0, l = 0;
-      while (l < e_local && 2 * rows < total_rows) rows += padded[rank * e_local + l++];
+      while (l < e_local && 100ll * rows < 1ll * split_percent * total_rows) rows += padded[rank * e_local + l++];
       t.split[0] = rows / 128;
       t.split[1] = total_rows / 128;
       t.split[2] = l < e_local ? pair_first[l] : p;
@@ -285,8 +287,15 @@ int route_local(const RouteShape& s, const int* routes, int tokens, RouteLocal o
 
 int route_global(const RouteShape& s, const int* count_matrix, const int* flag_counts,
                  int generation, int row_capacity, PlanTables t, int* status, cudaStream_t stream) {
+  // Share of the owner's rows in the first of the two halves that are pipelined at world > 1
+  // (WM_SPLIT_PERCENT, 10..90).
+  static const int split_percent = [] {
+    const char* v = std::getenv("WM_SPLIT_PERCENT");
+    const int n = v ? std::atoi(v) : 50;
+    return n >= 10 && n <= 90 ? n : 50;
+  }();
   global_plan_kernel<<<1, 1024, 2 * s.experts * sizeof(int), stream>>>(
-      count_matrix, flag_counts, generation, s.world, s.rank, s.experts, row_capacity, t, status);
+      count_matrix, flag_counts, generation, s.world, s.rank, s.experts, row_capacity, t, status, split_percent);
   count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
