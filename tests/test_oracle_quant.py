@@ -60,3 +60,19 @@ def test_nvfp4_midpoint_known_answer(golden):
     packed, sf, _ = c_oracle.nvfp4_quantize(mid["x"].float().numpy(), mid["scale"])
     assert (sf == mid["sf_byte"]).all()
     assert np.array_equal(packed, mid["packed"].numpy())
+
+
+def test_nvfp4_midpoint_known_answer_holds_in_both_orientations(golden):
+    """tests/torchrun_sm100_nvfp4_backward.py:29-45 checks the same block both along the columns and along
+    the rows (the weight-gradient operands are quantised along the rows): in the transposed matrix every
+    16-block again holds the maximum 0.1171875, so the scale byte is E4M3(0.75) and the codes are the
+    transpose of the row-wise codes (7 = 6.0 everywhere, 2 = 1.0 at rows 0 mod 4 x odd columns)."""
+    mid = torch.load(golden / "nvfp4_round.pt")["midpoint"]
+    x = mid["x"].float()
+    assert x.shape == (128, 128)
+    packed_t, sf_t, _ = c_oracle.nvfp4_quantize(x.T.contiguous().numpy(), mid["scale"])
+    assert (sf_t == mid["sf_byte"]).all()
+    codes = torch.full((128, 128), 7, dtype=torch.uint8)
+    codes[::4, 1::2] = 2
+    expected = codes.T.contiguous()
+    assert np.array_equal(packed_t, (expected[:, ::2] | (expected[:, 1::2] << 4)).numpy())
