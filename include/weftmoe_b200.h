@@ -183,6 +183,10 @@ typedef struct wm_route_out {
   int32_t* tile_group;    /* [row_capacity/128]                                                 */
   int32_t* num_tiles;     /* [1]                                                                */
   int32_t* padded_rows;   /* [1]                                                                */
+  int32_t* dst_primary;   /* [T*K] optional (NULL = skip): dst_prow of the token's first route (lowest
+                             combine position) to the same owner rank; equal to dst_prow for that route.
+                             At world > 1 only such rows are pulled over NVLink, the others are copied
+                             from them inside the owner.  -1 = no route                               */
 } wm_route_out;
 
 WM_API int wm_route_plan(int32_t phase, int32_t world, int32_t rank, int32_t experts, int32_t top_k,

@@ -63,11 +63,14 @@ def route_plan(world: int, experts: int, top_k: int, routes_per_rank: list[np.nd
         drank, drow, dprow = (np.zeros((t, top_k), np.int32) for _ in range(3))
         L.wm_oracle_route_rows(world, experts, top_k, r, ctypes.c_int64(t), _p(routes), _p(lo), _p(cm),
                                _p(base), _p(pbase), _p(drank), _p(drow), _p(dprow))
+        dprimary = np.zeros((t, top_k), np.int32)
+        L.wm_oracle_route_primary(experts, top_k, ctypes.c_int64(t), _p(routes), _p(drank), _p(dprow), _p(dprimary))
         pstart = np.zeros(e_local + 1, np.int32)
         tiles = np.zeros(max(1, int(padded_rows[r]) // 128), np.int32)
         n_tiles = L.wm_oracle_owner_tiles(world, experts, r, _p(total), _p(pstart), _p(tiles))
         out.append(dict(sorted_slot=ss, sorted_expert=se, local_offset=lo, count_matrix=cm.copy(),
-                        dst_rank=drank, dst_row=drow, dst_prow=dprow, expert_total=total.copy(),
+                        dst_rank=drank, dst_row=drow, dst_prow=dprow, dst_primary=dprimary,
+                        expert_total=total.copy(),
                         expert_base=base.copy(), expert_pbase=pbase.copy(), padded_start=pstart,
                         tile_group=tiles[:n_tiles].copy(), num_tiles=n_tiles,
                         padded_rows=int(padded_rows[r])))

@@ -104,6 +104,34 @@ void wm_oracle_route_rows(int world, int experts, int top_k, int rank, int64_t t
   }
 }
 
+/* Which row of the owner holds the only copy of the token's activation that crosses NVLink: a token
+ * routed to several experts of ONE owner rank is pulled once, into the row of its first such route in
+ * combine order (stable sort of the token's slots by expert id, src/cuda/weftmoe_pf/route_plan.cuh:29-50),
+ * and the token's other rows in that owner are copies of it.  dst_primary[i] = dst_prow of that first
+ * route (so dst_primary[i] == dst_prow[i] marks the pulled rows); -1 for invalid routes.  This is this
+ * build's transport choice; the reference pulls every routed row (routed_bf16.cuh:378-557), so the
+ * function is pinned by its definition only (hand-made cases in tests/test_oracle_route.py).        */
+void wm_oracle_route_primary(int experts, int top_k, int64_t tokens, const int32_t* routes,
+                             const int32_t* dst_rank, const int32_t* dst_prow, int32_t* dst_primary) {
+  for (int64_t t = 0; t < tokens; ++t) {
+    const int32_t* r = routes + t * top_k;
+    for (int s = 0; s < top_k; ++s) {
+      const int64_t i = t * top_k + s;
+      if (!valid_expert(r[s], experts)) {
+        dst_primary[i] = -1;
+        continue;
+      }
+      int head = s;
+      for (int o = 0; o < top_k; ++o) {
+        if (!valid_expert(r[o], experts) || dst_rank[t * top_k + o] != dst_rank[i]) continue;
+        /* earlier in the stable sort by expert id: smaller id, or equal id and smaller slot */
+        if (r[o] < r[head] || (r[o] == r[head] && o < head)) head = o;
+      }
+      dst_primary[i] = dst_prow[t * top_k + head];
+    }
+  }
+}
+
 /* Owner-side tables of `owner`: padded row start of every local expert [per_rank+1], the expert of
  * every 128-row tile, and the number of tiles.  Returns the number of tiles.                   */
 int wm_oracle_owner_tiles(int world, int experts, int owner, const int32_t* expert_total,

@@ -28,7 +28,7 @@ def device_route_plan(world, experts, top_k, routes_per_rank, cap=None, row_capa
                         dst_rank=i32(t, top_k), dst_row=i32(t, top_k), dst_prow=i32(t, top_k),
                         expert_total=i32(experts), expert_base=i32(experts), expert_pbase=i32(experts),
                         padded_start=i32(e_local + 1), tile_group=i32(row_capacity // 128 + 1),
-                        num_tiles=i32(1), padded_rows=i32(1))
+                        num_tiles=i32(1), padded_rows=i32(1), dst_primary=i32(t, top_k))
             out = _lib.WmRouteOut(**{k: v.data_ptr() for k, v in bufs.items()})
             rc = lib.wm_route_plan(phase, world, rank, experts, top_k, t, cap, row_capacity,
                                    _lib.ptr(r) if t else None, _lib.ptr(cm), ctypes.byref(out), None)

@@ -11,7 +11,7 @@ from tests.gpu_util import device_route_plan
 
 pytestmark = pytest.mark.gpu
 
-KEYS = ("sorted_slot", "sorted_expert", "local_offset", "dst_rank", "dst_row", "dst_prow")
+KEYS = ("sorted_slot", "sorted_expert", "local_offset", "dst_rank", "dst_row", "dst_prow", "dst_primary")
 OWNER_KEYS = ("expert_total", "expert_base", "expert_pbase", "padded_start", "tile_group")
 
 

@@ -68,3 +68,31 @@ def test_padded_layout_properties():
         for src in range(world):
             bad = (routes[src] < 0) | (routes[src] >= experts)
             assert (plan[src]["dst_prow"][bad] == -1).all()
+
+
+def test_primary_rows_hand_made_case_and_properties():
+    """One NVLink pull per (token, owner): dst_primary names the owner row that is pulled; the token's other
+    rows in that owner are copied from it.  Hand-made case: 2 ranks x 2 experts each, top-4."""
+    routes = [np.array([[3, 0, 1, 2],      # experts 0, 1 -> rank 0 (head = slot 1); 3, 2 -> rank 1 (head = slot 3)
+                        [1, 1, -1, 0],     # rank 0 three times: head = expert 0 (slot 3); duplicates of expert 1 copy
+                        [2, 2, 2, 2]],     # one expert four times: head = slot 0
+                       np.int32), np.zeros((0, 4), np.int32)]
+    p = c_oracle.route_plan(2, 4, 4, routes)[0]
+    prow, primary = p["dst_prow"], p["dst_primary"]
+    assert primary[0].tolist() == [prow[0, 3], prow[0, 1], prow[0, 1], prow[0, 3]]
+    assert primary[1].tolist() == [prow[1, 3], prow[1, 3], -1, prow[1, 3]]
+    assert primary[2].tolist() == [prow[2, 0]] * 4
+    # properties on random routes: the primary is a row of the same token and owner, never above the row
+    # itself (so the first pipelined half never waits for the second), and every (token, owner) has one
+    rng = np.random.default_rng(11)
+    world, experts, top_k = 4, 32, 8
+    routes = [rng.integers(-1, experts, size=(int(rng.integers(1, 200)), top_k)).astype(np.int32) for _ in range(world)]
+    for p in c_oracle.route_plan(world, experts, top_k, routes):
+        valid = p["dst_rank"] >= 0
+        assert ((p["dst_primary"] == -1) == ~valid).all()
+        assert (p["dst_primary"][valid] <= p["dst_prow"][valid]).all()
+        for t in range(p["dst_rank"].shape[0]):
+            for owner in set(p["dst_rank"][t][valid[t]].tolist()):
+                mine = p["dst_rank"][t] == owner
+                heads = p["dst_prow"][t][mine & (p["dst_primary"][t] == p["dst_prow"][t])]
+                assert len(heads) == 1 and (p["dst_primary"][t][mine] == heads[0]).all()

@@ -36,7 +36,7 @@ class WmRouteOut(Structure):
     _fields_ = [(name, c_void_p) for name in (
         "sorted_slot", "sorted_expert", "local_offset", "dst_rank", "dst_row", "dst_prow",
         "expert_total", "expert_base", "expert_pbase", "padded_start", "tile_group", "num_tiles",
-        "padded_rows")]
+        "padded_rows", "dst_primary")]
 
 
 # name -> (restype, argtypes); every entry is declared in include/weftmoe_b200.h

@@ -236,11 +236,14 @@ __global__ void route_rows_kernel(const int* __restrict__ routes, const float* _
 __global__ void route_primary_kernel(const int* __restrict__ slot_pos,
                                      const int* __restrict__ dst_rank,
                                      const int* __restrict__ dst_prow, int n, int top_k,
-                                     PeerInts meta_primary) {
+                                     PeerInts meta_primary, int* __restrict__ per_route) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int owner = dst_rank[i];
-  if (owner < 0) return;
+  if (owner < 0) {
+    if (per_route) per_route[i] = -1;
+    return;
+  }
   const int base = (i / top_k) * top_k;
   int head = i, head_pos = slot_pos[i];
   for (int j = 0; j < top_k; ++j) {
@@ -250,16 +253,17 @@ __global__ void route_primary_kernel(const int* __restrict__ slot_pos,
       head_pos = slot_pos[r];
     }
   }
-  meta_primary.p[owner][dst_prow[i]] = dst_prow[head];
+  if (meta_primary.p[owner] != nullptr) meta_primary.p[owner][dst_prow[i]] = dst_prow[head];
+  if (per_route) per_route[i] = dst_prow[head];
 }
 
 // ------------------------------------------------------------------ host side
 int route_primary(const RouteShape& s, int tokens, const RouteLocal& local, const RouteRows& rows,
-                  const PeerInts& meta_primary, cudaStream_t stream) {
+                  const PeerInts& meta_primary, int* per_route, cudaStream_t stream) {
   const int n = tokens * s.top_k;
   if (n == 0) return 0;
   route_primary_kernel<<<(n + 255) / 256, 256, 0, stream>>>(local.slot_pos, rows.dst_rank, rows.dst_prow, n,
-                                                           s.top_k, meta_primary);
+                                                           s.top_k, meta_primary, per_route);
   count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;

@@ -74,8 +74,10 @@ int route_rows(const RouteShape& s, const int* routes, const float* gates, int t
 // For every route, meta_primary[owner][row] = the owner row of the token's first route (lowest
 // combine position) to that owner; rows whose value is their own index are pulled, the others are
 // copied from that row inside the owner.
+// `per_route` (nullable) also receives that row per route, in route order (-1 = no route); entries of
+// meta_primary may be null (nothing is sent to that owner).
 int route_primary(const RouteShape& s, int tokens, const RouteLocal& local, const RouteRows& rows,
-                  const PeerInts& meta_primary, cudaStream_t stream);
+                  const PeerInts& meta_primary, int* per_route, cudaStream_t stream);
 
 // ------------------------------------------------------------------ transport (transport.cu)
 struct OwnerRows {

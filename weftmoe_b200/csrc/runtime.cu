@@ -601,7 +601,7 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
                             tables, rows, meta_origin, meta_prob, stream))
       return rc;
     if (world > 1)
-      if (int rc = route_primary(shape, tokens, local, rows, meta_primary, stream)) return rc;
+      if (int rc = route_primary(shape, tokens, local, rows, meta_primary, nullptr, stream)) return rc;
   }
   if (world > 1) {
     StageScope scope(timing, kStageSyncReady, stream);
@@ -1379,6 +1379,7 @@ extern "C" int wm_route_plan(int32_t phase, int32_t world, int32_t rank, int32_t
     if (!rc)
       rc = route_rows(shape, routes, nullptr, tokens, local, at<int>(tmp, o_hist), t, rows,
                       no_origin, no_prob, stream);
+    if (!rc && out->dst_primary) rc = route_primary(shape, tokens, local, rows, no_origin, out->dst_primary, stream);
     if (!rc && cudaMemcpyAsync(&device_code, tmp + o_status, sizeof(int), cudaMemcpyDeviceToHost,
                                stream) != cudaSuccess)
       rc = WM_ERR_CUDA;
