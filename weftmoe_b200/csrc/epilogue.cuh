@@ -176,6 +176,97 @@ struct EpilogueSwiglu {
   }
 };
 
+// dU epilogue with the SwiGLU backward fused in (reference math: weftmoe/blackwell_backward.py:81-113),
+// for the one-CTA kernel with EIGHT epilogue warps (two per TMEM lane quarter; `part` picks the half of the
+// tile's 256 columns): four warps would need longer for this arithmetic than the main loop of a tile.
+// The accumulator holds dU for intermediate columns n_tile*256 .. +255; it is rounded to BF16 (the value a
+// separate dU buffer would have held) and combined with the saved BF16 gate/up row:
+//   sig = sigmoid(a); silu = a*sig; U = bf16(silu*b*p)
+//   dA = bf16(dU*p*b*sig*(1+a*(1-sig))); dB = bf16(dU*p*silu); dprob += dU*silu*b
+// U, dA and dB leave one after the other through a 32-row x 32-column staging block (80-byte row pitch:
+// the eight lanes of a store phase hit distinct banks); the row's partial dprob over this warp's 128
+// columns goes to dprob_part[2*n_tile + part][row] and is summed in fixed order by dprob_finish.
+struct EpilogueSwigluBackward {
+  const __nv_bfloat16* ab;   // [rows, 2I] saved gate | up
+  const float* row_prob;     // [rows]
+  __nv_bfloat16* u;          // [rows, I]
+  __nv_bfloat16* dab;        // [rows, 2I]
+  float* dprob_part;         // [I / 128][row_capacity]
+  int inter;                 // I
+  int row_capacity;
+
+  __device__ __forceinline__ void flush(const uint8_t* stage, int lane, const uint32_t (&w)[16],
+                                        __nv_bfloat16* dst, long long ld) const {
+    constexpr int kPitch = 80;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      *reinterpret_cast<uint4*>(const_cast<uint8_t*>(stage) + lane * kPitch + j * 16) =
+          make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+    __syncwarp();
+    const int j = lane & 3;  // four lanes cover one 64-byte row segment: eight rows per store instruction
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int r = 8 * it + (lane >> 2);
+      *reinterpret_cast<uint4*>(dst + r * ld + j * 8) = *reinterpret_cast<const uint4*>(stage + r * kPitch + j * 16);
+    }
+    __syncwarp();
+  }
+
+  __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane,
+                                             bool zero, uint8_t* stage, int part) const {
+    const long long row0 = static_cast<long long>(t.m_tile) * kBlockM + q * 32;
+    const long long row = row0 + lane;
+    const float p = row_prob[row];
+    const int col0 = t.n_tile * 256 + part * 128;
+    const __nv_bfloat16* arow = ab + row * (2 * inter) + col0;
+    float dsum = 0.0f;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint4 va[4], vb[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        va[j] = reinterpret_cast<const uint4*>(arow + c * 32)[j];
+        vb[j] = reinterpret_cast<const uint4*>(arow + inter + c * 32)[j];
+      }
+      uint32_t d[32];
+      if (zero) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) d[j] = 0;
+      } else {
+        tmem_ld_32x32(taddr + part * 128 + c * 32, d);
+        tmem_ld_wait();
+      }
+      const uint32_t* wa = reinterpret_cast<const uint32_t*>(va);
+      const uint32_t* wb = reinterpret_cast<const uint32_t*>(vb);
+      uint32_t ou[16], oa[16], ob[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        float ru[2], ra[2], rb[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float a = __uint_as_float(h ? (wa[k] & 0xffff0000u) : (wa[k] << 16));
+          const float b = __uint_as_float(h ? (wb[k] & 0xffff0000u) : (wb[k] << 16));
+          const float du = bf16_round(__uint_as_float(d[2 * k + h]));
+          const float sig = __fdividef(1.0f, 1.0f + __expf(-a));
+          const float silu = a * sig;
+          const float act = silu * b;
+          ru[h] = act * p;
+          ra[h] = du * p * b * (sig * (1.0f + a * (1.0f - sig)));
+          rb[h] = du * p * silu;
+          dsum += du * act;
+        }
+        ou[k] = pack_bf16x2(ru[0], ru[1]);
+        oa[k] = pack_bf16x2(ra[0], ra[1]);
+        ob[k] = pack_bf16x2(rb[0], rb[1]);
+      }
+      flush(stage, lane, ou, u + row0 * inter + col0 + c * 32, inter);
+      flush(stage, lane, oa, dab + row0 * (2 * inter) + col0 + c * 32, 2 * inter);
+      flush(stage, lane, ob, dab + row0 * (2 * inter) + inter + col0 + c * 32, 2 * inter);
+    }
+    dprob_part[static_cast<long long>(2 * t.n_tile + part) * row_capacity + row] = dsum;
+  }
+};
+
 // Return epilogue (FC2 contributions and backward dX rows): each routed row is written as
 // BF16 into the SOURCE rank's mailbox [sorted_slot][token][N], local or over NVLink through
 // the peer-mapped arena (reference: routed_bf16.cuh:1028-1139 and

@@ -97,17 +97,17 @@ static bool use_pairs(const Schedule& s, bool backward_contraction) {
   return backward_contraction && s.many_rows_per_expert;
 }
 
-template <int BLOCK_N, bool A_MN, bool B_MN, bool GATE_UP, bool K_GROUPED, class Epi>
+template <int BLOCK_N, bool A_MN, bool B_MN, bool GATE_UP, bool K_GROUPED, class Epi, int EPI_WARPS = 4>
 static int launch_single(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
                          const Epi& epi, int sms, cudaStream_t stream) {
-  auto kernel = gemm_kernel<BLOCK_N, A_MN, B_MN, GATE_UP, K_GROUPED, Epi>;
+  auto kernel = gemm_kernel<BLOCK_N, A_MN, B_MN, GATE_UP, K_GROUPED, Epi, EPI_WARPS>;
   constexpr int smem = GemmSmem<BLOCK_N>::kTotal;
   static bool configured = false;  // one flag per template instantiation
   if (!configured) {
     WM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  kernel<<<sms, kGemmThreads, smem, stream>>>(ta, tb, args, epi);
+  kernel<<<sms, 64 + 32 * EPI_WARPS, smem, stream>>>(ta, tb, args, epi);
   WM_CUDA(cudaGetLastError());
   count_launch();
   return 0;
@@ -280,6 +280,23 @@ static int launch_mgrouped(const Schedule& s, const __nv_bfloat16* a_ptr, const 
   }
   EpilogueStore<128> epi{out, 0, n};
   return launch<128, false, B_MN, false, false>(pair, ta, tb, a, s, epi, sms, stream);
+}
+
+int launch_du_swiglu_backward(const Schedule& s, const __nv_bfloat16* dy_rows, const __nv_bfloat16* w2,
+                              const __nv_bfloat16* ab, const float* row_prob, __nv_bfloat16* u,
+                              __nv_bfloat16* dab, float* dprob_part, int inter, int hidden, int* status,
+                              int sms, cudaStream_t stream) {
+  if (inter % 256 || use_pairs(s, true)) return -1;
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap_2d(&ta, dy_rows, 2, hidden, s.row_capacity, (uint64_t)hidden * 2, 64, 128)) return rc;
+  if (int rc = make_tmap_2d(&tb, w2, 2, inter, (uint64_t)s.groups * hidden, (uint64_t)inter * 2, 64, 64)) return rc;
+  GemmArgs a = base_args(s, status);
+  a.n_tiles = inter / 256;
+  a.k_total = hidden;
+  a.b_group_rows = hidden;
+  TimelineScope timeline("du", a);
+  EpilogueSwigluBackward epi{ab, row_prob, u, dab, dprob_part, inter, s.row_capacity};
+  return launch_single<256, false, true, false, false, EpilogueSwigluBackward, 8>(ta, tb, a, epi, sms, stream);
 }
 
 int launch_mgrouped_nt(const Schedule& s, const __nv_bfloat16* a, const __nv_bfloat16* b,

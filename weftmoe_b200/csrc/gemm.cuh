@@ -119,8 +119,22 @@ __device__ __forceinline__ auto epilogue_finish(const Epilogue& e, int lane, int
 template <class Epilogue>
 __device__ __forceinline__ void epilogue_finish(const Epilogue&, int, long) {}
 
-template <int BLOCK_N, bool A_MN, bool B_MN, bool GATE_UP, bool K_GROUPED, class Epilogue>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// An epilogue may take a seventh argument, `part`: with EPI_WARPS = 8 two warps share each TMEM lane
+// quarter and the warp with part 0 / 1 handles the first / second half of the tile's columns.
+template <class Epilogue>
+__device__ __forceinline__ auto call_epilogue(const Epilogue& e, uint32_t taddr, const TileCoord& t, int q, int lane,
+                                              bool zero, uint8_t* stage, int part, int)
+    -> decltype(e(taddr, t, q, lane, zero, stage, part)) {
+  e(taddr, t, q, lane, zero, stage, part);
+}
+template <class Epilogue>
+__device__ __forceinline__ void call_epilogue(const Epilogue& e, uint32_t taddr, const TileCoord& t, int q, int lane,
+                                              bool zero, uint8_t* stage, int, long) {
+  e(taddr, t, q, lane, zero, stage);
+}
+
+template <int BLOCK_N, bool A_MN, bool B_MN, bool GATE_UP, bool K_GROUPED, class Epilogue, int EPI_WARPS = 4>
+__global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const GemmArgs args, const __grid_constant__ Epilogue epilogue) {
   using S = GemmSmem<BLOCK_N>;
@@ -151,7 +165,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(tmem_full + s, 1);
-      mbar_init(tmem_empty + s, 4);  // one arrival per epilogue warp
+      mbar_init(tmem_empty + s, EPI_WARPS);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -283,17 +297,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     int local_tile = 0;
     for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local_tile) {
       const bool stamp = args.timeline != nullptr && blockIdx.x == args.timeline_cta && local_tile < 64 && lane == 0;
-      unsigned long long* tl = args.timeline + local_tile * kTimelineTileStamps + 8 + (warp - 2);
+      unsigned long long* tl = args.timeline + local_tile * kTimelineTileStamps + 8 + ((warp - 2) & 3);
       const TileCoord t = decode_tile<K_GROUPED>(args, tile);
       ok = mbar_wait(tmem_full + acc, acc_phase, abort_flag, args.status, kStatusTimeoutTmemFull);
       if (!ok) break;
       if (stamp && warp == 2) tl[0] = global_timer_ns();
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
-      epilogue(taddr, t, q, lane, t.num_kb == 0, staging + (warp - 2) * (32 * 256));
+      call_epilogue(epilogue, taddr, t, q, lane, t.num_kb == 0,
+                    staging + (warp - 2) * (S::kStagingBytes / EPI_WARPS), (warp - 2) >> 2, 0);
       tc_fence_before();
       __syncwarp();
-      if (stamp && warp > 2) tl[0] = global_timer_ns();
+      if (stamp && warp > 2 && warp < 6) tl[0] = global_timer_ns();
       if (lane == 0) mbar_arrive(tmem_empty + acc);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }

@@ -69,6 +69,14 @@ int launch_mgrouped_nt(const Schedule& s, const __nv_bfloat16* a, const __nv_bfl
 int launch_mgrouped_nn(const Schedule& s, const __nv_bfloat16* a, const __nv_bfloat16* b,
                        __nv_bfloat16* out, const PushTarget* push, int n, int k, int* status,
                        int sms, cudaStream_t stream);
+// dU = dY rows * W2[e] (B MN-major, N = I, K = H) with the SwiGLU backward fused into the epilogue of
+// the one-CTA kernel (eight epilogue warps): writes U [rows, I], dAB [rows, 2I] and the dprob partials
+// [I / 128][row_capacity] instead of dU.  Needs I % 256 == 0; returns -1 (nothing launched) where the
+// CTA-pair kernel is the better choice for the shape, and the caller runs the two-kernel form.
+int launch_du_swiglu_backward(const Schedule& s, const __nv_bfloat16* dy_rows, const __nv_bfloat16* w2,
+                              const __nv_bfloat16* ab, const float* row_prob, __nv_bfloat16* u,
+                              __nv_bfloat16* dab, float* dprob_part, int inter, int hidden, int* status,
+                              int sms, cudaStream_t stream);
 // K-grouped: out[e][m, n] = sum over the expert's rows r of a[r, m] * b[r, n].
 int launch_kgrouped_tn(const Schedule& s, const __nv_bfloat16* a, const __nv_bfloat16* b,
                        __nv_bfloat16* out, int m, int n, int* status, int sms,

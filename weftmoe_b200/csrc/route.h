@@ -120,6 +120,10 @@ int unpermute_dgates(const float* dgate_box, const int* sorted_slot, const int* 
                      int tokens, int top_k, float* dgates, cudaStream_t stream);
 // Owner side, backward elementwise: from saved gate/up (ab), dU and prob compute
 // U = bf16(silu(a) b p), dAB, and the per-row dprob, which is sent to the source's dgate box.
+// Finish of the fused dU + SwiGLU-backward epilogue: sum the per-block dprob partials of each row in
+// block order and send them to the sources' dprob boxes.
+int dprob_finish(DeviceRange rows, const float* part, int blocks, int row_capacity, const int* origin, int cap,
+                 int top_k, const PeerFloats& dgate_box, cudaStream_t stream);
 int swiglu_backward(DeviceRange rows, const __nv_bfloat16* ab, const __nv_bfloat16* du,
                     const float* prob, const int* origin, int inter, int cap, int top_k,
                     __nv_bfloat16* u, __nv_bfloat16* dab, const PeerFloats& dgate_box, int sms,

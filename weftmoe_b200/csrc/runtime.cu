@@ -72,7 +72,7 @@ struct ScratchLayout {
   size_t status, sorted_slot, sorted_expert, slot_pos, local_offset, dst_rank, dst_row, dst_prow,
       chunk_hist, local_count, expert_total, expert_before, expert_base, expert_pbase, padded_start,
       tile_group, num_tiles, padded_rows, pair_tiles, num_pairs, split, origin, prob, xrows, u, recv, du,
-      dab, abq, sfa_x, sfa_u, primary, wq_a, wq_b, wsf_a, wsf_b, wt, total;
+      dab, abq, sfa_x, sfa_u, primary, wq_a, wq_b, wsf_a, wsf_b, wt, dprob_part, total;
 };
 // Training cache carved out of the caller's tape buffer.
 struct TapeLayout {
@@ -173,6 +173,7 @@ ScratchLayout scratch_layout(const wm_config& c, int row_cap) {
     s.recv = k.take(2ull * row_cap * c.hidden);
     s.du = k.take(2ull * row_cap * c.intermediate);
     s.dab = k.take(4ull * row_cap * c.intermediate);
+    s.dprob_part = k.take(sizeof(float) * row_cap * ((c.intermediate + 127) / 128));
   }
   if (c.training && c.reserved == 1) {
     // FP8 weight gradients: both operands of each contraction, re-quantised along the rows and stored
@@ -778,7 +779,28 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
   auto schedule = [&](int half) {
     return Schedule{split, tile_group, padded_start, rt->e_local, rt->row_cap, pair_tiles, many_rows, half};
   };
+  // dU with the SwiGLU backward in its epilogue (no dU buffer, no separate elementwise pass) where the
+  // one-CTA kernel runs dU and I is a multiple of 256; WM_FUSED_DU=0 keeps the two-kernel form.
+  static const bool fused_allowed = [] {
+    const char* v = std::getenv("WM_FUSED_DU");
+    return !(v && v[0] == '0');
+  }();
+  auto* dprob_part = at<float>(S, rt->sl.dprob_part);
   auto du_and_swiglu = [&](int half, int stage_du, int stage_sw, int sms) -> int {
+    if (fused_allowed) {
+      int rc;
+      {
+        StageScope scope(timing, stage_du, stream);
+        rc = launch_du_swiglu_backward(schedule(half), recv, static_cast<const __nv_bfloat16*>(w2), ab, prob, u,
+                                       dab, dprob_part, c.intermediate, c.hidden, status, sms, stream);
+      }
+      if (rc > 0) return rc;
+      if (rc == 0) {
+        StageScope scope(timing, stage_sw, stream);
+        return dprob_finish(split_range(split, 2, half), dprob_part, c.intermediate / 128, rt->row_cap, origin,
+                            c.max_tokens, c.top_k, dgate_box, stream);
+      }
+    }
     {
       StageScope scope(timing, stage_du, stream);
       if (int rc = launch_mgrouped_nn(schedule(half), recv, static_cast<const __nv_bfloat16*>(w2), du, nullptr,

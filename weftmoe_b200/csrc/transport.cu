@@ -289,6 +289,30 @@ __global__ void swiglu_backward_kernel(DeviceRange range, const __nv_bfloat16* _
     }
   }
 }
+// dprob of a row = its partial sums over the column blocks of the fused dU epilogue, added in block
+// order; sent to the source rank's dprob box like swiglu_backward does.
+__global__ void dprob_finish_kernel(DeviceRange range, const float* __restrict__ part, int blocks,
+                                    int row_capacity, const int* __restrict__ origin, int cap, int top_k,
+                                    PeerFloats dgate_box) {
+  const int rows = *range.end;
+  for (int r = *range.begin + blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += gridDim.x * blockDim.x) {
+    const int org = origin[r];
+    if (org < 0) continue;
+    float sum = 0.0f;
+    for (int t = 0; t < blocks; ++t) sum += part[static_cast<size_t>(t) * row_capacity + r];
+    const int per = cap * top_k;
+    const int src = org / per;
+    dgate_box.p[src][org - src * per] = sum;
+  }
+}
+int dprob_finish(DeviceRange rows, const float* part, int blocks, int row_capacity, const int* origin, int cap,
+                 int top_k, const PeerFloats& dgate_box, cudaStream_t stream) {
+  dprob_finish_kernel<<<256, 256, 0, stream>>>(rows, part, blocks, row_capacity, origin, cap, top_k, dgate_box);
+  count_launch();
+  WM_CUDA(cudaGetLastError());
+  return 0;
+}
+
 int swiglu_backward(DeviceRange rows, const __nv_bfloat16* ab, const __nv_bfloat16* du,
                     const float* prob, const int* origin, int inter, int cap, int top_k,
                     __nv_bfloat16* u, __nv_bfloat16* dab, const PeerFloats& dgate_box, int sms,
