@@ -505,6 +505,19 @@ extern "C" int wm_status_poll(wm_runtime* rt, int32_t* code, void* stream_) {
   return WM_OK;
 }
 
+// The cross-rank flags carry generation numbers that are launch arguments: a captured multi-rank call
+// would replay with stale generations and its waits would pass without synchronising.  Refuse it.
+static int refuse_multirank_capture(const wm_runtime* rt, cudaStream_t stream, const char* what) {
+  if (rt->cfg.world == 1) return 0;
+  cudaStreamCaptureStatus state = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &state) == cudaSuccess && state != cudaStreamCaptureStatusNone) {
+    set_error("%s: CUDA-graph capture is supported for single-rank runtimes only (the cross-rank flags "
+              "carry per-call generation numbers); run multi-rank calls eagerly", what);
+    return WM_ERR_STATE;
+  }
+  return 0;
+}
+
 // =============================================================================== forward
 extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, const float* gates,
                           const void* w1, const void* w2, int32_t tokens, void* y, void* tape,
@@ -526,6 +539,7 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
     return WM_ERR_STATE;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (int rc = refuse_multirank_capture(rt, stream, "wm_forward")) return rc;
   const int gen = ++rt->generation;
   const int world = c.world;
   uint8_t* S = rt->scratch;
@@ -713,6 +727,7 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
     return WM_ERR_INVALID;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (int rc = refuse_multirank_capture(rt, stream, "wm_backward")) return rc;
   const int gen = ++rt->generation;
   const int world = c.world;
   uint8_t* S = rt->scratch;
@@ -918,6 +933,7 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
     return WM_ERR_STATE;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (int rc = refuse_multirank_capture(rt, stream, "wm_forward_quantized")) return rc;
   const int gen = ++rt->generation;
   const int world = c.world;
   const int H = c.hidden, I = c.intermediate;
@@ -1071,6 +1087,7 @@ static int backward_nvfp4(wm_runtime* rt, const void* tape, const void* dy, cons
     return WM_ERR_INVALID;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (int rc = refuse_multirank_capture(rt, stream, "wm_backward_quantized")) return rc;
   const int gen = ++rt->generation;
   const int world = c.world;
   uint8_t* S = rt->scratch;
@@ -1211,6 +1228,7 @@ extern "C" int wm_backward_quantized(wm_runtime* rt, const void* tape, const voi
     return WM_ERR_INVALID;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (int rc = refuse_multirank_capture(rt, stream, "wm_backward_quantized")) return rc;
   const int gen = ++rt->generation;
   const int world = c.world;
   const int H = c.hidden, I = c.intermediate;
