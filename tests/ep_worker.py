@@ -90,6 +90,35 @@ def main():
         ep1.close()
         if rank == 0:
             print(f"EP{world} {scenario}: oracle parity, bitwise repeat and EP1 == EP{world} bits passed", flush=True)
+    # ---- decode under a CUDA graph across ranks (DT contract, docs/usage.md:104-112): the multi-stream
+    #      forward is captured by the caller's graph; every replay advances the device-side generation
+    #      of the cross-rank flags, reads fresh inputs from the same addresses and gives the eager bits
+    inf = TensorRuntime(group=dist.group.WORLD, experts=E, top_k=K, hidden=H, intermediate=I,
+                        max_tokens=cap, max_rows=sum(counts) * K, training=False)
+    eager = inf.inference_eager(x, routes, gates, lw1, lw2).clone()
+    x2 = (x * 0.5).contiguous()
+    eager2 = inf.inference_eager(x2, routes, gates, lw1, lw2).clone()
+    xg = x.clone()
+    inf.inference(0, xg, routes, gates, lw1, lw2)             # warm-up of this layer outside capture
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y_graph = inf.inference(0, xg, routes, gates, lw1, lw2)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(bits(y_graph), bits(eager)), "graph replay differs from eager"
+    xg.copy_(x2)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(bits(y_graph), bits(eager2)), "graph replay with new inputs differs from eager"
+    # eager calls still line up with the peers after the replays (generations stayed in step)
+    assert torch.equal(bits(inf.inference_eager(x, routes, gates, lw1, lw2)), bits(eager))
+    del graph
+    inf.close()
+    if rank == 0:
+        print(f"EP{world} decode under a CUDA graph: replays == eager bits passed", flush=True)
     # ---- quantised inference (NVFP4 and blockwise FP8) over the EP group: EPn bits == EP1 bits
     from weftmoe_b200.fp8 import prepare_fp8_weights
     from weftmoe_b200.nvfp4 import prepare_nvfp4_weights

@@ -90,7 +90,7 @@ __global__ void chunk_scan_kernel(int* __restrict__ chunk_hist, int chunks, int 
 // total rows, rows from lower ranks, unpadded and padded base inside the owner; and for this
 // rank as owner: padded row start per local expert, the 128-row tile -> expert map, tile count.
 __global__ void global_plan_kernel(const int* __restrict__ count_matrix, const int* flag_counts,
-                                   int generation, int world, int rank, int experts,
+                                   Gen gen, int world, int rank, int experts,
                                    int row_capacity, PlanTables t, int* status, int split_percent) {
   extern __shared__ int sh[];
   int* total = sh;               // [experts]
@@ -99,7 +99,7 @@ __global__ void global_plan_kernel(const int* __restrict__ count_matrix, const i
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
   if (threadIdx.x < world) {
-    if (!wait_flag_ge(flag_counts + threadIdx.x * kFlagStride, generation, status)) ok = 0;
+    if (!wait_flag_ge(flag_counts + threadIdx.x * kFlagStride, gen.value(), status)) ok = 0;
   }
   __syncthreads();
   const int e_local = experts / world;
@@ -290,7 +290,7 @@ int route_local(const RouteShape& s, const int* routes, int tokens, RouteLocal o
 }
 
 int route_global(const RouteShape& s, const int* count_matrix, const int* flag_counts,
-                 int generation, int row_capacity, PlanTables t, int* status, cudaStream_t stream) {
+                 Gen generation, int row_capacity, PlanTables t, int* status, cudaStream_t stream) {
   // Share of the owner's rows in the first of the two halves that are pipelined at world > 1
   // (WM_SPLIT_PERCENT, 10..90).
   static const int split_percent = [] {

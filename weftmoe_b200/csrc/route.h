@@ -13,6 +13,18 @@ struct PeerFloats { float* p[kMaxWorld]; };
 struct PeerRows { __nv_bfloat16* p[kMaxWorld]; };
 struct PeerConstRows { const __nv_bfloat16* p[kMaxWorld]; };
 
+// A generation number that kernels read on the device: *dev + delta (dev == nullptr: just delta).
+// The runtime bumps *dev with a one-thread kernel at the start of every multi-rank call, so a call
+// captured in a CUDA graph advances the generation at every replay.
+struct Gen {
+  const int* dev = nullptr;
+  int delta = 0;
+  Gen operator-(int d) const { return Gen{dev, delta - d}; }
+#ifdef __CUDACC__
+  __device__ __forceinline__ int value() const { return (dev ? *dev : 0) + delta; }
+#endif
+};
+
 struct RouteShape {
   int experts, top_k, world, rank, cap;  // cap = token capacity per rank
 };
@@ -65,7 +77,7 @@ int route_local(const RouteShape& s, const int* routes, int tokens, RouteLocal o
                 int* chunk_hist, int* local_count, const PeerInts& count_matrix,
                 cudaStream_t stream);
 int route_global(const RouteShape& s, const int* count_matrix, const int* flag_counts,
-                 int generation, int row_capacity, PlanTables t, int* status, cudaStream_t stream);
+                 Gen generation, int row_capacity, PlanTables t, int* status, cudaStream_t stream);
 int route_rows(const RouteShape& s, const int* routes, const float* gates, int tokens,
                const RouteLocal& local, const int* chunk_base, PlanTables t, RouteRows out,
                const PeerInts& meta_origin, const PeerFloats& meta_prob, cudaStream_t stream);
@@ -88,9 +100,9 @@ struct OwnerRows {
 };
 
 // Wait until flags[r] >= generation for r < world (bounded); flags are kFlagStride apart.
-int wait_flags(const int* flags, int world, int generation, int* status, cudaStream_t stream);
+int wait_flags(const int* flags, int world, Gen generation, int* status, cudaStream_t stream);
 // Store `generation` into flag slot `slot` of every rank's flag group (peer-mapped).
-int signal_peers(const PeerInts& flag_group, int world, int slot, int generation,
+int signal_peers(const PeerInts& flag_group, int world, int slot, Gen generation,
                  cudaStream_t stream);
 
 // The row-copy kernels take their CTA count: 8 CTAs of 8 warps per SM when they run alone (enough

@@ -72,7 +72,7 @@ struct ScratchLayout {
   size_t status, sorted_slot, sorted_expert, slot_pos, local_offset, dst_rank, dst_row, dst_prow,
       chunk_hist, local_count, expert_total, expert_before, expert_base, expert_pbase, padded_start,
       tile_group, num_tiles, padded_rows, pair_tiles, num_pairs, split, origin, prob, xrows, u, recv, du,
-      dab, abq, sfa_x, sfa_u, primary, wq_a, wq_b, wsf_a, wsf_b, wt, dprob_part, total;
+      dab, abq, sfa_x, sfa_u, primary, wq_a, wq_b, wsf_a, wsf_b, wt, dprob_part, gen, total;
 };
 // Training cache carved out of the caller's tape buffer.
 struct TapeLayout {
@@ -137,6 +137,7 @@ ScratchLayout scratch_layout(const wm_config& c, int row_cap) {
   const size_t chunks = (routes + 1023) / 1024 + 1;
   const int e_local = c.experts / c.world;
   s.status = k.take(sizeof(int) * 4);
+  s.gen = k.take(sizeof(int));  // device copy of the call generation (bumped by a kernel per call)
   s.sorted_slot = k.take(sizeof(int) * routes);
   s.sorted_expert = k.take(sizeof(int) * routes);
   s.slot_pos = k.take(sizeof(int) * routes);
@@ -374,6 +375,7 @@ extern "C" int wm_runtime_create(const wm_config* config, wm_runtime** out) {
   // and synchronised so that peers may write as soon as they have imported the handle.
   e = cudaMemset(rt->arena, 0, rt->al.stage);
   if (e == cudaSuccess) e = cudaMemset(rt->scratch + rt->sl.status, 0, sizeof(int) * 4);
+  if (e == cudaSuccess) e = cudaMemset(rt->scratch + rt->sl.gen, 0, sizeof(int));
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     set_error("workspace initialisation failed: %s", cudaGetErrorString(e));
@@ -505,17 +507,17 @@ extern "C" int wm_status_poll(wm_runtime* rt, int32_t* code, void* stream_) {
   return WM_OK;
 }
 
-// The cross-rank flags carry generation numbers that are launch arguments: a captured multi-rank call
-// would replay with stale generations and its waits would pass without synchronising.  Refuse it.
-static int refuse_multirank_capture(const wm_runtime* rt, cudaStream_t stream, const char* what) {
-  if (rt->cfg.world == 1) return 0;
-  cudaStreamCaptureStatus state = cudaStreamCaptureStatusNone;
-  if (cudaStreamIsCapturing(stream, &state) == cudaSuccess && state != cudaStreamCaptureStatusNone) {
-    set_error("%s: CUDA-graph capture is supported for single-rank runtimes only (the cross-rank flags "
-              "carry per-call generation numbers); run multi-rank calls eagerly", what);
-    return WM_ERR_STATE;
-  }
-  return 0;
+// Every collective call takes the next generation.  At world > 1 the number lives on the device and is
+// bumped by a one-thread kernel on the call's stream, so that the flag kernels of a call captured in a
+// CUDA graph see a new generation at every replay.
+__global__ void bump_generation_kernel(int* gen) { *gen += 1; }
+static Gen begin_generation(wm_runtime* rt, cudaStream_t stream) {
+  ++rt->generation;
+  if (rt->cfg.world == 1) return Gen{nullptr, rt->generation};
+  int* dev = reinterpret_cast<int*>(rt->scratch + rt->sl.gen);
+  bump_generation_kernel<<<1, 1, 0, stream>>>(dev);
+  count_launch();
+  return Gen{dev, 0};
 }
 
 // =============================================================================== forward
@@ -539,8 +541,7 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
     return WM_ERR_STATE;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (int rc = refuse_multirank_capture(rt, stream, "wm_forward")) return rc;
-  const int gen = ++rt->generation;
+  const Gen gen = begin_generation(rt, stream);
   const int world = c.world;
   uint8_t* S = rt->scratch;
   uint8_t* T = static_cast<uint8_t*>(tape);
@@ -608,7 +609,7 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
     if (world > 1)
       if (int rc = signal_peers(flag_group(rt, kCounts), world, c.rank, gen, stream)) return rc;
     if (int rc = route_global(shape, at<int>(rt->arena, rt->al.counts), my_flags(rt, kCounts),
-                              world > 1 ? gen : 0, rt->row_cap, tables, status, stream))
+                              world > 1 ? gen : Gen{}, rt->row_cap, tables, status, stream))
       return rc;
     RouteRows rows{at<int>(S, rt->sl.local_offset), at<int>(S, rt->sl.dst_rank),
                    at<int>(S, rt->sl.dst_row), at<int>(S, rt->sl.dst_prow)};
@@ -727,8 +728,7 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
     return WM_ERR_INVALID;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (int rc = refuse_multirank_capture(rt, stream, "wm_backward")) return rc;
-  const int gen = ++rt->generation;
+  const Gen gen = begin_generation(rt, stream);
   const int world = c.world;
   uint8_t* S = rt->scratch;
   const uint8_t* T = static_cast<const uint8_t*>(tape);
@@ -933,8 +933,7 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
     return WM_ERR_STATE;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (int rc = refuse_multirank_capture(rt, stream, "wm_forward_quantized")) return rc;
-  const int gen = ++rt->generation;
+  const Gen gen = begin_generation(rt, stream);
   const int world = c.world;
   const int H = c.hidden, I = c.intermediate;
   uint8_t* S = rt->scratch;
@@ -1006,7 +1005,7 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
   if (world > 1)
     if (int rc = signal_peers(flag_group(rt, kCounts), world, c.rank, gen, stream)) return rc;
   if (int rc = route_global(shape, at<int>(rt->arena, rt->al.counts), my_flags(rt, kCounts),
-                            world > 1 ? gen : 0, rt->row_cap, tables, status, stream))
+                            world > 1 ? gen : Gen{}, rt->row_cap, tables, status, stream))
     return rc;
   RouteRows rows{at<int>(S, rt->sl.local_offset), at<int>(S, rt->sl.dst_rank), at<int>(S, rt->sl.dst_row),
                  at<int>(S, rt->sl.dst_prow)};
@@ -1087,8 +1086,7 @@ static int backward_nvfp4(wm_runtime* rt, const void* tape, const void* dy, cons
     return WM_ERR_INVALID;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (int rc = refuse_multirank_capture(rt, stream, "wm_backward_quantized")) return rc;
-  const int gen = ++rt->generation;
+  const Gen gen = begin_generation(rt, stream);
   const int world = c.world;
   uint8_t* S = rt->scratch;
   const uint8_t* T = static_cast<const uint8_t*>(tape);
@@ -1228,8 +1226,7 @@ extern "C" int wm_backward_quantized(wm_runtime* rt, const void* tape, const voi
     return WM_ERR_INVALID;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (int rc = refuse_multirank_capture(rt, stream, "wm_backward_quantized")) return rc;
-  const int gen = ++rt->generation;
+  const Gen gen = begin_generation(rt, stream);
   const int world = c.world;
   const int H = c.hidden, I = c.intermediate;
   uint8_t* S = rt->scratch;
@@ -1411,7 +1408,7 @@ extern "C" int wm_route_plan(int32_t phase, int32_t world, int32_t rank, int32_t
                  out->padded_start, out->tile_group, out->num_tiles, out->padded_rows,
                  at<int>(tmp, o_pairs) + 1, at<int>(tmp, o_pairs)};
     // No exchange to wait for: generation 0 is satisfied by the zeroed flag words.
-    rc = route_global(shape, count_matrix, at<int>(tmp, o_flags), 0, row_capacity, t,
+    rc = route_global(shape, count_matrix, at<int>(tmp, o_flags), Gen{}, row_capacity, t,
                       at<int>(tmp, o_status), stream);
     RouteRows rows{out->local_offset, out->dst_rank, out->dst_row, out->dst_prow};
     PeerInts no_origin{};

@@ -16,22 +16,23 @@
 namespace wm {
 
 // ------------------------------------------------------------------ flags
-__global__ void wait_flags_kernel(const int* flags, int world, int generation, int* status) {
-  if (threadIdx.x < world) wait_flag_ge(flags + threadIdx.x * kFlagStride, generation, status);
+__global__ void wait_flags_kernel(const int* flags, int world, Gen generation, int* status) {
+  if (threadIdx.x < world) wait_flag_ge(flags + threadIdx.x * kFlagStride, generation.value(), status);
 }
-__global__ void signal_peers_kernel(PeerInts group, int world, int slot, int generation) {
+__global__ void signal_peers_kernel(PeerInts group, int world, int slot, Gen gen) {
+  const int generation = gen.value();
   if (threadIdx.x < world) {
     __threadfence_system();
     st_release_sys(group.p[threadIdx.x] + slot * kFlagStride, generation);
   }
 }
-int wait_flags(const int* flags, int world, int generation, int* status, cudaStream_t stream) {
+int wait_flags(const int* flags, int world, Gen generation, int* status, cudaStream_t stream) {
   wait_flags_kernel<<<1, 32, 0, stream>>>(flags, world, generation, status);
   count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
 }
-int signal_peers(const PeerInts& group, int world, int slot, int generation, cudaStream_t stream) {
+int signal_peers(const PeerInts& group, int world, int slot, Gen generation, cudaStream_t stream) {
   signal_peers_kernel<<<1, 32, 0, stream>>>(group, world, slot, generation);
   count_launch();
   WM_CUDA(cudaGetLastError());
