@@ -234,14 +234,16 @@ WM_API int wm_nvfp4_gemm(const void* a, const void* a_sf, const void* b, const v
                          int32_t m, int32_t n, int32_t k, float alpha, int32_t out_is_f32, void* stream);
 
 /* Route planning for callers that must not allocate.  It has no counterpart in the reference.
- * Same arguments, outputs and phases as wm_route_plan, but no cudaMalloc/cudaFree: the temporaries
- * live in a fixed 1 MiB __device__ array inside the library (held by every GPU that loads it until
- * the process exits).  Meant for hosts whose own pool owns all free HBM, and for latency-critical
+ * Same arguments, outputs (dst_primary included) and phases as wm_route_plan, but no
+ * cudaMalloc/cudaFree: the temporaries live in a fixed 1 MiB __device__ array inside the library
+ * (held by every GPU that loads it until the process exits).  Meant for hosts whose own pool owns all free HBM, and for latency-critical
  * paths where cudaMalloc's device-wide synchronisation would stall every stream.
  * Limits: tokens * top_k <= 131072, experts <= 512, row_capacity <= 262144; larger requests return
  * WM_ERR_CAPACITY with a message that names the limit.  The first call on a device looks up the
- * array's device address (cudaGetSymbolAddress); make that first call outside stream capture.
- * All calls on a device share the array, so calls whose GPU work overlaps race: serialise them. */
+ * array's device address (cudaGetSymbolAddress); make that first call before any stream capture.
+ * Every call, like wm_route_plan, ends by synchronising `stream` and reading the device status word
+ * on the host.  All calls on a device share the array, so calls whose GPU work overlaps race:
+ * serialise them. */
 WM_API int wm_route_plan_noalloc(int32_t phase, int32_t world, int32_t rank, int32_t experts,
                                  int32_t top_k, int32_t tokens, int32_t cap, int32_t row_capacity,
                                  const int32_t* routes, int32_t* count_matrix, const wm_route_out* out,
@@ -262,6 +264,17 @@ WM_API int wm_debug_grouped_gemm(int kind, const void* a, const void* b, void* o
  * one-CTA kernel, 1 the CTA-pair (cta_group::2) kernel.  No counterpart in the reference, whose
  * tile heuristic lives in weftmoe/blackwell_cutlass.py:80-88. */
 WM_API void wm_debug_force_gemm_pairs(int mode);
+
+/* Diagnostics of the bounded cross-rank waits (reference: the transport deadline,
+ * ActivationTransportRunOptions.deadline_after -> NotifyErrorCode::TransportTimeout,
+ * include/weftmoe/cuda/activation_transport.hpp:169-175, src/cuda/activation_transport/execution.cuh:1243-1250).
+ * wm_debug_set_wait_budget: process-wide budget, in SM clock cycles, of every wait on a generation flag
+ *   (cycles <= 0 restores the default of about two seconds).  Applies to launches made afterwards.
+ * wm_debug_wait_flag: enqueue one flag wait of `rt` on a caller-owned device word: the kernel returns
+ *   when *flag_word >= target or when the budget runs out; in that case the runtime's status word is
+ *   set and the next wm_status_poll reports WM_ERR_TIMEOUT (and clears it).  Nothing traps or spins on. */
+WM_API int wm_debug_set_wait_budget(long long cycles);
+WM_API int wm_debug_wait_flag(wm_runtime* rt, const int32_t* flag_word, int32_t target, void* stream);
 
 #ifdef __cplusplus
 }

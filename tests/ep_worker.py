@@ -189,13 +189,157 @@ def main():
         failed = True
     flags = [None] * world
     dist.all_gather_object(flags, failed)
-    assert flags[0], "rank 0 must report the overflow"
+    # every rank holds the same count matrix, so every rank reports the owner's overflow
+    # (the reference fails collectively too: src/metadata/notify_dispatch.cpp:2003-2035)
+    assert all(flags), f"all ranks must report the overflow, got {flags}"
     y = small.inference_eager(x[:4], routes[:4], gates[:4], lw1, lw2)
     assert torch.isfinite(y.float()).all()
     small.close()
     if rank == 0:
         print(f"EP{world} overflow reporting passed", flush=True)
+    if os.environ.get("WM_EP_HEADLINE", "1") != "0":
+        headline_scenario(rank, world)
+    absent_rank_scenario(rank, world, w1, w2, E, K, H, I)
     dist.destroy_process_group()
+
+
+def headline_scenario(rank, world):
+    """The headline training shape over the EP group (E=256, K=8, H=2048, I=512, 8192 tokens per rank, router
+    bias shared by all ranks so that owners are unevenly loaded).  The whole-layer oracle would take minutes
+    per rank, so parity is sampled the way tests/test_gpu_layer.py does at EP1:
+      * forward + backward twice: all five tensors repeat bit for bit;
+      * y / dX / dprob of a few of this rank's tokens against the oracle (they depend only on the token's
+        row and the weights of the experts it is routed to, wherever those live);
+      * dW1 / dW2 of this rank's most and least loaded expert against the oracle (they depend only on the
+        rows routed to that expert, from every rank);
+      * this rank's first 256 tokens through an EP1 runtime holding all experts: same forward bits.
+    Every rank regenerates the other ranks' seeded inputs on its own GPU (same seed, same Philox stream)."""
+    E, K, H, I, T = 256, 8, 2048, 512, 8192
+    e_local = E // world
+    dev = torch.device("cuda", torch.cuda.current_device())
+
+    def rank_inputs(r):
+        g = torch.Generator(device=dev).manual_seed(9000 + r)
+        x = torch.randn(T, H, device=dev, generator=g).bfloat16()
+        dy = torch.randn(T, H, device=dev, generator=g).bfloat16()
+        logits = torch.randn(T, E, device=dev, generator=g)
+        bias = torch.randn(E, device=dev, generator=torch.Generator(device=dev).manual_seed(77)) * 0.5
+        scores, routes = (logits + bias).topk(K, dim=-1)
+        return x, dy, routes.int().contiguous(), scores.softmax(-1).float().contiguous()
+
+    def rank_weights(r):
+        g = torch.Generator(device=dev).manual_seed(500 + r)
+        w1 = (torch.randn(e_local, 2 * I, H, device=dev, generator=g) * 0.02).bfloat16()
+        w2 = (torch.randn(e_local, H, I, device=dev, generator=g) * 0.02).bfloat16()
+        return w1, w2
+
+    x, dy, routes, gates = rank_inputs(rank)
+    w1, w2 = rank_weights(rank)
+    rt = TensorRuntime(group=dist.group.WORLD, experts=E, top_k=K, hidden=H, intermediate=I, max_tokens=T,
+                       max_rows=2 * T * K, training=True, max_saved=1)
+    runs = []
+    for _ in range(2):
+        tape = rt.forward_async(x, routes, gates, w1, w2)
+        runs.append((tape.output, *rt.backward_async(tape, dy)))
+        rt.drain()
+    for a, b in zip(*runs):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), "headline shape: repeat differs"
+    y, dx, dg, dw1, dw2 = runs[0]
+    rt.close()
+
+    weights = {}
+
+    def expert_weights(ids):
+        out1, out2 = [], []
+        for e in ids:
+            owner = e // e_local
+            if owner not in weights:
+                weights[owner] = tuple(t.cpu() for t in rank_weights(owner))
+            out1.append(weights[owner][0][e % e_local])
+            out2.append(weights[owner][1][e % e_local])
+        return torch.stack(out1), torch.stack(out2)
+
+    def compact(xs, routes_, gates_, dys):
+        """The oracle on a few tokens with only the experts they touch (ids renumbered)."""
+        used = routes_[routes_ >= 0].unique()
+        remap = torch.full((E,), -1, dtype=torch.int32)
+        remap[used.long()] = torch.arange(len(used), dtype=torch.int32)
+        local = torch.where(routes_ >= 0, remap[routes_.clamp_min(0).long()], routes_)
+        ow1, ow2 = expert_weights(used.tolist())
+        return used, O.moe_layer(xs, local, gates_, ow1, ow2, dys)
+
+    sample = torch.tensor([0, 1, 4097, 8191])
+    cs = lambda t: t[sample.to(dev)].cpu()
+    _, (ys, dxs, dgs, _, _) = compact(cs(x), cs(routes), cs(gates), cs(dy))
+    for name, mine, ref in (("y", y, ys), ("dx", dx, dxs), ("dgates", dg, dgs)):
+        err = rel_l2(cs(mine), ref)
+        assert err < 2e-3, ("headline shape", rank, name, err)
+    everyone = [rank_inputs(r) for r in range(world)]
+    all_routes = torch.cat([v[2] for v in everyone])
+    counts = torch.bincount(all_routes.flatten().long(), minlength=E)[rank * e_local:(rank + 1) * e_local]
+    for local_e in (int(counts.argmax()), int(counts.argmin())):
+        expert = rank * e_local + local_e
+        hit = (all_routes == expert).any(dim=1).nonzero().flatten()
+        pick = lambda i: torch.cat([v[i] for v in everyone])[hit].cpu()
+        only = torch.where(pick(2) == expert, pick(2), torch.full_like(pick(2), -1))
+        used, (_, _, _, w1g, w2g) = compact(pick(0), only, pick(3), pick(1))
+        assert used.tolist() == [expert]
+        for name, mine, ref in (("dw1", dw1[local_e], w1g[0]), ("dw2", dw2[local_e], w2g[0])):
+            err = rel_l2(mine, ref)
+            assert err < 2e-3, ("headline shape", rank, name, expert, err)
+    del everyone
+    # EP1 with every expert on this GPU: the same tokens give the same forward bits
+    full = [rank_weights(r) for r in range(world)]
+    fw1, fw2 = torch.cat([f[0] for f in full]), torch.cat([f[1] for f in full])
+    del full
+    ep1 = TensorRuntime(group=SingleRankGroup(), experts=E, top_k=K, hidden=H, intermediate=I, max_tokens=256,
+                        max_rows=256 * K, training=False)
+    y1 = ep1.inference_eager(x[:256].contiguous(), routes[:256].contiguous(), gates[:256].contiguous(), fw1, fw2)
+    assert torch.equal(bits(y1), bits(y[:256])), "headline shape: EP1 != EPn forward bits"
+    ep1.close()
+    ok = [None] * world
+    dist.all_gather_object(ok, True)
+    if rank == 0:
+        print(f"EP{world} headline shape (E=256 K=8 H=2048 I=512, 8192 tokens/rank): sampled oracle parity "
+              f"(y, dx, dgates, dw1, dw2), bitwise repeat and EP1 == EP{world} forward bits passed", flush=True)
+
+
+def absent_rank_scenario(rank, world, w1, w2, E, K, H, I):
+    """One rank leaves between steps (it simply makes no further call; nothing of it is in flight): the
+    other ranks' next call must end by itself with a RuntimeError from the bounded flag wait instead of
+    waiting for ever, and the group must still close cleanly.  The wait budget is shortened to about
+    50 ms through the diagnostic setter; the failure is made on the host only."""
+    from weftmoe_b200 import _lib
+    lib = _lib.load()
+    rt = TensorRuntime(group=dist.group.WORLD, experts=E, top_k=K, hidden=H, intermediate=I, max_tokens=32,
+                       max_rows=32 * K * world, training=False)
+    g = torch.Generator().manual_seed(900 + rank)
+    x = torch.randn(32, H, generator=g).bfloat16().cuda()
+    routes = torch.rand(32, E, generator=g).topk(K).indices.int().cuda()
+    gates = torch.rand(32, K, generator=g).cuda()
+    lw1, lw2 = w1.chunk(world)[rank].cuda(), w2.chunk(world)[rank].cuda()
+    good = rt.inference_eager(x, routes, gates, lw1, lw2).clone()        # every rank takes part
+    torch.cuda.synchronize()
+    dist.barrier()
+    raised = None
+    if rank != world - 1:
+        lib.wm_debug_set_wait_budget(100_000_000)
+        try:
+            rt.inference_eager(x, routes, gates, lw1, lw2)
+            raised = False
+        except RuntimeError as exc:
+            raised = "wait" in str(exc)
+        finally:
+            lib.wm_debug_set_wait_budget(0)
+    torch.cuda.synchronize()
+    seen = [None] * world
+    dist.all_gather_object(seen, raised)
+    assert all(v is True for v in seen[:-1]) and seen[-1] is None, seen
+    assert torch.isfinite(good.float()).all()
+    rt.close()
+    if rank == 0:
+        print(f"EP{world} absent rank: the others' bounded waits ran out with RuntimeError, clean close passed",
+              flush=True)
 
 
 if __name__ == "__main__":

@@ -42,3 +42,26 @@ def test_contract_errors_without_a_gpu():
     assert "world" in _lib.last_error()
     cfg.world, cfg.hidden = 1, 100
     assert lib.wm_runtime_create(ctypes.byref(cfg), ctypes.byref(handle)) == _lib.WM_ERR_INVALID
+
+
+def test_route_plan_refuses_oversized_expert_shards_before_any_device_work():
+    """The planning kernel keeps one shared-memory word per local expert (at most 512).  The stand-alone
+    entry points must refuse a larger shard, and top_k > experts, from the host-side argument check:
+    no CUDA call is made (this test runs without a GPU)."""
+    lib = _lib.load()
+    out = _lib.WmRouteOut()
+    counts = (ctypes.c_int32 * 4096)()
+    routes = (ctypes.c_int32 * 8)()
+    for entry in (lib.wm_route_plan, lib.wm_route_plan_noalloc):
+        rc = entry(1, 1, 0, 1024, 2, 4, 4, 1024 * 128, routes, counts, ctypes.byref(out), None)
+        assert rc in (_lib.WM_ERR_INVALID, _lib.WM_ERR_CAPACITY), rc
+        rc = entry(1, 1, 0, 4, 8, 1, 1, 1024, routes, counts, ctypes.byref(out), None)
+        assert rc == _lib.WM_ERR_INVALID, rc
+    rc = lib.wm_route_plan(1, 2, 0, 2048, 2, 4, 4, 1024 * 128, routes, counts, ctypes.byref(out), None)
+    assert rc == _lib.WM_ERR_INVALID and "512" in _lib.last_error()
+
+
+def test_wait_budget_setter_is_exported_and_restores_its_default():
+    lib = _lib.load()
+    assert lib.wm_debug_set_wait_budget(1000) == _lib.WM_OK
+    assert lib.wm_debug_set_wait_budget(0) == _lib.WM_OK   # back to the default

@@ -2,20 +2,25 @@
 (a server whose own pool holds all free HBM, or a latency-critical path that cannot afford
 cudaMalloc's device-wide synchronisation).  It keeps its temporaries in a fixed 1 MiB device array
 inside the library, so this file checks, through the C ABI, that two calls in a row (which share
-that array and see each other's leftovers) each give exactly the output of wm_route_plan, and that
-requests beyond the fixed size are refused with a message.  Collected last on purpose."""
+that array and see each other's leftovers) each give exactly the output of wm_route_plan and of the
+CPU oracle (every field, the per-owner primary rows included), and that requests beyond the fixed size
+are refused with a message.  Collected last on purpose."""
 import ctypes
 
 import numpy as np
 import pytest
 import torch
 
+from oracle import c_oracle
 from weftmoe_b200 import _lib
 
 pytestmark = pytest.mark.gpu
 
-FIELDS = ("sorted_slot", "sorted_expert", "local_offset", "dst_rank", "dst_row", "dst_prow", "expert_total",
-          "expert_base", "expert_pbase", "padded_start", "tile_group", "num_tiles", "padded_rows")
+FIELDS = ("sorted_slot", "sorted_expert", "local_offset", "dst_rank", "dst_row", "dst_prow", "dst_primary",
+          "expert_total", "expert_base", "expert_pbase", "padded_start", "tile_group", "num_tiles", "padded_rows")
+# Fields the CPU oracle (oracle/route_oracle.c) also produces, compared bit for bit below.
+ORACLE_FIELDS = ("sorted_slot", "sorted_expert", "local_offset", "dst_rank", "dst_row", "dst_prow", "dst_primary",
+                 "expert_total", "expert_base", "expert_pbase", "padded_start", "tile_group")
 
 
 def plan(entry, world, experts, top_k, routes_per_rank, row_capacity):
@@ -37,7 +42,7 @@ def plan(entry, world, experts, top_k, routes_per_rank, row_capacity):
                         dst_rank=i32(t, top_k), dst_row=i32(t, top_k), dst_prow=i32(t, top_k),
                         expert_total=i32(experts), expert_base=i32(experts), expert_pbase=i32(experts),
                         padded_start=i32(e_local + 1), tile_group=i32(row_capacity // 128 + 1),
-                        num_tiles=i32(1), padded_rows=i32(1))
+                        num_tiles=i32(1), padded_rows=i32(1), dst_primary=i32(t, top_k))
             out = _lib.WmRouteOut(**{k: v.data_ptr() for k, v in bufs.items()})
             _lib.check(fn(phase, world, rank, experts, top_k, t, cap, row_capacity,
                           _lib.ptr(r) if t else None, _lib.ptr(cm), ctypes.byref(out), None))
@@ -67,9 +72,14 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point():
         row_capacity = (rows + 127) // 128 * 128 + 128 * (experts // world)
         mine = plan("wm_route_plan_noalloc", world, experts, top_k, routes, row_capacity)
         ref = plan("wm_route_plan", world, experts, top_k, routes, row_capacity)
+        oracle = c_oracle.route_plan(world, experts, top_k, routes)
         for rank in range(world):
             for k in FIELDS + ("count_matrix",):
                 assert np.array_equal(mine[rank][k], ref[rank][k]), (seed, rank, k)  # integers: bit-exact
+            for k in ORACLE_FIELDS:  # and against the CPU restatement of the reference's planner
+                assert np.array_equal(mine[rank][k].reshape(-1), np.asarray(oracle[rank][k]).reshape(-1)), (seed, rank, k)
+            assert int(mine[rank]["num_tiles"][0]) == oracle[rank]["num_tiles"]
+            assert int(mine[rank]["padded_rows"][0]) == oracle[rank]["padded_rows"]
 
 
 def test_sizes_beyond_the_fixed_scratch_are_refused():

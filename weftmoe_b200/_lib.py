@@ -72,6 +72,8 @@ SIGNATURES = {
     "wm_nvfp4_gemm": (c_int, [c_void_p] * 5 + [c_int32] * 3 + [c_float, c_int32, c_void_p]),
     "wm_route_plan_noalloc": (c_int, [c_int32] * 8 + [c_void_p, c_void_p, POINTER(WmRouteOut), c_void_p]),
     "wm_debug_force_gemm_pairs": (None, [c_int]),
+    "wm_debug_set_wait_budget": (c_int, [ctypes.c_longlong]),
+    "wm_debug_wait_flag": (c_int, [c_void_p, c_void_p, c_int32, c_void_p]),
     "wm_debug_grouped_gemm": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       POINTER(c_int), c_int, c_int, c_int, c_void_p, c_void_p]),
 }

@@ -355,12 +355,14 @@ __device__ __forceinline__ int ld_relaxed_sys(const int* p) {
   return v;
 }
 
-// Wait until *flag >= target (generation flags only ever grow).  Bounded.
-__device__ __forceinline__ bool wait_flag_ge(const int* flag, int target, int* status) {
+// Wait until *flag >= target (generation flags only ever grow).  Bounded by `budget` SM cycles
+// (the host passes kWaitBudgetCycles unless a test shortened it with wm_debug_set_wait_budget).
+__device__ __forceinline__ bool wait_flag_ge(const int* flag, int target, int* status,
+                                             long long budget = kWaitBudgetCycles) {
   const long long start = clock64();
   for (;;) {
     if (ld_acquire_sys(flag) - target >= 0) return true;
-    if (clock64() - start > kWaitBudgetCycles) {
+    if (clock64() - start > budget) {
       atomicCAS(status, 0, kStatusTimeoutPeerFlag);
       return false;
     }

@@ -63,7 +63,8 @@ __device__ __forceinline__ int chunk_word(int r) { return (r & 31) * 4 + ((r & 1
 // its scale words into the chunked layout; padding rows get zero data and neutral scales.
 // by_origin != 0 (backward): `meta_origin` is the saved origin array (-1 on padding rows) and nothing is
 // written to origin_out / prob_out.
-__global__ void gather_q_kernel(OwnerRows o, int rank, int e_local, int cap, int top_k, int kind, int hidden,
+__global__ void gather_q_kernel(OwnerRows o, int rank, int e_local, int world, int cap, int top_k, int kind,
+                                int hidden,
                                 PeerBytes stage, size_t sf_offset, const int* __restrict__ meta_origin,
                                 const float* __restrict__ meta_prob, uint8_t* __restrict__ rows_out,
                                 uint32_t* __restrict__ sfa_out, int* __restrict__ origin_out,
@@ -84,8 +85,9 @@ __global__ void gather_q_kernel(OwnerRows o, int rank, int e_local, int cap, int
     }
     uint4* dst = reinterpret_cast<uint4*>(rows_out + static_cast<size_t>(r) * row_bytes);
     uint32_t* sf_dst = sfa_out + static_cast<size_t>(r >> 7) * sf_words * 128 + chunk_word(r);
-    if (live) {
-      const int org = meta_origin[r];
+    // An origin outside [0, world * cap * top_k) is a word its source never wrote: treat the row as padding.
+    const int org = live ? meta_origin[r] : -1;
+    if (live && org >= 0 && org < world * cap * top_k) {
       const int src = org / (cap * top_k);
       const int token = (org - src * cap * top_k) / top_k;
       const uint8_t* base = stage.p[src];
@@ -372,11 +374,11 @@ __global__ void fp8_quantize_cols_chunked_kernel(DeviceRange range, const __nv_b
 
 }  // namespace
 
-int gather_q_rows(const OwnerRows& o, int rank, int e_local, int cap, int top_k, int kind, int hidden,
+int gather_q_rows(const OwnerRows& o, int rank, int e_local, int world, int cap, int top_k, int kind, int hidden,
                   const PeerBytes& stage, size_t sf_offset, const int* meta_origin, const float* meta_prob,
                   uint8_t* rows_out, uint32_t* sfa_out, int* origin_out, float* prob_out, int by_origin,
                   int ctas, cudaStream_t stream) {
-  gather_q_kernel<<<ctas, 256, 0, stream>>>(o, rank, e_local, cap, top_k, kind, hidden, stage, sf_offset,
+  gather_q_kernel<<<ctas, 256, 0, stream>>>(o, rank, e_local, world, cap, top_k, kind, hidden, stage, sf_offset,
                                             meta_origin, meta_prob, rows_out, sfa_out, origin_out, prob_out,
                                             by_origin);
   WM_CUDA(cudaGetLastError());

@@ -28,7 +28,7 @@ int pack_fp8_scales(const float* scales, int rows, int kblocks, int block_rows, 
                     cudaStream_t stream);
 
 // quant_path.cu
-int gather_q_rows(const OwnerRows& o, int rank, int e_local, int cap, int top_k, int kind, int hidden,
+int gather_q_rows(const OwnerRows& o, int rank, int e_local, int world, int cap, int top_k, int kind, int hidden,
                   const PeerBytes& stage, size_t sf_offset, const int* meta_origin, const float* meta_prob,
                   uint8_t* rows_out, uint32_t* sfa_out, int* origin_out, float* prob_out, int by_origin,
                   int ctas, cudaStream_t stream);

@@ -11,6 +11,7 @@
 // All kernels are HBM/latency-bound integer work over T*K route words.
 #include "kernels.h"
 #include "ptx.cuh"
+#include <atomic>
 #include <cstdlib>
 
 #include "route.h"
@@ -89,22 +90,35 @@ __global__ void chunk_scan_kernel(int* __restrict__ chunk_hist, int chunks, int 
 // Single CTA.  Waits for every rank's count row of this generation, then derives per expert:
 // total rows, rows from lower ranks, unpadded and padded base inside the owner; and for this
 // rank as owner: padded row start per local expert, the 128-row tile -> expert map, tile count.
+// Publish an empty owner schedule: every later kernel of the call finds empty ranges (M-grouped work,
+// copies) or zero-length reductions (K-grouped GEMMs then write zero gradients).
+__device__ void publish_empty_schedule(const PlanTables& t, int e_local) {
+  for (int l = threadIdx.x; l <= e_local; l += blockDim.x) t.padded_start[l] = 0;
+  if (threadIdx.x == 0) {
+    *t.num_tiles = 0;
+    *t.padded_rows = 0;
+    *t.num_pairs = 0;
+  }
+  if (t.split != nullptr && threadIdx.x < 8) t.split[threadIdx.x] = 0;
+}
+
 __global__ void global_plan_kernel(const int* __restrict__ count_matrix, const int* flag_counts,
                                    Gen gen, int world, int rank, int experts,
-                                   int row_capacity, PlanTables t, int* status, int split_percent) {
+                                   int row_capacity, PlanTables t, int* status, int split_percent,
+                                   long long wait_budget) {
   extern __shared__ int sh[];
   int* total = sh;               // [experts]
   int* padded = sh + experts;    // [experts]
-  __shared__ int ok;
-  if (threadIdx.x == 0) ok = 1;
+  __shared__ int ok, overflow;
+  if (threadIdx.x == 0) { ok = 1; overflow = 0; }
   __syncthreads();
   if (threadIdx.x < world) {
-    if (!wait_flag_ge(flag_counts + threadIdx.x * kFlagStride, gen.value(), status)) ok = 0;
+    if (!wait_flag_ge(flag_counts + threadIdx.x * kFlagStride, gen.value(), status, wait_budget)) ok = 0;
   }
   __syncthreads();
   const int e_local = experts / world;
-  if (!ok) {
-    if (threadIdx.x == 0) { *t.num_tiles = 0; *t.padded_rows = 0; }
+  if (!ok) {  // a count row never arrived: the status word is set, nothing may be derived from the counts
+    publish_empty_schedule(t, e_local);
     return;
   }
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
@@ -130,24 +144,21 @@ __global__ void global_plan_kernel(const int* __restrict__ count_matrix, const i
       base += total[e];
       pbase += padded[e];
     }
+    // Every rank holds the same count matrix and the same row capacity, so every rank sees every
+    // owner's overflow and all of them fail the call together (the reference checks every destination
+    // rank's rows on every rank too: src/metadata/notify_dispatch.cpp:2003-2035).
+    if (pbase > row_capacity) overflow = 1;
     if (threadIdx.x == rank) {
-      int tiles = pbase / 128;
-      if (pbase > row_capacity) {
-        atomicCAS(status, 0, kStatusRowOverflow);
-        tiles = 0;
-        pbase = 0;
-      }
-      *t.num_tiles = tiles;
+      *t.num_tiles = pbase / 128;
       *t.padded_rows = pbase;
       t.padded_start[e_local] = pbase;
     }
   }
   __syncthreads();
-  if (*t.num_tiles == 0 && *t.padded_rows == 0) {
-    // overflow or no rows: still publish zeroed starts so K-grouped GEMMs write zero gradients
-    for (int l = threadIdx.x; l <= e_local; l += blockDim.x) t.padded_start[l] = 0;
-    if (threadIdx.x == 0) *t.num_pairs = 0;
-    if (t.split != nullptr && threadIdx.x < 8) t.split[threadIdx.x] = 0;
+  if (overflow || *t.padded_rows == 0) {
+    if (overflow && threadIdx.x == 0) atomicCAS(status, 0, kStatusRowOverflow);
+    __syncthreads();
+    publish_empty_schedule(t, e_local);
     return;
   }
   // CTA-pair schedule: consecutive 128-row tiles of one expert are paired; an odd last tile
@@ -198,8 +209,11 @@ __global__ void route_rows_kernel(const int* __restrict__ routes, const float* _
                                   PlanTables t, int* __restrict__ local_offset,
                                   int* __restrict__ dst_rank, int* __restrict__ dst_row,
                                   int* __restrict__ dst_prow, PeerInts meta_origin,
-                                  PeerFloats meta_prob) {
+                                  PeerFloats meta_prob, int row_capacity,
+                                  const int* __restrict__ status) {
   extern __shared__ unsigned short warp_cnt[];  // [32][experts]
+  // A failed plan (a wait that ran out, a row overflow) left no tables to read: push nothing.
+  if (status != nullptr && *status != 0) return;
   for (int k = threadIdx.x; k < 32 * experts; k += blockDim.x) warp_cnt[k] = 0;
   __syncthreads();
   const int i = blockIdx.x * kChunk + threadIdx.x;
@@ -226,7 +240,7 @@ __global__ void route_rows_kernel(const int* __restrict__ routes, const float* _
   dst_rank[i] = owner;
   dst_row[i] = t.expert_base[id] + within;
   dst_prow[i] = prow;
-  if (meta_origin.p[owner] != nullptr) {
+  if (meta_origin.p[owner] != nullptr && prow >= 0 && prow < row_capacity) {
     const int token = i / top_k;
     meta_origin.p[owner][prow] = rank * cap * top_k + token * top_k + slot_pos[i];
     meta_prob.p[owner][prow] = gates[i];
@@ -236,9 +250,11 @@ __global__ void route_rows_kernel(const int* __restrict__ routes, const float* _
 __global__ void route_primary_kernel(const int* __restrict__ slot_pos,
                                      const int* __restrict__ dst_rank,
                                      const int* __restrict__ dst_prow, int n, int top_k,
-                                     PeerInts meta_primary, int* __restrict__ per_route) {
+                                     PeerInts meta_primary, int* __restrict__ per_route,
+                                     int row_capacity, const int* __restrict__ status) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
+  if (status != nullptr && *status != 0) return;  // route_rows wrote nothing
   const int owner = dst_rank[i];
   if (owner < 0) {
     if (per_route) per_route[i] = -1;
@@ -253,17 +269,27 @@ __global__ void route_primary_kernel(const int* __restrict__ slot_pos,
       head_pos = slot_pos[r];
     }
   }
-  if (meta_primary.p[owner] != nullptr) meta_primary.p[owner][dst_prow[i]] = dst_prow[head];
+  const int prow = dst_prow[i];
+  if (meta_primary.p[owner] != nullptr && prow >= 0 && prow < row_capacity)
+    meta_primary.p[owner][prow] = dst_prow[head];
   if (per_route) per_route[i] = dst_prow[head];
 }
 
 // ------------------------------------------------------------------ host side
+static std::atomic<long long> g_flag_wait_budget{kWaitBudgetCycles};
+long long flag_wait_budget() { return g_flag_wait_budget.load(std::memory_order_relaxed); }
+void set_flag_wait_budget(long long cycles) {
+  g_flag_wait_budget.store(cycles > 0 ? cycles : kWaitBudgetCycles, std::memory_order_relaxed);
+}
+
 int route_primary(const RouteShape& s, int tokens, const RouteLocal& local, const RouteRows& rows,
-                  const PeerInts& meta_primary, int* per_route, cudaStream_t stream) {
+                  const PeerInts& meta_primary, int* per_route, int row_capacity, const int* status,
+                  cudaStream_t stream) {
   const int n = tokens * s.top_k;
   if (n == 0) return 0;
   route_primary_kernel<<<(n + 255) / 256, 256, 0, stream>>>(local.slot_pos, rows.dst_rank, rows.dst_prow, n,
-                                                           s.top_k, meta_primary, per_route);
+                                                           s.top_k, meta_primary, per_route, row_capacity,
+                                                           status);
   count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
@@ -299,7 +325,8 @@ int route_global(const RouteShape& s, const int* count_matrix, const int* flag_c
     return n >= 10 && n <= 90 ? n : 50;
   }();
   global_plan_kernel<<<1, 1024, 2 * s.experts * sizeof(int), stream>>>(
-      count_matrix, flag_counts, generation, s.world, s.rank, s.experts, row_capacity, t, status, split_percent);
+      count_matrix, flag_counts, generation, s.world, s.rank, s.experts, row_capacity, t, status, split_percent,
+      flag_wait_budget());
   count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
@@ -307,20 +334,25 @@ int route_global(const RouteShape& s, const int* count_matrix, const int* flag_c
 
 int route_rows(const RouteShape& s, const int* routes, const float* gates, int tokens,
                const RouteLocal& local, const int* chunk_base, PlanTables t, RouteRows out,
-               const PeerInts& meta_origin, const PeerFloats& meta_prob, cudaStream_t stream) {
+               const PeerInts& meta_origin, const PeerFloats& meta_prob, int row_capacity,
+               const int* status, cudaStream_t stream) {
   const int n = tokens * s.top_k;
   if (n == 0) return 0;
   const int chunks = (n + kChunk - 1) / kChunk;
   const size_t smem = 32u * s.experts * sizeof(unsigned short);
-  static bool configured = false;
-  if (!configured && smem > 48 * 1024) {
+  // Opt in once per device to the largest size any accepted shape needs (64 B x 2048 experts).
+  static bool configured[64] = {};
+  int device = 0;
+  WM_CUDA(cudaGetDevice(&device));
+  if (device >= 0 && device < 64 && !configured[device]) {
     WM_CUDA(cudaFuncSetAttribute(route_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
-    configured = true;
+                                 32 * 2048 * (int)sizeof(unsigned short)));
+    configured[device] = true;
   }
   route_rows_kernel<<<chunks, kChunk, smem, stream>>>(
       routes, gates, local.slot_pos, n, s.top_k, s.experts, s.world, s.rank, s.cap, chunk_base, t,
-      out.local_offset, out.dst_rank, out.dst_row, out.dst_prow, meta_origin, meta_prob);
+      out.local_offset, out.dst_rank, out.dst_row, out.dst_prow, meta_origin, meta_prob, row_capacity,
+      status);
   count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;

@@ -78,9 +78,17 @@ int route_local(const RouteShape& s, const int* routes, int tokens, RouteLocal o
                 cudaStream_t stream);
 int route_global(const RouteShape& s, const int* count_matrix, const int* flag_counts,
                  Gen generation, int row_capacity, PlanTables t, int* status, cudaStream_t stream);
+// `status` (nullable): when the status word is already non-zero (the plan failed) nothing is written.
+// Words for rows at or beyond `row_capacity` are never pushed to an owner.
 int route_rows(const RouteShape& s, const int* routes, const float* gates, int tokens,
                const RouteLocal& local, const int* chunk_base, PlanTables t, RouteRows out,
-               const PeerInts& meta_origin, const PeerFloats& meta_prob, cudaStream_t stream);
+               const PeerInts& meta_origin, const PeerFloats& meta_prob, int row_capacity,
+               const int* status, cudaStream_t stream);
+
+// Cycle budget of the cross-rank flag waits (default: kWaitBudgetCycles, about 2 s).  Process-wide;
+// tests shorten it through wm_debug_set_wait_budget to make a wait run out quickly.
+long long flag_wait_budget();
+void set_flag_wait_budget(long long cycles);
 
 // Source side, world > 1: a token routed to several experts of ONE owner rank crosses NVLink once.
 // For every route, meta_primary[owner][row] = the owner row of the token's first route (lowest
@@ -89,7 +97,8 @@ int route_rows(const RouteShape& s, const int* routes, const float* gates, int t
 // `per_route` (nullable) also receives that row per route, in route order (-1 = no route); entries of
 // meta_primary may be null (nothing is sent to that owner).
 int route_primary(const RouteShape& s, int tokens, const RouteLocal& local, const RouteRows& rows,
-                  const PeerInts& meta_primary, int* per_route, cudaStream_t stream);
+                  const PeerInts& meta_primary, int* per_route, int row_capacity, const int* status,
+                  cudaStream_t stream);
 
 // ------------------------------------------------------------------ transport (transport.cu)
 struct OwnerRows {
@@ -100,7 +109,11 @@ struct OwnerRows {
 };
 
 // Wait until flags[r] >= generation for r < world (bounded); flags are kFlagStride apart.
-int wait_flags(const int* flags, int world, Gen generation, int* status, cudaStream_t stream);
+// When a wait runs out the status word is set and, if `split_on_fail` is given, the eight words of the
+// owner schedule's split are zeroed, so that every later owner-side kernel of the call finds an empty
+// range and touches no row whose indices might not have arrived.
+int wait_flags(const int* flags, int world, Gen generation, int* status, int* split_on_fail,
+               cudaStream_t stream);
 // Store `generation` into flag slot `slot` of every rank's flag group (peer-mapped).
 int signal_peers(const PeerInts& flag_group, int world, int slot, Gen generation,
                  cudaStream_t stream);
@@ -112,13 +125,14 @@ int signal_peers(const PeerInts& flag_group, int world, int slot, Gen generation
 // copy origin/prob words from the meta mailbox to local arrays, zero the padding rows.
 // meta_primary (nullable = every row is pulled) names the row a duplicate is copied from;
 // primary_out (nullable) keeps it for the backward pass.  Call copy_duplicate_rows afterwards.
-int gather_rows(const OwnerRows& o, int rank, int e_local, int cap, int top_k, int hidden,
+int gather_rows(const OwnerRows& o, int rank, int e_local, int world, int row_capacity, int cap, int top_k,
+                int hidden,
                 const PeerConstRows& stage, const int* meta_origin, const float* meta_prob,
                 const int* meta_primary, __nv_bfloat16* rows_out, int* origin_out, float* prob_out,
                 int* primary_out, int ctas, cudaStream_t stream);
 // Owner side, backward: pull dY rows by the saved origins (only rows with primary[r] == r when
 // `primary` is given).
-int gather_by_origin(DeviceRange rows, const int* origin, const int* primary, int cap, int top_k,
+int gather_by_origin(DeviceRange rows, const int* origin, const int* primary, int world, int cap, int top_k,
                      int hidden, const PeerConstRows& stage, __nv_bfloat16* rows_out, int ctas,
                      cudaStream_t stream);
 // Owner side: rows_out[r] = rows_out[primary[r]] for the rows of the range with primary[r] != r.

@@ -11,7 +11,8 @@
 // 1 MiB until the process exits.  Its name is only a host-side handle, not a device address, so
 // the address is looked up once per device with cudaGetSymbolAddress (with that device current)
 // and that pointer is what the kernels receive.  The look-up happens in the first call made on a
-// device; make that first call outside stream capture.
+// device; make that first call before any stream capture.  Every call, the first included, ends by
+// synchronising `stream` and reading the device status word back on the host.
 //
 // All calls on a device share the array and it keeps whatever the previous call left in it.  The
 // words that must start at zero (status, flag words) are cleared on the caller's stream at the
@@ -83,7 +84,7 @@ extern "C" int wm_route_plan_noalloc(int32_t phase, int32_t world, int32_t rank,
                                      int32_t row_capacity, const int32_t* routes,
                                      int32_t* count_matrix, const wm_route_out* out, void* stream_) {
   if (!out || !count_matrix || world < 1 || world > kMaxWorld || rank < 0 || rank >= world ||
-      experts < 1 || experts % world || top_k < 1 || top_k > 32 || tokens < 0 || tokens > cap ||
+      experts < 1 || experts % world || top_k < 1 || top_k > 32 || top_k > experts || tokens < 0 || tokens > cap ||
       (tokens > 0 && !routes) || row_capacity < 0 || row_capacity % 128) {
     set_error("wm_route_plan_noalloc: bad argument");
     return WM_ERR_INVALID;
@@ -119,7 +120,11 @@ extern "C" int wm_route_plan_noalloc(int32_t phase, int32_t world, int32_t rank,
     PeerFloats no_prob{};
     if (!rc)
       rc = route_rows(shape, routes, nullptr, tokens, local, at<int>(tmp, kOffHist), t, rows, no_origin,
-                      no_prob, stream);
+                      no_prob, row_capacity, at<int>(tmp, kOffStatus), stream);
+    // Needs no scratch of its own: it reads the per-route arrays written just above.
+    if (!rc && out->dst_primary)
+      rc = route_primary(shape, tokens, local, rows, no_origin, out->dst_primary, row_capacity,
+                         at<int>(tmp, kOffStatus), stream);
     if (!rc && cudaMemcpyAsync(&device_code, tmp + kOffStatus, sizeof(int), cudaMemcpyDeviceToHost,
                                stream) != cudaSuccess)
       rc = WM_ERR_CUDA;

@@ -371,9 +371,11 @@ extern "C" int wm_runtime_create(const wm_config* config, wm_runtime** out) {
               rt->sl.total, cudaGetErrorString(e));
     return fail(WM_ERR_CUDA);
   }
-  // Zero only what must start at zero: flags, count matrix, status.  Done on the legacy stream
-  // and synchronised so that peers may write as soon as they have imported the handle.
-  e = cudaMemset(rt->arena, 0, rt->al.stage);
+  // Zero what must start at zero (flags, count matrix, status) and everything an owner may read
+  // before its source wrote it when a source drops out (staging rows, origin / prob / primary words:
+  // zero is a valid value for each).  Done on the legacy stream and synchronised so that peers may
+  // write as soon as they have imported the handle.
+  e = cudaMemset(rt->arena, 0, rt->al.mailbox);
   if (e == cudaSuccess) e = cudaMemset(rt->scratch + rt->sl.status, 0, sizeof(int) * 4);
   if (e == cudaSuccess) e = cudaMemset(rt->scratch + rt->sl.gen, 0, sizeof(int));
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
@@ -594,7 +596,7 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
     stage.p[0] = static_cast<const __nv_bfloat16*>(x);  // no peers: owners read x itself
   } else {
     StageScope scope(timing, kStageStageIn, stream);
-    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, nullptr, stream)) return rc;
     if (tokens > 0)
       WM_CUDA(cudaMemcpyAsync(rt->arena + rt->al.stage, x, 2ull * tokens * c.hidden,
                               cudaMemcpyDeviceToDevice, stream));
@@ -614,15 +616,16 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
     RouteRows rows{at<int>(S, rt->sl.local_offset), at<int>(S, rt->sl.dst_rank),
                    at<int>(S, rt->sl.dst_row), at<int>(S, rt->sl.dst_prow)};
     if (int rc = route_rows(shape, routes, gates, tokens, local, at<int>(S, rt->sl.chunk_hist),
-                            tables, rows, meta_origin, meta_prob, stream))
+                            tables, rows, meta_origin, meta_prob, rt->row_cap, status, stream))
       return rc;
     if (world > 1)
-      if (int rc = route_primary(shape, tokens, local, rows, meta_primary, nullptr, stream)) return rc;
+      if (int rc = route_primary(shape, tokens, local, rows, meta_primary, nullptr, rt->row_cap, status, stream))
+        return rc;
   }
   if (world > 1) {
     StageScope scope(timing, kStageSyncReady, stream);
     if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
-    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, tables.split, stream)) return rc;
   }
   // 3. owner side: pull rows, then the two grouped GEMMs; FC2 pushes into the sources' mailboxes.
   //    world > 1: the rows are split at an expert boundary; the second half is pulled on the side
@@ -634,7 +637,8 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
   };
   auto pull = [&](int half, cudaStream_t st) -> int {
     const int ctas = st == rt->side ? rt->sms * 2 : rt->sms * 8;  // the side stream copies beside a GEMM
-    if (int rc = gather_rows(owner_rows(half), c.rank, rt->e_local, c.max_tokens, c.top_k, c.hidden, stage,
+    if (int rc = gather_rows(owner_rows(half), c.rank, rt->e_local, world, rt->row_cap, c.max_tokens, c.top_k,
+                             c.hidden, stage,
                              at<int>(rt->arena, rt->al.meta_origin), at<float>(rt->arena, rt->al.meta_prob),
                              primary ? at<int>(rt->arena, rt->al.meta_primary) : nullptr, xrows, origin,
                              prob, primary, ctas, st))
@@ -700,7 +704,7 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
   if (world > 1) {
     StageScope scope(timing, kStageSyncContrib, stream);
     if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
-    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, nullptr, stream)) return rc;
   }
   // 4. source side: ordered FP32 combine.
   StageScope scope(timing, kStageCombine, stream);
@@ -767,14 +771,17 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
   } else {
     {
       StageScope scope(timing, kStageStageInBwd, stream);
-      if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, stream)) return rc;
+      if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, nullptr, stream)) return rc;
       if (tokens > 0)
         WM_CUDA(cudaMemcpyAsync(rt->arena + rt->al.stage, dy, 2ull * tokens * c.hidden,
                                 cudaMemcpyDeviceToDevice, stream));
     }
     StageScope scope(timing, kStageSyncReadyBwd, stream);
     if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
-    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
+    // (the saved split is only read by this call: emptying it on a failed wait is harmless)
+    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status,
+                            reinterpret_cast<int*>(tp(rt->tl.split)), stream))
+      return rc;
   }
   // 2./3. owner side: pull dY rows in the saved row order; dU = dY * W2; SwiGLU backward (U, dAB,
   //       dprob -> sources); dX = dAB * W1 -> sources.  world > 1: two halves, the second half's
@@ -786,7 +793,7 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
   const int* primary = world == 1 ? nullptr : reinterpret_cast<const int*>(tp(rt->tl.primary));
   auto pull = [&](int half, cudaStream_t st) -> int {
     const int ctas = st == rt->side ? rt->sms * 2 : rt->sms * 8;  // the side stream copies beside a GEMM
-    if (int rc = gather_by_origin(split_range(split, 2, half), origin, primary, c.max_tokens, c.top_k,
+    if (int rc = gather_by_origin(split_range(split, 2, half), origin, primary, world, c.max_tokens, c.top_k,
                                   c.hidden, stage, recv, ctas, st))
       return rc;
     return primary ? copy_duplicate_rows(split_range(split, 2, half), primary, c.hidden, recv, ctas, st) : 0;
@@ -891,7 +898,7 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
   // 5. source side: ordered combine of dX, dprob back to the original slots.
   if (world > 1) {
     StageScope scope(timing, kStageSyncContribBwd, stream);
-    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, nullptr, stream)) return rc;
   }
   StageScope scope(timing, kStageCombineDx, stream);
   if (int rc = combine_rows(at<__nv_bfloat16>(rt->arena, rt->al.mailbox), sorted_expert, tokens,
@@ -986,7 +993,7 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
   const size_t row_bytes = kind == kKindFp8 ? H : H / 2;
   const size_t sf_offset = align_up(static_cast<size_t>(c.max_tokens) * row_bytes);
   if (world > 1)
-    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, nullptr, stream)) return rc;
   uint8_t* my_stage = rt->arena + rt->al.stage;
   if (tokens > 0) {
     if (kind == kKindFp8) {
@@ -1010,16 +1017,16 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
   RouteRows rows{at<int>(S, rt->sl.local_offset), at<int>(S, rt->sl.dst_rank), at<int>(S, rt->sl.dst_row),
                  at<int>(S, rt->sl.dst_prow)};
   if (int rc = route_rows(shape, routes, gates, tokens, local, at<int>(S, rt->sl.chunk_hist), tables, rows,
-                          meta_origin, meta_prob, stream))
+                          meta_origin, meta_prob, rt->row_cap, status, stream))
     return rc;
   if (world > 1) {
     if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
-    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, tables.split, stream)) return rc;
   }
   // 3. owner side: pull quantised rows + scale factors, FC1, SwiGLU + re-quantisation, FC2 -> mailboxes.
   OwnerRows owner{tables.padded_start, tables.tile_group, split_range(tables.split, 2, kWhole),
                   tables.expert_total};
-  if (int rc = gather_q_rows(owner, c.rank, rt->e_local, c.max_tokens, c.top_k, kind, H, stage, sf_offset,
+  if (int rc = gather_q_rows(owner, c.rank, rt->e_local, world, c.max_tokens, c.top_k, kind, H, stage, sf_offset,
                              at<int>(rt->arena, rt->al.meta_origin), at<float>(rt->arena, rt->al.meta_prob),
                              xq, sfa_x, origin, prob, 0, rt->sms * 8, stream))
     return rc;
@@ -1050,7 +1057,7 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
     return rc;
   if (world > 1) {
     if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
-    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, nullptr, stream)) return rc;
   }
   return combine_rows(at<__nv_bfloat16>(rt->arena, rt->al.mailbox), local.sorted_expert, tokens,
                       c.max_tokens, c.top_k, c.hidden, static_cast<__nv_bfloat16*>(y), stream);
@@ -1132,17 +1139,17 @@ static int backward_nvfp4(wm_runtime* rt, const void* tape, const void* dy, cons
 
   // 1. stage dY (BF16) and pull its rows in the saved row order.
   if (world > 1)
-    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, nullptr, stream)) return rc;
   if (world == 1)
     stage.p[0] = static_cast<const __nv_bfloat16*>(dy);
   else if (tokens > 0)
     WM_CUDA(cudaMemcpyAsync(rt->arena + rt->al.stage, dy, 2ull * tokens * H, cudaMemcpyDeviceToDevice, stream));
   if (world > 1) {
     if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
-    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, const_cast<int*>(split), stream)) return rc;
   }
   const DeviceRange all_rows = split_range(split, 2, kWhole);
-  if (int rc = gather_by_origin(all_rows, origin, nullptr, c.max_tokens, c.top_k, H, stage, recv, rt->sms * 8,
+  if (int rc = gather_by_origin(all_rows, origin, nullptr, world, c.max_tokens, c.top_k, H, stage, recv, rt->sms * 8,
                                 stream))
     return rc;
   if (world > 1)
@@ -1192,7 +1199,7 @@ static int backward_nvfp4(wm_runtime* rt, const void* tape, const void* dy, cons
     return rc;
   // 6. source side: ordered combine of dX, dprob back to the original slots.
   if (world > 1)
-    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, nullptr, stream)) return rc;
   if (int rc = combine_rows(at<__nv_bfloat16>(rt->arena, rt->al.mailbox), sorted_expert, tokens, c.max_tokens,
                             c.top_k, H, static_cast<__nv_bfloat16*>(dx), stream))
     return rc;
@@ -1273,7 +1280,7 @@ extern "C" int wm_backward_quantized(wm_runtime* rt, const void* tape, const voi
   // 1. quantise dY (1 x 128) into the staging buffer, as X was in the forward pass.
   const size_t sf_offset = align_up(static_cast<size_t>(c.max_tokens) * H);
   if (world > 1)
-    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, nullptr, stream)) return rc;
   uint8_t* my_stage = rt->arena + rt->al.stage;
   if (tokens > 0)
     if (int rc = fp8_quantize_rows(dy, tokens, H, my_stage, reinterpret_cast<float*>(my_stage + sf_offset),
@@ -1281,12 +1288,12 @@ extern "C" int wm_backward_quantized(wm_runtime* rt, const void* tape, const voi
       return rc;
   if (world > 1) {
     if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
-    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, const_cast<int*>(split), stream)) return rc;
   }
   // 2. owner side: pull the quantised dY rows by the saved origins.
   const DeviceRange all_rows = split_range(split, 2, kWhole);
   OwnerRows owner{padded_start, tile_group, all_rows, nullptr};
-  if (int rc = gather_q_rows(owner, c.rank, rt->e_local, c.max_tokens, c.top_k, kKindFp8, H, stage, sf_offset,
+  if (int rc = gather_q_rows(owner, c.rank, rt->e_local, world, c.max_tokens, c.top_k, kKindFp8, H, stage, sf_offset,
                              origin, nullptr, qrows, sfa_q, nullptr, nullptr, 1, rt->sms * 8, stream))
     return rc;
   if (world > 1)
@@ -1354,7 +1361,7 @@ extern "C" int wm_backward_quantized(wm_runtime* rt, const void* tape, const voi
   }
   // 7. source side: ordered combine of dX, dprob back to the original slots.
   if (world > 1)
-    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, stream)) return rc;
+    if (int rc = wait_flags(my_flags(rt, kContrib), world, gen, status, nullptr, stream)) return rc;
   if (int rc = combine_rows(at<__nv_bfloat16>(rt->arena, rt->al.mailbox), sorted_expert, tokens, c.max_tokens,
                             c.top_k, c.hidden, static_cast<__nv_bfloat16*>(dx), stream))
     return rc;
@@ -1378,8 +1385,14 @@ extern "C" int wm_route_plan(int32_t phase, int32_t world, int32_t rank, int32_t
                              void* stream_) {
   if (!out || !count_matrix || world < 1 || world > kMaxWorld || rank < 0 || rank >= world ||
       experts < 1 || experts % world || experts > 2048 || top_k < 1 || top_k > 32 || tokens < 0 ||
-      tokens > cap || (tokens > 0 && !routes) || row_capacity % 128) {
+      tokens > cap || (tokens > 0 && !routes) || row_capacity < 0 || row_capacity % 128) {
     set_error("wm_route_plan: bad argument");
+    return WM_ERR_INVALID;
+  }
+  // The planning kernel keeps one shared-memory word per local expert (at most 512), like the runtime.
+  if (experts / world > 512 || top_k > experts) {
+    set_error("wm_route_plan: experts / world must be <= 512 and top_k <= experts (E=%d world=%d K=%d)",
+              experts, world, top_k);
     return WM_ERR_INVALID;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -1395,32 +1408,39 @@ extern "C" int wm_route_plan(int32_t phase, int32_t world, int32_t rank, int32_t
   const size_t o_pairs = k.take(sizeof(int) * (2 * (row_capacity / 128 + 1) + 1));
   uint8_t* tmp = nullptr;
   WM_CUDA(cudaMalloc(&tmp, k.cursor));
-  WM_CUDA(cudaMemsetAsync(tmp + o_status, 0, k.cursor - o_status, stream));
-  RouteShape shape{experts, top_k, world, rank, cap};
-  RouteLocal local{out->sorted_slot, out->sorted_expert, at<int>(tmp, o_pos)};
-  PeerInts counts{};
-  for (int r = 0; r < world; ++r) counts.p[r] = count_matrix;  // every "rank" shares one matrix
-  int rc = route_local(shape, routes, tokens, local, at<int>(tmp, o_hist), at<int>(tmp, o_cnt), counts,
-                       stream);
   int device_code = 0;
-  if (!rc && phase == 1) {
+  // Everything between the allocation and the free reports through rc, so tmp is never leaked.
+  auto body = [&]() -> int {
+    WM_CUDA(cudaMemsetAsync(tmp + o_status, 0, k.cursor - o_status, stream));
+    RouteShape shape{experts, top_k, world, rank, cap};
+    RouteLocal local{out->sorted_slot, out->sorted_expert, at<int>(tmp, o_pos)};
+    PeerInts counts{};
+    for (int r = 0; r < world; ++r) counts.p[r] = count_matrix;  // every "rank" shares one matrix
+    if (int rc = route_local(shape, routes, tokens, local, at<int>(tmp, o_hist), at<int>(tmp, o_cnt), counts,
+                             stream))
+      return rc;
+    if (phase != 1) return 0;
     PlanTables t{out->expert_total, at<int>(tmp, o_before), out->expert_base, out->expert_pbase,
                  out->padded_start, out->tile_group, out->num_tiles, out->padded_rows,
                  at<int>(tmp, o_pairs) + 1, at<int>(tmp, o_pairs)};
     // No exchange to wait for: generation 0 is satisfied by the zeroed flag words.
-    rc = route_global(shape, count_matrix, at<int>(tmp, o_flags), Gen{}, row_capacity, t,
-                      at<int>(tmp, o_status), stream);
+    if (int rc = route_global(shape, count_matrix, at<int>(tmp, o_flags), Gen{}, row_capacity, t,
+                              at<int>(tmp, o_status), stream))
+      return rc;
     RouteRows rows{out->local_offset, out->dst_rank, out->dst_row, out->dst_prow};
     PeerInts no_origin{};
     PeerFloats no_prob{};
-    if (!rc)
-      rc = route_rows(shape, routes, nullptr, tokens, local, at<int>(tmp, o_hist), t, rows,
-                      no_origin, no_prob, stream);
-    if (!rc && out->dst_primary) rc = route_primary(shape, tokens, local, rows, no_origin, out->dst_primary, stream);
-    if (!rc && cudaMemcpyAsync(&device_code, tmp + o_status, sizeof(int), cudaMemcpyDeviceToHost,
-                               stream) != cudaSuccess)
-      rc = WM_ERR_CUDA;
-  }
+    if (int rc = route_rows(shape, routes, nullptr, tokens, local, at<int>(tmp, o_hist), t, rows, no_origin,
+                            no_prob, row_capacity, at<int>(tmp, o_status), stream))
+      return rc;
+    if (out->dst_primary)
+      if (int rc = route_primary(shape, tokens, local, rows, no_origin, out->dst_primary, row_capacity,
+                                 at<int>(tmp, o_status), stream))
+        return rc;
+    WM_CUDA(cudaMemcpyAsync(&device_code, tmp + o_status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    return 0;
+  };
+  const int rc = body();
   cudaError_t e = cudaStreamSynchronize(stream);
   cudaFree(tmp);
   if (rc) return rc;
@@ -1433,6 +1453,23 @@ extern "C" int wm_route_plan(int32_t phase, int32_t world, int32_t rank, int32_t
     return map_status(device_code);
   }
   return WM_OK;
+}
+
+// =============================================================================== wait diagnostics
+extern "C" int wm_debug_set_wait_budget(long long cycles) {
+  set_flag_wait_budget(cycles);
+  return WM_OK;
+}
+
+extern "C" int wm_debug_wait_flag(wm_runtime* rt, const int32_t* flag_word, int32_t target, void* stream_) {
+  if (int rc = check_ready(rt, "wm_debug_wait_flag")) return rc;
+  if (!flag_word) {
+    set_error("wm_debug_wait_flag: null flag word");
+    return WM_ERR_INVALID;
+  }
+  // One flag ("world" 1) on the caller's word, this runtime's status word, the current budget.
+  return wait_flags(flag_word, 1, Gen{nullptr, target}, at<int>(rt->scratch, rt->sl.status), nullptr,
+                    static_cast<cudaStream_t>(stream_));
 }
 
 // =============================================================================== instrumentation

@@ -16,8 +16,16 @@
 namespace wm {
 
 // ------------------------------------------------------------------ flags
-__global__ void wait_flags_kernel(const int* flags, int world, Gen generation, int* status) {
-  if (threadIdx.x < world) wait_flag_ge(flags + threadIdx.x * kFlagStride, generation.value(), status);
+__global__ void wait_flags_kernel(const int* flags, int world, Gen generation, int* status,
+                                  int* split_on_fail, long long budget) {
+  bool ok = true;
+  if (threadIdx.x < world)
+    ok = wait_flag_ge(flags + threadIdx.x * kFlagStride, generation.value(), status, budget);
+  // A wait ran out (now or earlier in this call: the status word is sticky until the host polls it):
+  // empty the owner schedule's ranges so that no later kernel of the call follows indices that may
+  // never have arrived.
+  const bool failed = __any_sync(0xffffffffu, !ok) || *status != 0;
+  if (failed && split_on_fail != nullptr && threadIdx.x < 8) split_on_fail[threadIdx.x] = 0;
 }
 __global__ void signal_peers_kernel(PeerInts group, int world, int slot, Gen gen) {
   const int generation = gen.value();
@@ -26,8 +34,10 @@ __global__ void signal_peers_kernel(PeerInts group, int world, int slot, Gen gen
     st_release_sys(group.p[threadIdx.x] + slot * kFlagStride, generation);
   }
 }
-int wait_flags(const int* flags, int world, Gen generation, int* status, cudaStream_t stream) {
-  wait_flags_kernel<<<1, 32, 0, stream>>>(flags, world, generation, status);
+int wait_flags(const int* flags, int world, Gen generation, int* status, int* split_on_fail,
+               cudaStream_t stream) {
+  wait_flags_kernel<<<1, 32, 0, stream>>>(flags, world, generation, status, split_on_fail,
+                                          flag_wait_budget());
   count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
@@ -57,8 +67,8 @@ __device__ __forceinline__ void zero_row(uint4* __restrict__ dst, int vecs, int 
   for (int c = lane; c < vecs; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
 }
 
-__global__ void gather_rows_kernel(OwnerRows o, int rank, int e_local, int cap, int top_k,
-                                   int hidden, PeerConstRows stage,
+__global__ void gather_rows_kernel(OwnerRows o, int rank, int e_local, int world, int row_capacity,
+                                   int cap, int top_k, int hidden, PeerConstRows stage,
                                    const int* __restrict__ meta_origin,
                                    const float* __restrict__ meta_prob,
                                    const int* __restrict__ meta_primary,
@@ -74,9 +84,12 @@ __global__ void gather_rows_kernel(OwnerRows o, int rank, int e_local, int cap, 
     const int within = r - o.padded_start[l];
     const bool live = within < o.expert_total[rank * e_local + l];
     uint4* dst = reinterpret_cast<uint4*>(rows_out + static_cast<size_t>(r) * hidden);
-    if (live) {
-      const int org = meta_origin[r];
-      const int first = meta_primary ? meta_primary[r] : r;
+    // An origin word outside [0, world * cap * top_k) can only be a word its source never wrote (a
+    // source that failed its own plan): the row is treated as padding.
+    const int org = live ? meta_origin[r] : -1;
+    if (live && org >= 0 && org < world * cap * top_k) {
+      int first = meta_primary ? meta_primary[r] : r;
+      if (first < 0 || first >= row_capacity) first = r;
       if (first == r) {  // duplicates of a token inside this rank are copied locally afterwards
         const int src = org / (cap * top_k);
         const int token = (org - src * cap * top_k) / top_k;
@@ -100,7 +113,7 @@ __global__ void gather_rows_kernel(OwnerRows o, int rank, int e_local, int cap, 
 }
 
 __global__ void gather_by_origin_kernel(DeviceRange range, const int* __restrict__ origin,
-                                        const int* __restrict__ primary, int cap, int top_k,
+                                        const int* __restrict__ primary, int world, int cap, int top_k,
                                         int hidden, PeerConstRows stage,
                                         __nv_bfloat16* __restrict__ rows_out) {
   const int rows = *range.end;
@@ -110,7 +123,7 @@ __global__ void gather_by_origin_kernel(DeviceRange range, const int* __restrict
   for (int r = *range.begin + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += warps) {
     const int org = origin[r];
     uint4* dst = reinterpret_cast<uint4*>(rows_out + static_cast<size_t>(r) * hidden);
-    if (org >= 0) {
+    if (org >= 0 && org < world * cap * top_k) {
       if (primary != nullptr && primary[r] != r) continue;  // copied locally afterwards
       const int src = org / (cap * top_k);
       const int token = (org - src * cap * top_k) / top_k;
@@ -136,21 +149,22 @@ __global__ void copy_duplicate_rows_kernel(DeviceRange range, const int* __restr
   }
 }
 
-int gather_rows(const OwnerRows& o, int rank, int e_local, int cap, int top_k, int hidden,
+int gather_rows(const OwnerRows& o, int rank, int e_local, int world, int row_capacity, int cap, int top_k,
+                int hidden,
                 const PeerConstRows& stage, const int* meta_origin, const float* meta_prob,
                 const int* meta_primary, __nv_bfloat16* rows_out, int* origin_out, float* prob_out,
                 int* primary_out, int ctas, cudaStream_t stream) {
-  gather_rows_kernel<<<ctas, 256, 0, stream>>>(o, rank, e_local, cap, top_k, hidden, stage,
+  gather_rows_kernel<<<ctas, 256, 0, stream>>>(o, rank, e_local, world, row_capacity, cap, top_k, hidden, stage,
                                                   meta_origin, meta_prob, meta_primary, rows_out,
                                                   origin_out, prob_out, primary_out);
   count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
 }
-int gather_by_origin(DeviceRange rows, const int* origin, const int* primary, int cap, int top_k,
+int gather_by_origin(DeviceRange rows, const int* origin, const int* primary, int world, int cap, int top_k,
                      int hidden, const PeerConstRows& stage, __nv_bfloat16* rows_out, int ctas,
                      cudaStream_t stream) {
-  gather_by_origin_kernel<<<ctas, 256, 0, stream>>>(rows, origin, primary, cap, top_k, hidden, stage,
+  gather_by_origin_kernel<<<ctas, 256, 0, stream>>>(rows, origin, primary, world, cap, top_k, hidden, stage,
                                                    rows_out);
   count_launch();
   WM_CUDA(cudaGetLastError());

@@ -38,29 +38,49 @@ def _unsupported(layer) -> bool:
                 or get("activation_func_clamp_value") is not None or get("glu_linear_offset", 0) != 0)
 
 
+class _ExpertCall:
+    """What one routed-expert call has to remember between its forward and its backward."""
+
+    def __init__(self, manager, layer):
+        self.manager = manager
+        self.runtime = manager.get_runtime(layer)
+        self.version_at_forward = manager.weight_version
+        self.tape = None
+
+    def gradients(self, dy, parameters):
+        manager = self.manager
+        if manager.fp8:
+            # the FP8 tape references the weights prepared at forward time; an optimizer step in between
+            # would make the backward read a different weight version than the forward did
+            if manager.weight_version != self.version_at_forward:
+                raise RuntimeError("Expert weights changed before FP8 backward")
+        else:
+            # all layers share one packed buffer pair: put THIS layer's weights back before using it
+            manager.pack(parameters)
+        return self.runtime.backward_async(self.tape, dy)
+
+
 class _Routed(torch.autograd.Function):
-    """Keeps Megatron's per-expert Parameters as autograd leaves: their gradients are returned one by
-    one so DDP's hooks fire as usual."""
+    """Autograd edge between Megatron's per-expert Parameters and the stacked operator: every Parameter
+    is an input of the function, so each receives its own gradient tensor and DDP's hooks fire as usual.
+    Inputs: (manager, layer, x, routes, gates, fc1 weights..., fc2 weights...)."""
 
     @staticmethod
     def forward(ctx, manager, layer, x, routes, gates, *parameters):
-        ctx.manager = manager
-        ctx.runtime = manager.get_runtime(layer)
-        ctx.weight_version = manager.weight_version
-        ctx.save_for_backward(*parameters)  # autograd then detects an optimizer step before backward
-        ctx.tape = manager.forward_experts(layer, x, routes, gates, parameters)
-        return ctx.tape.output
+        call = _ExpertCall(manager, layer)
+        call.tape = manager.forward_experts(layer, x, routes, gates, parameters)
+        ctx.call = call
+        # saving the Parameters lets autograd itself flag an in-place update made before backward
+        ctx.save_for_backward(*parameters)
+        return call.tape.output
 
     @staticmethod
     def backward(ctx, dy):
-        manager, parameters = ctx.manager, ctx.saved_tensors
-        if manager.fp8 and ctx.weight_version != manager.weight_version:
-            raise RuntimeError("Expert weights changed before FP8 backward")
-        if not manager.fp8:
-            manager.pack(parameters)  # one packed workspace serves all layers: restore this layer's weights
-        dx, dg, dw1, dw2 = ctx.runtime.backward_async(ctx.tape, dy)
-        ctx.tape = ctx.runtime = ctx.manager = None
-        return (None, None, dx, None, dg, *dw1.unbind(), *dw2.unbind())
+        call, ctx.call = ctx.call, None
+        dx, dgates, dw1, dw2 = call.gradients(dy, ctx.saved_tensors)
+        per_expert = [*dw1.unbind(0), *dw2.unbind(0)]
+        # one entry per forward input: manager, layer, x, routes, gates, then the Parameters
+        return (None, None, dx, None, dgates, *per_expert)
 
 
 class MegatronAdapter:
@@ -98,18 +118,20 @@ class MegatronAdapter:
                 for i in range(layer.num_local_experts)]
 
     def pack(self, parameters):
-        """Stack per-expert [2I,H] / [H,I] Parameters into the operator's [E,2I,H] / [E,H,I] tensors.
-        One buffer pair per shape is reused by every layer."""
-        count = len(parameters) // 2
-        key = (count, tuple(parameters[0].shape), tuple(parameters[count].shape))
-        if key not in self.packed:
-            self.packed[key] = (parameters[0].new_empty((count, *parameters[0].shape)),
-                                parameters[count].new_empty((count, *parameters[count].shape)))
-        w1, w2 = self.packed[key]
-        with torch.no_grad():  # the packed tensors are plain buffers; gradients flow through _Routed
-            torch.stack(list(parameters[:count]), out=w1)
-            torch.stack(list(parameters[count:]), out=w2)
-        return w1, w2
+        """The operator wants [E,2I,H] and [E,H,I]; Megatron keeps one [2I,H] and one [H,I] Parameter per
+        local expert.  Copies them, expert by expert, into a buffer pair that is allocated once per
+        (expert count, shapes) and shared by all layers.  Returns (w1, w2)."""
+        half = len(parameters) // 2
+        fc1, fc2 = parameters[:half], parameters[half:]
+        key = (half, tuple(fc1[0].shape), tuple(fc2[0].shape))
+        buffers = self.packed.get(key)
+        if buffers is None:
+            buffers = tuple(group[0].new_empty((half, *group[0].shape)) for group in (fc1, fc2))
+            self.packed[key] = buffers
+        with torch.no_grad():  # plain buffers: the autograd edge to the Parameters is _Routed
+            for buffer, group in zip(buffers, (fc1, fc2)):
+                torch._foreach_copy_(list(buffer.unbind(0)), list(group))   # one multi-tensor copy
+        return buffers
 
     def bind_optimizer(self, optimizer):
         """Reuse prepared FP8 weights until this torch.optim.AdamW steps."""

@@ -35,24 +35,35 @@ class NVFP4Weights:
 
 
 def _validate_scales(scales):
-    if any(not math.isfinite(s) or s <= 0 for s in scales):
-        raise ValueError("NVFP4 tensor scales must be finite and positive")
+    """Layer scales divide and multiply values on the device: each must be a finite positive number."""
+    for value in scales:
+        if not (math.isfinite(value) and value > 0):
+            raise ValueError("NVFP4 tensor scales must be finite and positive")
+
+
+_E4M3_MAX = 448.0            # largest finite E4M3 value: the block scale saturates here
+_E2M1_MAX = 6.0              # largest E2M1 magnitude
+_E4M3_MIN_NORMAL = 2.0 ** -6
 
 
 def nvfp4_block_stats(tensor, scale):
-    """Count finite-input block-16 scale range events along the last (reduction) axis."""
+    """How the block-16 scales of `tensor` (blocks along its last axis) would fare with layer scale
+    `scale`: the number of blocks, and how many of them lose a non-zero block to a zero scale, land on a
+    subnormal E4M3 scale, or exceed the E4M3 range.  Used to calibrate layer scales before quantising
+    (same report as the reference's nvfp4_block_stats, weftmoe/nvfp4.py:102-119).  The counts are device
+    tensors: nothing is synchronised here."""
     _validate_scales((scale,))
-    if not tensor.is_floating_point() or tensor.ndim == 0 or tensor.shape[-1] % 16:
+    usable = tensor.is_floating_point() and tensor.ndim >= 1 and tensor.shape[-1] % 16 == 0
+    if not usable:
         raise ValueError("Expected floating-point data with a last dimension divisible by 16")
-    amax = tensor.detach().unflatten(-1, (-1, 16)).abs().amax(dim=-1).float()
-    unrounded = amax / (6.0 * scale)
-    encoded = unrounded.clamp(max=448).to(torch.float8_e4m3fn).float()
-    return {
-        "blocks": amax.numel(),
-        "nonzero_to_zero": ((amax > 0) & (encoded == 0)).sum(),
-        "subnormal_scale": ((encoded > 0) & (encoded < 2 ** -6)).sum(),
-        "above_range": (unrounded > 448).sum(),
-    }
+    blocks = tensor.detach().reshape(*tensor.shape[:-1], tensor.shape[-1] // 16, 16)
+    block_amax = blocks.abs().amax(dim=-1).float()
+    wanted = block_amax / (_E2M1_MAX * scale)                       # the scale each block asks for
+    stored = wanted.clamp(max=_E4M3_MAX).to(torch.float8_e4m3fn).float()
+    lost = (stored == 0) & (block_amax > 0)
+    tiny = (stored > 0) & (stored < _E4M3_MIN_NORMAL)
+    return {"blocks": block_amax.numel(), "nonzero_to_zero": lost.sum(), "subnormal_scale": tiny.sum(),
+            "above_range": (wanted > _E4M3_MAX).sum()}
 
 
 def quantize_nvfp4(x: torch.Tensor, scale: float, *, chunked: bool = False):
@@ -73,19 +84,28 @@ def quantize_nvfp4(x: torch.Tensor, scale: float, *, chunked: bool = False):
     return data, sf
 
 
+def _is_device_bf16(t):
+    return isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()
+
+
 def prepare_nvfp4_weights(w1, w2, *, weight_scales=(1 / 64, 1 / 64)):
-    """Quantize canonical BF16 expert weights. Scales are layer-wide dequantization factors."""
-    if w1.ndim != 3 or w2.ndim != 3 or w1.shape != (w2.shape[0], 2 * w2.shape[2], w2.shape[1]):
+    """Quantise BF16 expert weights w1 [E, 2I, H] (gate rows, then up rows) and w2 [E, H, I] once:
+    packed E2M1 [E, N, K/2] (int8 storage) plus the scale chunks the block-scaled kernel reads,
+    [E, N/128, K/64, 128] int32.  `weight_scales` are the two layer-wide dequantisation factors."""
+    if w1.ndim != 3 or w2.ndim != 3:
         raise ValueError("Expected canonical expert weights [E,2I,H] and [E,H,I]")
-    if w1.device != w2.device or any(not w.is_cuda or w.dtype != torch.bfloat16 or not w.is_contiguous()
-                                     for w in (w1, w2)):
+    experts, hidden, inter = w2.shape
+    if tuple(w1.shape) != (experts, 2 * inter, hidden):
+        raise ValueError("Expected canonical expert weights [E,2I,H] and [E,H,I]")
+    if not (_is_device_bf16(w1) and _is_device_bf16(w2) and w1.device == w2.device):
         raise ValueError("Expected contiguous CUDA BF16 weights on the same device")
-    if min(w1.shape) <= 0 or len(weight_scales) != 2 or w1.shape[1] % 256 or w1.shape[2] % 128:
+    if experts == 0 or hidden % 128 or inter % 128 or hidden == 0 or inter == 0 or len(weight_scales) != 2:
         raise ValueError("NVFP4 requires H and I divisible by 128 and two weight scales")
     _validate_scales(weight_scales)
-    matrices = []
-    for w, scale in zip((w1, w2), weight_scales):
-        e, n, k = w.shape
-        data, sf = quantize_nvfp4(w.view(e * n, k), scale, chunked=True)
-        matrices.append((data.view(torch.int8).view(e, n, k // 2), sf.view(e, n // 128, k // 64, 128)))
-    return NVFP4Weights(*matrices, tuple(weight_scales))
+
+    def pack(weight, scale):
+        e, n, k = weight.shape
+        data, chunks = quantize_nvfp4(weight.view(e * n, k), scale, chunked=True)
+        return data.view(torch.int8).view(e, n, k // 2), chunks.view(e, n // 128, k // 64, 128)
+
+    return NVFP4Weights(pack(w1, weight_scales[0]), pack(w2, weight_scales[1]), tuple(weight_scales))
