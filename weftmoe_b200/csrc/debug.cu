@@ -39,7 +39,8 @@ extern "C" int wm_debug_grouped_gemm(int kind, const void* a, const void* b, voi
   const int num_tiles = static_cast<int>(tile_group.size());
   tile_group.push_back(0);
   int *d_num = nullptr, *d_tiles = nullptr, *d_starts = nullptr, *d_pairs = nullptr;
-  const int split[8] = {num_tiles, num_tiles, num_pairs, num_pairs, rows, rows, 0, 0};
+  int split[kSplitWords];
+  fill_whole_split(split, num_tiles, num_pairs, rows);
   WM_CUDA(cudaMalloc(&d_pairs, pairs.size() * sizeof(int)));
   WM_CUDA(cudaMemcpyAsync(d_pairs, pairs.data(), pairs.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
   WM_CUDA(cudaMalloc(&d_num, sizeof(split)));

@@ -28,6 +28,25 @@ __device__ __forceinline__ void load_pack32(uint32_t taddr, bool zero, uint32_t 
   for (int j = 0; j < 16; ++j)
     w[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
 }
+// One step of a software-pipelined read-out in 64-column groups: wait for the group whose load is in
+// flight in `v`, round it to BF16 into `w`, and (when `next_taddr` != 0) start the load of the next
+// group into `v`, so that its latency overlaps whatever the caller does with `w`.
+__device__ __forceinline__ void take_pack64(uint32_t (&v)[64], uint32_t (&w)[32], uint32_t next_taddr) {
+  tmem_ld_wait();
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    w[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+  if (next_taddr != 0) tmem_ld_32x64(next_taddr, v);
+}
+// 64 packed BF16 columns (32 words) of row `lane` into chunk groups 2*c64, 2*c64+1 of the staging block.
+__device__ __forceinline__ void stage_put64(uint8_t* stage, int lane, int c64, const uint32_t (&w)[32]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int pos = (c64 * 8 + j) ^ (lane & 15);
+    *reinterpret_cast<uint4*>(stage + lane * 256 + pos * 16) =
+        make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+  }
+}
 // Write the staged 32 x 128 block: half-warp h handles row 2*it + h, lane&15 picks the 16-byte
 // chunk.  `row_dst(r)` returns the global address of column 0 of the block in row r (or nullptr
 // to skip the row).
@@ -82,28 +101,45 @@ template <int BLOCK_N>
 struct EpilogueStoreTma {
   alignas(64) CUtensorMap tmap;
   int rows_per_group;  // K-grouped: M (rows of one expert's output); 0 for M-grouped
+  int debug_skip;      // diagnostics (WM_DEBUG_EPILOGUE): 1 = pack but issue no store, 2 = read TMEM only
 
   __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane,
                                              bool zero, uint8_t* stage) const {
     const int row0 = t.group * rows_per_group + t.m_tile * kBlockM + q * 32;
     const int col0 = t.n_tile * BLOCK_N;
-#pragma unroll 1
-    for (int unit = 0; unit < BLOCK_N / 64; ++unit) {
+    constexpr int kUnits = BLOCK_N / 64;
+    // Software pipeline over the 64-column units: the TMEM load of unit u+1 is issued as soon as unit
+    // u's registers are packed, so its latency overlaps the shared-memory writes and the store issue of
+    // unit u instead of standing in front of every unit.
+    uint32_t v[64];
+    if (!zero) tmem_ld_32x64(taddr, v);
+#pragma unroll
+    for (int unit = 0; unit < kUnits; ++unit) {
+      uint32_t w[32];
+      if (zero) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) w[j] = 0;
+      } else {
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          w[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+        if (unit + 1 < kUnits) tmem_ld_32x64(taddr + (unit + 1) * 64, v);
+      }
       uint8_t* box = stage + (unit & 1) * 4096;
+      if (debug_skip == 2) {
+        if (w[0] == 0x7fc07fc1u) box[lane] = 1;  // keeps the read-out alive; never true for packed sums
+        continue;
+      }
       if (lane == 0) bulk_wait_group_read<1>();  // the store issued from this box two units ago
       __syncwarp();
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t w[16];
-        load_pack32(taddr + unit * 64 + c * 32, zero, w);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(box + lane * 128 + (((c * 4 + j) ^ (lane & 7)) << 4)) =
-              make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-      }
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(box + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+            make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
+      if (lane == 0 && debug_skip == 0) {
         tma_store_2d(&tmap, box, col0 + unit * 64, row0);
         bulk_commit_group();
       }
@@ -302,13 +338,19 @@ struct EpiloguePush {
       my_dst = reinterpret_cast<unsigned long long>(
           select_mailbox(src) + (static_cast<long long>(slot) * cap + token) * ld + t.n_tile * BLOCK_N);
     }
-#pragma unroll 1
+    // 64-column groups, read one group ahead: the load of the next group (or half) is in flight while
+    // this half is staged and written out.
+    constexpr int kGroups = BLOCK_N / 64;
+    uint32_t v[64];
+    tmem_ld_32x64(taddr, v);
+#pragma unroll
     for (int half = 0; half < BLOCK_N / 128; ++half) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t w[16];
-        load_pack32(taddr + half * 128 + c * 32, false, w);
-        stage_put32(stage, lane, c, w);
+      for (int c = 0; c < 2; ++c) {
+        const int group = half * 2 + c;
+        uint32_t w[32];
+        take_pack64(v, w, group + 1 < kGroups ? taddr + (group + 1) * 64 : 0u);
+        stage_put64(stage, lane, c, w);
       }
       __syncwarp();
       stage_flush(stage, lane, [my_dst, half](int r) {

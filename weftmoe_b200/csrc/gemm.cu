@@ -45,8 +45,54 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
+// Encoded maps are cached per thread by (base, shape, box): a training step issues the same dozen
+// descriptions every call (weights, row buffers of the arena and scratch, tape sections that the
+// caching allocator hands back at the same addresses), so steady-state calls encode nothing on the host.
+// A map only describes addresses and extents, it holds no reference to the memory: a stale entry whose
+// key matches again describes the same bytes.
+namespace {
+struct TmapKey {
+  const void* base;
+  uint64_t inner, outer, stride;
+  uint32_t box_inner, box_outer;
+  int elem_bytes;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && inner == o.inner && outer == o.outer && stride == o.stride &&
+           box_inner == o.box_inner && box_outer == o.box_outer && elem_bytes == o.elem_bytes;
+  }
+};
+struct TmapSlot {
+  TmapKey key{};
+  CUtensorMap map;
+  bool used = false;
+};
+constexpr int kTmapSlots = 256;  // direct-mapped; a collision just re-encodes
+}  // namespace
+
+static int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
+                          uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
+
 int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
                  uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  static thread_local TmapSlot cache[kTmapSlots];
+  const TmapKey key{base, inner, outer, row_stride_bytes, box_inner, box_outer, elem_bytes};
+  uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
+  h = (h ^ (inner * 0x9E3779B97F4A7C15ull) ^ (outer * 0xC2B2AE3D27D4EB4Full) ^ (box_outer * 0x165667B19E3779F9ull) ^
+       (static_cast<uint64_t>(box_inner) << 7) ^ static_cast<uint64_t>(elem_bytes)) * 0xD6E8FEB86659FD93ull;
+  TmapSlot& slot = cache[(h >> 40) % kTmapSlots];
+  if (slot.used && slot.key == key) {
+    *out = slot.map;
+    return 0;
+  }
+  if (int rc = encode_tmap_2d(out, base, elem_bytes, inner, outer, row_stride_bytes, box_inner, box_outer)) return rc;
+  slot.key = key;
+  slot.map = *out;
+  slot.used = true;
+  return 0;
+}
+
+static int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
+                          uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
   auto fn = encode_fn();
   if (!fn) {
     set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
@@ -91,10 +137,22 @@ static int forced_pairs() {
   }
   return value;
 }
-static bool use_pairs(const Schedule& s, bool backward_contraction) {
+// Per-contraction overrides for A/B runs: WM_PAIR_FWD (FC1 / FC2), WM_PAIR_DGRAD (dU / dX), WM_PAIR_WGRAD
+// (dW1 / dW2) = 0 / 1; unset = the measured default below.
+enum Contraction { kForward = 0, kDgrad = 1, kWgrad = 2 };
+static int contraction_override(Contraction c) {
+  static const int values[3] = {
+      [] { const char* v = std::getenv("WM_PAIR_FWD"); return v ? (v[0] != '0') : -1; }(),
+      [] { const char* v = std::getenv("WM_PAIR_DGRAD"); return v ? (v[0] != '0') : -1; }(),
+      [] { const char* v = std::getenv("WM_PAIR_WGRAD"); return v ? (v[0] != '0') : -1; }()};
+  return values[c];
+}
+static bool use_pairs(const Schedule& s, Contraction c) {
   const int forced = forced_pairs();
   if (forced >= 0) return forced == 1;
-  return backward_contraction && s.many_rows_per_expert;
+  const int override = contraction_override(c);
+  if (override >= 0) return override == 1;
+  return c != kForward && s.many_rows_per_expert;
 }
 
 template <int BLOCK_N, bool A_MN, bool B_MN, bool GATE_UP, bool K_GROUPED, class Epi, int EPI_WARPS = 4>
@@ -123,7 +181,7 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
     WM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  const DeviceRange pairs = split_range(s.split, 1, s.half);
+  const DeviceRange pairs = split_range(s.split, 1, s.chunk);
   Gemm2Args a2{args, pairs.begin, pairs.end, s.pair_tiles};
   kernel<<<sms & ~1, kGemmThreads, smem, stream>>>(ta, tb, a2, epi);  // clusters of two CTAs
   WM_CUDA(cudaGetLastError());
@@ -204,11 +262,12 @@ static bool tma_epilogue() {
 
 static GemmArgs base_args(const Schedule& s, int* status) {
   GemmArgs a{};
-  const DeviceRange tiles = split_range(s.split, 0, s.half);
+  const DeviceRange tiles = split_range(s.split, 0, s.chunk);
   a.tile_begin = tiles.begin;
   a.tile_end = tiles.end;
   a.tile_group = s.tile_group;
   a.group_row_start = s.group_row_start;
+  a.group_live_rows = s.group_live_rows;
   a.groups = s.groups;
   a.status = status;
   return a;
@@ -228,7 +287,7 @@ int launch_fc1(const Schedule& s, const __nv_bfloat16* x, const __nv_bfloat16* w
   a.gate_up_half = inter;
   EpilogueSwiglu epi{u, ab, row_prob, inter};
   TimelineScope timeline("fc1", a);
-  return launch<256, false, false, true, false>(use_pairs(s, false), ta, tb, a, s, epi, sms, stream);
+  return launch<256, false, false, true, false>(use_pairs(s, kForward), ta, tb, a, s, epi, sms, stream);
 }
 
 template <bool B_MN>
@@ -242,7 +301,7 @@ static int launch_mgrouped(const Schedule& s, const __nv_bfloat16* a_ptr, const 
     set_error("grouped GEMM needs N %% 128 == 0, got %d", n);
     return 2;
   }
-  const bool pair = use_pairs(s, B_MN);  // B MN-major = dU / dX
+  const bool pair = use_pairs(s, B_MN ? kDgrad : kForward);  // B MN-major = dU / dX
   if (B_MN) {
     if (int rc = make_tmap_2d(&tb, b_ptr, 2, n, (uint64_t)s.groups * k, (uint64_t)n * 2, 64, 64)) return rc;
   } else {
@@ -272,6 +331,7 @@ static int launch_mgrouped(const Schedule& s, const __nv_bfloat16* a_ptr, const 
     EpilogueStoreTma<256> epi{};
     if (int rc = make_tmap_2d(&epi.tmap, out, 2, n, s.row_capacity, (uint64_t)n * 2, 64, 32)) return rc;
     epi.rows_per_group = 0;
+    epi.debug_skip = 0;
     return launch<256, false, B_MN, false, false>(pair, ta, tb, a, s, epi, sms, stream);
   }
   if (bn == 256) {
@@ -286,7 +346,7 @@ int launch_du_swiglu_backward(const Schedule& s, const __nv_bfloat16* dy_rows, c
                               const __nv_bfloat16* ab, const float* row_prob, __nv_bfloat16* u,
                               __nv_bfloat16* dab, float* dprob_part, int inter, int hidden, int* status,
                               int sms, cudaStream_t stream) {
-  if (inter % 256 || use_pairs(s, true)) return -1;
+  if (inter % 256 || use_pairs(s, kDgrad)) return -1;
   CUtensorMap ta, tb;
   if (int rc = make_tmap_2d(&ta, dy_rows, 2, hidden, s.row_capacity, (uint64_t)hidden * 2, 64, 128)) return rc;
   if (int rc = make_tmap_2d(&tb, w2, 2, inter, (uint64_t)s.groups * hidden, (uint64_t)inter * 2, 64, 64)) return rc;
@@ -321,7 +381,7 @@ int launch_kgrouped_tn(const Schedule& s, const __nv_bfloat16* a_ptr, const __nv
   if (int rc = make_tmap_2d(&ta, a_ptr, 2, m, s.row_capacity, (uint64_t)m * 2, 64, 64)) return rc;
   if (int rc = make_tmap_2d(&tb, b_ptr, 2, n, s.row_capacity, (uint64_t)n * 2, 64, 64)) return rc;
   const int bn = (n % 256 == 0) ? 256 : 128;
-  const bool pair = use_pairs(s, true) && m % 256 == 0;  // a pair covers 256 output rows
+  const bool pair = use_pairs(s, kWgrad) && m % 256 == 0;  // a pair covers 256 output rows
   GemmArgs a = base_args(s, status);
   a.m_tiles_per_group = m / 128;
   a.n_tiles = n / bn;
@@ -330,6 +390,8 @@ int launch_kgrouped_tn(const Schedule& s, const __nv_bfloat16* a_ptr, const __nv
     EpilogueStoreTma<256> epi{};
     if (int rc = make_tmap_2d(&epi.tmap, out, 2, n, (uint64_t)s.groups * m, (uint64_t)n * 2, 64, 32)) return rc;
     epi.rows_per_group = m;
+    static const int debug_skip = [] { const char* v = std::getenv("WM_DEBUG_EPILOGUE"); return v ? std::atoi(v) : 0; }();
+    epi.debug_skip = debug_skip;
     return launch<256, true, true, false, true>(pair, ta, tb, a, s, epi, sms, stream);
   }
   if (bn == 256) {

@@ -36,6 +36,7 @@ struct GemmArgs {
   const int* tile_end;
   const int* tile_group;       // M-grouped: expert of each 128-row tile
   const int* group_row_start;  // K-grouped: [groups + 1] padded row offsets (multiples of 64)
+  const int* group_live_rows;  // K-grouped, optional: [groups] rows that are not padding (the rest are zero)
   int groups;                  // K-grouped: number of experts
   int m_tiles_per_group;       // K-grouped: M_total / 128
   int n_tiles;                 // N_total / BLOCK_N  (gate/up pair: I / 128)
@@ -75,6 +76,15 @@ struct TileCoord {
   int num_kb;    // number of 64-wide k blocks
 };
 
+// Reduction length of a K-grouped tile in 64-row blocks: the expert's padded rows, or, when the live
+// row counts are known, only the blocks that hold a live row (the padding rows behind them are zero in
+// both operands, so leaving their blocks out changes no bit of the result).
+__device__ __forceinline__ int kgrouped_k_blocks(const GemmArgs& a, int group, int row0) {
+  const int padded = __ldg(a.group_row_start + group + 1) - row0;
+  const int rows = a.group_live_rows != nullptr ? min(__ldg(a.group_live_rows + group), padded) : padded;
+  return (rows + kBlockK - 1) / kBlockK;
+}
+
 template <bool K_GROUPED>
 __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& a, int tile) {
   TileCoord t;
@@ -91,7 +101,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& a, int tile) {
     t.m_tile = rem / a.n_tiles;
     t.n_tile = rem - t.m_tile * a.n_tiles;
     t.row0 = __ldg(a.group_row_start + t.group);
-    t.num_kb = (__ldg(a.group_row_start + t.group + 1) - t.row0) / kBlockK;
+    t.num_kb = kgrouped_k_blocks(a, t.group, t.row0);
   }
   return t;
 }

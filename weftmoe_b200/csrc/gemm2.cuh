@@ -73,7 +73,7 @@ __device__ __forceinline__ PairTile decode_pair(const Gemm2Args& a, int work, in
     p.load_m = p.t.m_tile;
     p.live = true;
     p.t.row0 = __ldg(g.group_row_start + p.t.group);
-    p.t.num_kb = (__ldg(g.group_row_start + p.t.group + 1) - p.t.row0) / kBlockK;
+    p.t.num_kb = kgrouped_k_blocks(g, p.t.group, p.t.row0);
   }
   return p;
 }

@@ -40,14 +40,15 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t in
 
 // ------------------------------------------------------------------ grouped GEMM launchers
 struct Schedule {
-  const int* split;            // device [8]: tile / pair / row split points and totals (route.h)
+  const int* split;            // device [kSplitWords]: tile / pair / row chunk boundaries (route.h)
   const int* tile_group;       // device [max tiles]
   const int* group_row_start;  // device [groups + 1]
   int groups;
   int row_capacity;            // rows addressable in the row-indexed operands
   const int* pair_tiles;       // device [2 * pairs]: CTA-pair work items (two tiles of one expert)
   bool many_rows_per_expert;   // host estimate: experts average >= 1024 rows (long K loops, few odd tiles)
-  int half;                    // which part of the M-grouped work to run: 0 all, 1 first half, 2 second half
+  int chunk;                   // which chunk of the M-grouped work to run (kWhole = all of it)
+  const int* group_live_rows = nullptr;  // device [groups], optional: unpadded rows per expert (K-grouped)
 };
 
 struct PushTarget {

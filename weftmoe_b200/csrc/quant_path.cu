@@ -268,7 +268,7 @@ int launch_bs_grouped(const Schedule& s, const void* a, const SfLayout& sfa, con
   if (int rc = make_tmap_2d(&ta, a, 1, kbytes, s.row_capacity, kbytes, 128, 128)) return rc;
   if (int rc = make_tmap_2d(&tb, b, 1, kbytes, static_cast<uint64_t>(s.groups) * n, kbytes, 128, 128)) return rc;
   BsArgs args{};
-  const DeviceRange tiles = split_range(s.split, 0, s.half);
+  const DeviceRange tiles = split_range(s.split, 0, s.chunk);
   args.base.tile_begin = tiles.begin;
   args.base.tile_end = tiles.end;
   args.base.tile_group = s.tile_group;

@@ -94,33 +94,24 @@ __global__ void chunk_scan_kernel(int* __restrict__ chunk_hist, int chunks, int 
 // copies) or zero-length reductions (K-grouped GEMMs then write zero gradients).
 __device__ void publish_empty_schedule(const PlanTables& t, int e_local) {
   for (int l = threadIdx.x; l <= e_local; l += blockDim.x) t.padded_start[l] = 0;
+  if (t.live_rows != nullptr)
+    for (int l = threadIdx.x; l < e_local; l += blockDim.x) t.live_rows[l] = 0;
   if (threadIdx.x == 0) {
     *t.num_tiles = 0;
     *t.padded_rows = 0;
     *t.num_pairs = 0;
   }
-  if (t.split != nullptr && threadIdx.x < 8) t.split[threadIdx.x] = 0;
+  if (t.split != nullptr && threadIdx.x < kSplitWords) t.split[threadIdx.x] = 0;
 }
 
-__global__ void global_plan_kernel(const int* __restrict__ count_matrix, const int* flag_counts,
-                                   Gen gen, int world, int rank, int experts,
-                                   int row_capacity, PlanTables t, int* status, int split_percent,
-                                   long long wait_budget) {
-  extern __shared__ int sh[];
-  int* total = sh;               // [experts]
-  int* padded = sh + experts;    // [experts]
-  __shared__ int ok, overflow;
-  if (threadIdx.x == 0) { ok = 1; overflow = 0; }
-  __syncthreads();
-  if (threadIdx.x < world) {
-    if (!wait_flag_ge(flag_counts + threadIdx.x * kFlagStride, gen.value(), status, wait_budget)) ok = 0;
-  }
-  __syncthreads();
+// The plan itself, for one CTA whose threads have all seen every count row (callers wait for the COUNTS
+// flags and synchronise the block first).  total / padded: [experts] words, pair_first: [513] words and
+// flags: [1] word of shared memory.
+__device__ void global_plan_body(const int* __restrict__ count_matrix, int world, int rank, int experts,
+                                 int row_capacity, const PlanTables& t, int* status, int split_percent,
+                                 int chunks, int* total, int* padded, int* pair_first, int* overflow) {
   const int e_local = experts / world;
-  if (!ok) {  // a count row never arrived: the status word is set, nothing may be derived from the counts
-    publish_empty_schedule(t, e_local);
-    return;
-  }
+  if (threadIdx.x == 0) *overflow = 0;
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
     int sum = 0, before = 0;
     for (int s = 0; s < world; ++s) {
@@ -147,7 +138,7 @@ __global__ void global_plan_kernel(const int* __restrict__ count_matrix, const i
     // Every rank holds the same count matrix and the same row capacity, so every rank sees every
     // owner's overflow and all of them fail the call together (the reference checks every destination
     // rank's rows on every rank too: src/metadata/notify_dispatch.cpp:2003-2035).
-    if (pbase > row_capacity) overflow = 1;
+    if (pbase > row_capacity) *overflow = 1;
     if (threadIdx.x == rank) {
       *t.num_tiles = pbase / 128;
       *t.padded_rows = pbase;
@@ -155,15 +146,14 @@ __global__ void global_plan_kernel(const int* __restrict__ count_matrix, const i
     }
   }
   __syncthreads();
-  if (overflow || *t.padded_rows == 0) {
-    if (overflow && threadIdx.x == 0) atomicCAS(status, 0, kStatusRowOverflow);
+  if (*overflow || *t.padded_rows == 0) {
+    if (*overflow && threadIdx.x == 0) atomicCAS(status, 0, kStatusRowOverflow);
     __syncthreads();
     publish_empty_schedule(t, e_local);
     return;
   }
   // CTA-pair schedule: consecutive 128-row tiles of one expert are paired; an odd last tile
   // is paired with -1.  pair_first[l] = pairs of lower local experts (sequential, E/EP <= 512).
-  __shared__ int pair_first[513];
   if (threadIdx.x == 0) {
     int p = 0;
     for (int l = 0; l < e_local; ++l) {
@@ -172,18 +162,27 @@ __global__ void global_plan_kernel(const int* __restrict__ count_matrix, const i
     }
     *t.num_pairs = p;
     if (t.split != nullptr) {
-      // first expert boundary at or beyond split_percent of the padded rows (half by default)
+      // Chunk c ends at the first expert boundary at or beyond c / chunks of the padded rows (with two
+      // chunks: at split_percent of them).
       const int total_rows = *t.padded_rows;
+      int* tiles_b = t.split;
+      int* pairs_b = t.split + kSplitStride;
+      int* rows_b = t.split + 2 * kSplitStride;
+      tiles_b[0] = pairs_b[0] = rows_b[0] = 0;
       int rows = 0, l = 0;
-      while (l < e_local && 100ll * rows < 1ll * split_percent * total_rows) rows += padded[rank * e_local + l++];
-      t.split[0] = rows / 128;
-      t.split[1] = total_rows / 128;
-      t.split[2] = l < e_local ? pair_first[l] : p;
-      t.split[3] = p;
-      t.split[4] = rows;
-      t.split[5] = total_rows;
-      t.split[6] = 0;
-      t.split[7] = 0;
+      for (int c = 1; c <= kMaxChunks; ++c) {
+        if (c < chunks) {
+          const long long share = chunks == 2 ? split_percent : 100ll * c / chunks;
+          while (l < e_local && 100ll * rows < share * total_rows) rows += padded[rank * e_local + l++];
+          tiles_b[c] = rows / 128;
+          pairs_b[c] = l < e_local ? pair_first[l] : p;
+          rows_b[c] = rows;
+        } else {
+          tiles_b[c] = total_rows / 128;
+          pairs_b[c] = p;
+          rows_b[c] = total_rows;
+        }
+      }
     }
   }
   __syncthreads();
@@ -192,12 +191,36 @@ __global__ void global_plan_kernel(const int* __restrict__ count_matrix, const i
     const int start = t.expert_pbase[e];
     const int tiles = padded[e] / 128;
     t.padded_start[l] = start;
+    if (t.live_rows != nullptr) t.live_rows[l] = total[e];
     for (int k = 0; k < tiles; ++k) t.tile_group[start / 128 + k] = l;
     for (int j = 0; j < (tiles + 1) / 2; ++j) {
       t.pair_tiles[2 * (pair_first[l] + j)] = start / 128 + 2 * j;
       t.pair_tiles[2 * (pair_first[l] + j) + 1] = (2 * j + 1 < tiles) ? start / 128 + 2 * j + 1 : -1;
     }
   }
+}
+
+__global__ void global_plan_kernel(const int* __restrict__ count_matrix, const int* flag_counts,
+                                   Gen gen, int world, int rank, int experts,
+                                   int row_capacity, PlanTables t, int* status, int split_percent,
+                                   int chunks, long long wait_budget) {
+  extern __shared__ int sh[];
+  int* total = sh;               // [experts]
+  int* padded = sh + experts;    // [experts]
+  __shared__ int ok, overflow;
+  __shared__ int pair_first[513];
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    if (!wait_flag_ge(flag_counts + threadIdx.x * kFlagStride, gen.value(), status, wait_budget)) ok = 0;
+  }
+  __syncthreads();
+  if (!ok) {  // a count row never arrived: the status word is set, nothing may be derived from the counts
+    publish_empty_schedule(t, experts / world);
+    return;
+  }
+  global_plan_body(count_matrix, world, rank, experts, row_capacity, t, status, split_percent, chunks, total,
+                   padded, pair_first, &overflow);
 }
 
 // ------------------------------------------------------------------ K2c: destination rows + meta push
@@ -275,6 +298,154 @@ __global__ void route_primary_kernel(const int* __restrict__ slot_pos,
   if (per_route) per_route[i] = dst_prow[head];
 }
 
+// ------------------------------------------------------------------ Ks: the whole plan in one CTA
+// For calls of at most kSmallPlanRoutes routes (decode, small prefill): per-token sort, stable ordinals
+// and counts, count exchange, global plan, destination rows, origin / prob / primary words to the
+// owners and the READY hand-shake, all in ONE launch of one 1024-thread CTA instead of nine small
+// launches in a row.  Every step computes exactly what the stand-alone kernels above compute.
+// Shared memory: total[E], padded[E], running[E] ints and warp_cnt[32][E] shorts.
+__global__ void __launch_bounds__(1024, 1) plan_small_kernel(const SmallPlan a) {
+  extern __shared__ int sh[];
+  const int E = a.shape.experts, K = a.shape.top_k, world = a.shape.world, rank = a.shape.rank;
+  int* total = sh;
+  int* padded = sh + E;
+  int* running = sh + 2 * E;
+  unsigned short* warp_cnt = reinterpret_cast<unsigned short*>(sh + 3 * E);  // [32][E]
+  __shared__ int pair_first[513];
+  __shared__ int ok, overflow;
+  const int n = a.tokens * K;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int generation = a.generation.value();
+
+  // (1) per-token combine order: one warp per token
+  for (int token = warp; token < a.tokens; token += 32) {
+    const int id = lane < K ? a.routes[token * K + lane] : E + 1;
+    const bool valid = id >= 0 && id < E;
+    const int key = lane < K ? (valid ? id : E) : E + 1;
+    int pos = 0;
+    for (int j = 0; j < K; ++j) {
+      const int kj = __shfl_sync(0xffffffffu, key, j);
+      pos += (kj < key) || (kj == key && j < lane);
+    }
+    if (lane < K) {
+      a.local.sorted_slot[token * K + pos] = lane;
+      a.local.sorted_expert[token * K + pos] = valid ? id : -1;
+      a.local.slot_pos[token * K + lane] = pos;
+    }
+  }
+  // (2) stable ordinal of every route among this rank's routes to the same expert (route order), 1024
+  //     routes at a time; `running` ends as the per-expert counts
+  for (int e = threadIdx.x; e < E; e += blockDim.x) running[e] = 0;
+  __syncthreads();
+  for (int base = 0; base < n; base += 1024) {
+    for (int k = threadIdx.x; k < 16 * E; k += blockDim.x) reinterpret_cast<int*>(warp_cnt)[k] = 0;
+    __syncthreads();
+    const int i = base + threadIdx.x;
+    const int id = i < n ? a.routes[i] : -1;
+    const bool valid = id >= 0 && id < E;
+    const unsigned peers = __match_any_sync(0xffffffffu, valid ? id : E);
+    const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (valid && rank_in_warp == 0) warp_cnt[warp * E + id] = static_cast<unsigned short>(__popc(peers));
+    __syncthreads();
+    if (i < n) {
+      int ordinal = -1;
+      if (valid) {
+        ordinal = running[id] + rank_in_warp;
+        for (int w = 0; w < warp; ++w) ordinal += warp_cnt[w * E + id];
+      }
+      a.rows.local_offset[i] = ordinal;
+    }
+    __syncthreads();
+    if (valid && rank_in_warp == 0) atomicAdd(&running[id], __popc(peers));
+    __syncthreads();
+  }
+  // (3) counts to every rank's matrix, then the COUNTS flag
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    a.local_count[e] = running[e];
+    for (int r = 0; r < world; ++r)
+      if (a.count_matrix.p[r] != nullptr) a.count_matrix.p[r][rank * E + e] = running[e];
+  }
+  if (a.exchange) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < world) st_release_sys(a.flag_counts.p[threadIdx.x] + rank * kFlagStride, generation);
+  }
+  if (!a.global_part) return;
+  // (4) every rank's counts, the global plan
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (a.exchange && threadIdx.x < world &&
+      !wait_flag_ge(a.my_flag_counts + threadIdx.x * kFlagStride, generation, a.status, a.wait_budget))
+    ok = 0;
+  __syncthreads();
+  if (!ok) {
+    publish_empty_schedule(a.tables, E / world);
+  } else {
+    global_plan_body(a.my_count_matrix, world, rank, E, a.row_capacity, a.tables, a.status, a.split_percent,
+                     a.chunks, total, padded, pair_first, &overflow);
+  }
+  __syncthreads();
+  // (5) destination rows and the words the owners need; nothing on a failed plan (sticky status word)
+  const bool healthy = *reinterpret_cast<volatile int*>(a.status) == 0;
+  const int e_local = E / world;
+  if (healthy) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const int id = a.routes[i];
+      if (id < 0 || id >= E) {
+        a.rows.dst_rank[i] = a.rows.dst_row[i] = a.rows.dst_prow[i] = -1;
+        continue;
+      }
+      const int owner = id / e_local;
+      const int within = a.tables.expert_before[id] + a.rows.local_offset[i];
+      const int prow = a.tables.expert_pbase[id] + within;
+      a.rows.dst_rank[i] = owner;
+      a.rows.dst_row[i] = a.tables.expert_base[id] + within;
+      a.rows.dst_prow[i] = prow;
+      if (a.meta_origin.p[owner] != nullptr && prow >= 0 && prow < a.row_capacity) {
+        a.meta_origin.p[owner][prow] = rank * a.shape.cap * K + (i / K) * K + a.local.slot_pos[i];
+        a.meta_prob.p[owner][prow] = a.gates[i];
+      }
+    }
+    __syncthreads();
+    if (a.want_primary) {
+      for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int owner = a.rows.dst_rank[i];
+        if (owner < 0) {
+          if (a.per_route_primary) a.per_route_primary[i] = -1;
+          continue;
+        }
+        const int first = (i / K) * K;
+        int head = i, head_pos = a.local.slot_pos[i];
+        for (int j = 0; j < K; ++j) {
+          const int r = first + j;
+          if (a.rows.dst_rank[r] == owner && a.local.slot_pos[r] < head_pos) {
+            head = r;
+            head_pos = a.local.slot_pos[r];
+          }
+        }
+        const int prow = a.rows.dst_prow[i];
+        if (a.meta_primary.p[owner] != nullptr && prow >= 0 && prow < a.row_capacity)
+          a.meta_primary.p[owner][prow] = a.rows.dst_prow[head];
+        if (a.per_route_primary) a.per_route_primary[i] = a.rows.dst_prow[head];
+      }
+    }
+  }
+  // (6) READY hand-shake: my words are in the owners' arenas; wait for every source's words
+  if (a.exchange) {
+    __threadfence_system();
+    __syncthreads();
+    bool arrived = true;
+    if (threadIdx.x < world) {
+      st_release_sys(a.flag_ready.p[threadIdx.x] + rank * kFlagStride, generation);
+      arrived = wait_flag_ge(a.my_flag_ready + threadIdx.x * kFlagStride, generation, a.status, a.wait_budget);
+    }
+    if (threadIdx.x < 32) {
+      const bool failed = __any_sync(0xffffffffu, !arrived) || *reinterpret_cast<volatile int*>(a.status) != 0;
+      if (failed && a.tables.split != nullptr && threadIdx.x < kSplitWords) a.tables.split[threadIdx.x] = 0;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ host side
 static std::atomic<long long> g_flag_wait_budget{kWaitBudgetCycles};
 long long flag_wait_budget() { return g_flag_wait_budget.load(std::memory_order_relaxed); }
@@ -290,6 +461,31 @@ int route_primary(const RouteShape& s, int tokens, const RouteLocal& local, cons
   route_primary_kernel<<<(n + 255) / 256, 256, 0, stream>>>(local.slot_pos, rows.dst_rank, rows.dst_prow, n,
                                                            s.top_k, meta_primary, per_route, row_capacity,
                                                            status);
+  count_launch();
+  WM_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int route_plan_small(SmallPlan plan, cudaStream_t stream) {
+  static const int split_percent = [] {
+    const char* v = std::getenv("WM_SPLIT_PERCENT");
+    const int n = v ? std::atoi(v) : 50;
+    return n >= 10 && n <= 90 ? n : 50;
+  }();
+  plan.split_percent = split_percent;
+  plan.wait_budget = flag_wait_budget();
+  plan.chunks = plan.chunks < 1 ? 1 : (plan.chunks > kMaxChunks ? kMaxChunks : plan.chunks);
+  const int E = plan.shape.experts;
+  const size_t smem = static_cast<size_t>(E) * (3 * sizeof(int) + 32 * sizeof(unsigned short));
+  static bool configured[64] = {};
+  int device = 0;
+  WM_CUDA(cudaGetDevice(&device));
+  if (device >= 0 && device < 64 && !configured[device]) {
+    WM_CUDA(cudaFuncSetAttribute(plan_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 2048 * (3 * (int)sizeof(int) + 32 * (int)sizeof(unsigned short))));
+    configured[device] = true;
+  }
+  plan_small_kernel<<<1, 1024, smem, stream>>>(plan);
   count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;
@@ -316,9 +512,9 @@ int route_local(const RouteShape& s, const int* routes, int tokens, RouteLocal o
 }
 
 int route_global(const RouteShape& s, const int* count_matrix, const int* flag_counts,
-                 Gen generation, int row_capacity, PlanTables t, int* status, cudaStream_t stream) {
-  // Share of the owner's rows in the first of the two halves that are pipelined at world > 1
-  // (WM_SPLIT_PERCENT, 10..90).
+                 Gen generation, int row_capacity, PlanTables t, int* status, int chunks,
+                 cudaStream_t stream) {
+  // With two chunks: share of the owner's rows in the first one (WM_SPLIT_PERCENT, 10..90).
   static const int split_percent = [] {
     const char* v = std::getenv("WM_SPLIT_PERCENT");
     const int n = v ? std::atoi(v) : 50;
@@ -326,7 +522,7 @@ int route_global(const RouteShape& s, const int* count_matrix, const int* flag_c
   }();
   global_plan_kernel<<<1, 1024, 2 * s.experts * sizeof(int), stream>>>(
       count_matrix, flag_counts, generation, s.world, s.rank, s.experts, row_capacity, t, status, split_percent,
-      flag_wait_budget());
+      chunks < 1 ? 1 : (chunks > kMaxChunks ? kMaxChunks : chunks), flag_wait_budget());
   count_launch();
   WM_CUDA(cudaGetLastError());
   return 0;

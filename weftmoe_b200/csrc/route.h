@@ -54,30 +54,81 @@ struct PlanTables {
   int* padded_rows;    // scalar
   int* pair_tiles;     // [2 * pairs] two 128-row tiles of one expert per CTA pair, -1 = none
   int* num_pairs;      // scalar
-  // Optional [8]: the owner's work split at an expert boundary near the middle, so that the second
-  // half's transfers can overlap the first half's compute:
-  //   [0] tile split  [1] tiles  [2] pair split  [3] pairs  [4] row split  [5] padded rows  [6] 0
+  // Optional [kSplitWords]: the owner's work cut at expert boundaries into up to kMaxChunks chunks, so
+  // that a later chunk's transfers overlap an earlier chunk's compute.  Three rows of kMaxChunks + 1
+  // boundaries (tiles, CTA pairs, padded rows): chunk c is [b[c], b[c + 1]); b[0] = 0 and every
+  // boundary from the chunk count on equals the total, so unused chunks are empty.
   int* split;
+  // Optional [experts/world]: unpadded rows of each local expert of this rank (the K-grouped weight
+  // gradients stop their reduction at the last 64-row block that holds a live row).
+  int* live_rows;
 };
+
+constexpr int kMaxChunks = 8;
+constexpr int kSplitStride = kMaxChunks + 1;
+constexpr int kSplitWords = 3 * kSplitStride;
 
 // A [begin, end) range held in device memory (two pointers into PlanTables::split).
 struct DeviceRange {
   const int* begin;
   const int* end;
 };
-enum SplitHalf { kWhole = 0, kFirstHalf = 1, kSecondHalf = 2 };
-inline DeviceRange split_range(const int* split, int what /*0 tiles, 1 pairs, 2 rows*/, int half) {
-  const int* zero = split + 6;
-  const int* mid = split + 2 * what;
-  const int* all = split + 2 * what + 1;
-  return DeviceRange{half == kSecondHalf ? mid : zero, half == kFirstHalf ? mid : all};
+constexpr int kWhole = -1;  // "chunk" argument: all of the owner's work
+inline DeviceRange split_range(const int* split, int what /*0 tiles, 1 pairs, 2 rows*/, int chunk) {
+  const int* b = split + what * kSplitStride;
+  return chunk < 0 ? DeviceRange{b, b + kMaxChunks} : DeviceRange{b + chunk, b + chunk + 1};
 }
+// Host-side image of a split that has one chunk holding everything.
+inline void fill_whole_split(int* words, int tiles, int pairs, int rows) {
+  const int totals[3] = {tiles, pairs, rows};
+  for (int what = 0; what < 3; ++what) {
+    words[what * kSplitStride] = 0;
+    for (int c = 1; c <= kMaxChunks; ++c) words[what * kSplitStride + c] = totals[what];
+  }
+}
+
+// The whole plan of a small call (at most kSmallPlanRoutes routes) in one launch: what route_local,
+// route_global, route_rows and route_primary compute, plus (exchange != 0) the COUNTS and READY flag
+// hand-shakes that surround them at world > 1.
+constexpr int kSmallPlanRoutes = 4096;
+struct SmallPlan {
+  RouteShape shape;
+  const int* routes;
+  const float* gates;         // nullable when no owner words are pushed
+  int tokens;
+  RouteLocal local;
+  RouteRows rows;
+  PlanTables tables;
+  int* local_count;           // [experts]
+  PeerInts count_matrix;      // every rank's count matrix (row `rank` is written); null entries are skipped
+  const int* my_count_matrix; // this rank's matrix [world][experts]
+  PeerInts meta_origin;       // null entries: nothing is pushed to that owner
+  PeerFloats meta_prob;
+  PeerInts meta_primary;
+  int* per_route_primary;     // nullable
+  int want_primary;           // compute the per-owner primary rows
+  int global_part;            // 0: stop after the counts (phase 0 of the stand-alone planner)
+  int exchange;               // world > 1 inside a runtime: signal / wait the COUNTS and READY flags
+  PeerInts flag_counts;       // COUNTS flag group of every rank
+  const int* my_flag_counts;
+  PeerInts flag_ready;        // READY flag group of every rank
+  const int* my_flag_ready;
+  Gen generation;
+  int row_capacity;
+  int* status;
+  int chunks;
+  int split_percent;          // filled by route_plan_small
+  long long wait_budget;      // filled by route_plan_small
+};
+int route_plan_small(SmallPlan plan, cudaStream_t stream);
 
 int route_local(const RouteShape& s, const int* routes, int tokens, RouteLocal out,
                 int* chunk_hist, int* local_count, const PeerInts& count_matrix,
                 cudaStream_t stream);
+// `chunks` (1..kMaxChunks): how many chunks PlanTables::split cuts the owner's rows into.
 int route_global(const RouteShape& s, const int* count_matrix, const int* flag_counts,
-                 Gen generation, int row_capacity, PlanTables t, int* status, cudaStream_t stream);
+                 Gen generation, int row_capacity, PlanTables t, int* status, int chunks,
+                 cudaStream_t stream);
 // `status` (nullable): when the status word is already non-zero (the plan failed) nothing is written.
 // Words for rows at or beyond `row_capacity` are never pushed to an owner.
 int route_rows(const RouteShape& s, const int* routes, const float* gates, int tokens,

@@ -114,7 +114,7 @@ extern "C" int wm_route_plan_noalloc(int32_t phase, int32_t world, int32_t rank,
                  out->padded_start, out->tile_group, out->num_tiles, out->padded_rows,
                  at<int>(tmp, kOffPairs) + 1, at<int>(tmp, kOffPairs)};
     rc = route_global(shape, count_matrix, at<int>(tmp, kOffFlags), Gen{}, row_capacity, t,
-                      at<int>(tmp, kOffStatus), stream);
+                      at<int>(tmp, kOffStatus), 1, stream);
     RouteRows rows{out->local_offset, out->dst_rank, out->dst_row, out->dst_prow};
     PeerInts no_origin{};
     PeerFloats no_prob{};

@@ -34,7 +34,7 @@ enum FlagGroup { kCounts = 0, kReady = 1, kPulled = 2, kContrib = 3, kFlagGroups
 enum Stage {
   kStagePlan = 0, kStageGather, kStageFc1, kStageFc2, kStageCombine,
   kStageGatherDy, kStageDu, kStageSwigluBwd, kStageDx, kStageDw1, kStageDw2, kStageCombineDx,
-  // second halves (world > 1 only; the second half's rows are pulled on the side stream)
+  // later chunks (world > 1 only; chunks after the first are pulled on the side stream)
   kStageFc1B, kStageFc2B, kStageDuB, kStageSwigluBwdB, kStageDxB, kStageGatherB, kStageGatherDyB,
   // waits and staging copies around the kernels (they absorb the skew between ranks)
   kStageStageIn, kStageSyncReady, kStageSyncContrib, kStageStageInBwd, kStageSyncReadyBwd, kStageSyncContribBwd,
@@ -47,10 +47,11 @@ const char* const kStageNames[kStageCount] = {
     "gather_rows_b", "gather_dy_b", "stage_in", "sync_ready", "sync_contrib", "stage_in_bwd", "sync_ready_bwd",
     "sync_contrib_bwd"};
 constexpr int kTimingRing = 32;
+// One event pair per (stage, chunk) and call; created at first use.
 struct TimingSlot {
-  cudaEvent_t start[kStageCount] = {};
-  cudaEvent_t stop[kStageCount] = {};
-  bool used[kStageCount] = {};
+  cudaEvent_t start[kStageCount][kMaxChunks] = {};
+  cudaEvent_t stop[kStageCount][kMaxChunks] = {};
+  bool used[kStageCount][kMaxChunks] = {};
 };
 
 constexpr size_t kAlign = 256;
@@ -76,7 +77,7 @@ struct ScratchLayout {
 };
 // Training cache carved out of the caller's tape buffer.
 struct TapeLayout {
-  size_t sorted_slot, sorted_expert, padded_start, tile_group, num_tiles, padded_rows, pair_tiles,
+  size_t sorted_slot, sorted_expert, padded_start, live_rows, tile_group, num_tiles, padded_rows, pair_tiles,
       num_pairs, split, origin, prob, primary, xrows, ab, total;
 };
 
@@ -95,11 +96,13 @@ struct wm_runtime {
   // world > 1: the second half of the owner's rows is pulled on a side stream while the first
   // half is being computed (inbound NVLink beside compute and outbound pushes).
   cudaStream_t side = nullptr;
-  cudaEvent_t ev_first_pulled = nullptr, ev_second_pulled = nullptr;
+  int chunks = 1;                              // chunks the owner's rows are pipelined in (1 at world 1)
+  cudaEvent_t ev_pulled[kMaxChunks] = {};      // chunk c's rows are in this rank's row buffer
   // Optional (WM_PUSH_SMS = n > 0, world > 1): the first half's push GEMM (FC2 / dX, bound by NVLink)
   // runs on n SMs of a third stream beside the second half's compute-bound kernels on the other SMs.
   cudaStream_t push_stream = nullptr;
-  cudaEvent_t ev_half_ready = nullptr, ev_half_pushed = nullptr;
+  cudaEvent_t ev_ready[kMaxChunks] = {};       // chunk c's push GEMM may start (its input is complete)
+  cudaEvent_t ev_pushed = nullptr;             // the latest push GEMM issued on push_stream has finished
   int push_sms = 0, push_sms_bwd = 0;
   // Optional per-stage device timing (CUDA events on the caller's stream).
   bool timing = false;
@@ -157,7 +160,7 @@ ScratchLayout scratch_layout(const wm_config& c, int row_cap) {
   s.padded_rows = k.take(sizeof(int));
   s.pair_tiles = k.take(sizeof(int) * 2 * (row_cap / 128 + 1));
   s.num_pairs = k.take(sizeof(int));
-  s.split = k.take(sizeof(int) * 8);
+  s.split = k.take(sizeof(int) * kSplitWords);
   s.origin = k.take(sizeof(int) * row_cap);
   s.prob = k.take(sizeof(float) * row_cap);
   s.primary = k.take(sizeof(int) * row_cap);
@@ -207,12 +210,13 @@ TapeLayout tape_layout(const wm_config& c, int row_cap) {
   t.sorted_slot = k.take(sizeof(int) * routes);
   t.sorted_expert = k.take(sizeof(int) * routes);
   t.padded_start = k.take(sizeof(int) * (e_local + 1));
+  t.live_rows = k.take(sizeof(int) * e_local);
   t.tile_group = k.take(sizeof(int) * (row_cap / 128 + 1));
   t.num_tiles = k.take(sizeof(int));
   t.padded_rows = k.take(sizeof(int));
   t.pair_tiles = k.take(sizeof(int) * 2 * (row_cap / 128 + 1));
   t.num_pairs = k.take(sizeof(int));
-  t.split = k.take(sizeof(int) * 8);
+  t.split = k.take(sizeof(int) * kSplitWords);
   t.origin = k.take(sizeof(int) * row_cap);
   t.prob = k.take(sizeof(float) * row_cap);
   t.primary = k.take(sizeof(int) * row_cap);
@@ -290,19 +294,23 @@ void harvest(wm_runtime* rt, TimingSlot& slot) {
   // WM_DEBUG_STEP_TRACE=1: print each stage's start and end relative to the first timed call.
   static const bool trace = std::getenv("WM_DEBUG_STEP_TRACE") != nullptr;
   for (int k = 0; k < kStageCount; ++k) {
-    if (!slot.used[k]) continue;
-    float ms = 0.0f;
-    if (cudaEventSynchronize(slot.stop[k]) == cudaSuccess &&
-        cudaEventElapsedTime(&ms, slot.start[k], slot.stop[k]) == cudaSuccess) {
-      rt->stage_ms[k] += ms;
-      rt->stage_calls[k] += 1;
-      float at = 0.0f;
-      if (trace && rt->ev_trace_origin &&
-          cudaEventElapsedTime(&at, rt->ev_trace_origin, slot.start[k]) == cudaSuccess)
-        fprintf(stderr, "[trace rank %d] %-20s %9.1f %9.1f us\n", rt->cfg.rank, kStageNames[k], at * 1e3,
-                (at + ms) * 1e3);
+    bool any = false;
+    for (int c = 0; c < kMaxChunks; ++c) {
+      if (!slot.used[k][c]) continue;
+      float ms = 0.0f;
+      if (cudaEventSynchronize(slot.stop[k][c]) == cudaSuccess &&
+          cudaEventElapsedTime(&ms, slot.start[k][c], slot.stop[k][c]) == cudaSuccess) {
+        rt->stage_ms[k] += ms;   // a stage that ran once per chunk reports the sum over its chunks
+        any = true;
+        float at = 0.0f;
+        if (trace && rt->ev_trace_origin &&
+            cudaEventElapsedTime(&at, rt->ev_trace_origin, slot.start[k][c]) == cudaSuccess)
+          fprintf(stderr, "[trace rank %d] %-20s c%d %9.1f %9.1f us\n", rt->cfg.rank, kStageNames[k], c, at * 1e3,
+                  (at + ms) * 1e3);
+      }
+      slot.used[k][c] = false;
     }
-    slot.used[k] = false;
+    if (any) rt->stage_calls[k] += 1;
   }
 }
 TimingSlot* begin_timing(wm_runtime* rt, cudaStream_t stream) {
@@ -316,15 +324,21 @@ TimingSlot* begin_timing(wm_runtime* rt, cudaStream_t stream) {
 }
 struct StageScope {
   TimingSlot* slot;
-  int stage;
+  int stage, chunk;
   cudaStream_t stream;
-  StageScope(TimingSlot* s, int k, cudaStream_t st) : slot(s), stage(k), stream(st) {
-    if (slot) cudaEventRecord(slot->start[stage], stream);
+  StageScope(TimingSlot* s, int k, cudaStream_t st, int c = 0) : slot(s), stage(k), chunk(c), stream(st) {
+    if (!slot) return;
+    if (!slot->start[stage][chunk] && (cudaEventCreate(&slot->start[stage][chunk]) != cudaSuccess ||
+                                       cudaEventCreate(&slot->stop[stage][chunk]) != cudaSuccess)) {
+      slot = nullptr;
+      return;
+    }
+    cudaEventRecord(slot->start[stage][chunk], stream);
   }
   ~StageScope() {
     if (slot) {
-      cudaEventRecord(slot->stop[stage], stream);
-      slot->used[stage] = true;
+      cudaEventRecord(slot->stop[stage][chunk], stream);
+      slot->used[stage][chunk] = true;
     }
   }
 };
@@ -385,11 +399,19 @@ extern "C" int wm_runtime_create(const wm_config* config, wm_runtime** out) {
   }
   if (rt->cfg.world > 1) {
     e = cudaStreamCreateWithFlags(&rt->side, cudaStreamNonBlocking);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&rt->ev_first_pulled, cudaEventDisableTiming);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&rt->ev_second_pulled, cudaEventDisableTiming);
+    for (int c = 0; c < kMaxChunks && e == cudaSuccess; ++c) {
+      e = cudaEventCreateWithFlags(&rt->ev_pulled[c], cudaEventDisableTiming);
+      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&rt->ev_ready[c], cudaEventDisableTiming);
+    }
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&rt->push_stream, cudaStreamNonBlocking);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&rt->ev_half_ready, cudaEventDisableTiming);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&rt->ev_half_pushed, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&rt->ev_pushed, cudaEventDisableTiming);
+    // Chunks of the owner's rows: only the first chunk's pull is exposed, every later pull runs on the side
+    // stream beside the GEMMs of the chunks before it (WM_CHUNKS = 2..8).
+    rt->chunks = config->world == 8 ? 4 : 2;
+    if (const char* v = std::getenv("WM_CHUNKS")) {
+      const int n = std::atoi(v);
+      if (n >= 2 && n <= kMaxChunks) rt->chunks = n;
+    }
     // Measured on 8 x B200 (35B-A3B-like shape, skewed routing): 72 SMs for the pushes gives
     // 2.98 ms per step against 3.08 ms without the overlap; 48 SMs gives 3.06 ms.  Off below 8 ranks.
     rt->push_sms = rt->push_sms_bwd = config->world == 8 ? 72 : 0;
@@ -479,11 +501,18 @@ extern "C" int wm_runtime_destroy(wm_runtime* rt) {
   if (!rt) return WM_OK;
   wm_runtime_retire_peers(rt);
   if (rt->side) cudaStreamDestroy(rt->side);
-  if (rt->ev_first_pulled) cudaEventDestroy(rt->ev_first_pulled);
-  if (rt->ev_second_pulled) cudaEventDestroy(rt->ev_second_pulled);
+  for (int c = 0; c < kMaxChunks; ++c) {
+    if (rt->ev_pulled[c]) cudaEventDestroy(rt->ev_pulled[c]);
+    if (rt->ev_ready[c]) cudaEventDestroy(rt->ev_ready[c]);
+  }
   if (rt->push_stream) cudaStreamDestroy(rt->push_stream);
-  if (rt->ev_half_ready) cudaEventDestroy(rt->ev_half_ready);
-  if (rt->ev_half_pushed) cudaEventDestroy(rt->ev_half_pushed);
+  if (rt->ev_pushed) cudaEventDestroy(rt->ev_pushed);
+  for (auto& slot : rt->slots)
+    for (int k = 0; k < kStageCount; ++k)
+      for (int c = 0; c < kMaxChunks; ++c) {
+        if (slot.start[k][c]) cudaEventDestroy(slot.start[k][c]);
+        if (slot.stop[k][c]) cudaEventDestroy(slot.stop[k][c]);
+      }
   if (rt->ev_trace_origin) cudaEventDestroy(rt->ev_trace_origin);
   if (rt->arena) cudaFree(rt->arena);
   if (rt->scratch) cudaFree(rt->scratch);
@@ -523,6 +552,24 @@ static Gen begin_generation(wm_runtime* rt, cudaStream_t stream) {
 }
 
 // =============================================================================== forward
+// Calls of at most kSmallPlanRoutes routes plan in one launch (WM_SMALL_PLAN=0 keeps the general kernels).
+static bool small_plan_allowed(long long routes) {
+  static const bool on = [] {
+    const char* v = std::getenv("WM_SMALL_PLAN");
+    return !(v && v[0] == '0');
+  }();
+  return on && routes <= kSmallPlanRoutes;
+}
+
+// WM_PAIR_FWD=1 lets FC1 / FC2 take the CTA-pair kernel where experts average >= 1024 rows.
+static bool pairs_in_forward() {
+  static const bool on = [] {
+    const char* v = std::getenv("WM_PAIR_FWD");
+    return v && v[0] == '1';
+  }();
+  return on;
+}
+
 extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, const float* gates,
                           const void* w1, const void* w2, int32_t tokens, void* y, void* tape,
                           void* stream_) {
@@ -565,6 +612,7 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
   tables.pair_tiles = tape ? at<int>(T, rt->tl.pair_tiles) : at<int>(S, rt->sl.pair_tiles);
   tables.num_pairs = tape ? at<int>(T, rt->tl.num_pairs) : at<int>(S, rt->sl.num_pairs);
   tables.split = tape ? at<int>(T, rt->tl.split) : at<int>(S, rt->sl.split);
+  tables.live_rows = tape ? at<int>(T, rt->tl.live_rows) : nullptr;
   int* origin = tape ? at<int>(T, rt->tl.origin) : at<int>(S, rt->sl.origin);
   float* prob = tape ? at<float>(T, rt->tl.prob) : at<float>(S, rt->sl.prob);
   // world > 1: row a duplicate of a token is copied from (the token crosses NVLink once per owner).
@@ -590,6 +638,8 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
   push.cap = c.max_tokens;
   push.top_k = c.top_k;
 
+  // Rows per local expert if routing were uniform: tokens * K * world / E (kernel choice only).
+  const bool many_rows = pairs_in_forward() && 1ll * tokens * c.top_k * world >= 1024ll * c.experts;
   // 1. staging buffer free?  then stage x and plan locally; counts go to every rank.
   TimingSlot* timing = begin_timing(rt, stream);
   if (world == 1) {
@@ -603,102 +653,134 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
   }
   // 1b/2. local plan, count exchange, global plan (waits for all count rows), destination rows,
   //       origin/prob words to the owners.  At world > 1 the stage time includes the wait.
-  {
+  RouteRows rows{at<int>(S, rt->sl.local_offset), at<int>(S, rt->sl.dst_rank), at<int>(S, rt->sl.dst_row),
+                 at<int>(S, rt->sl.dst_prow)};
+  if (small_plan_allowed(1ll * tokens * c.top_k)) {
+    // decode and small prefill: everything above plus the COUNTS / READY hand-shakes in one launch
     StageScope scope(timing, kStagePlan, stream);
-    if (int rc = route_local(shape, routes, tokens, local, at<int>(S, rt->sl.chunk_hist),
-                             at<int>(S, rt->sl.local_count), counts, stream))
-      return rc;
-    if (world > 1)
-      if (int rc = signal_peers(flag_group(rt, kCounts), world, c.rank, gen, stream)) return rc;
-    if (int rc = route_global(shape, at<int>(rt->arena, rt->al.counts), my_flags(rt, kCounts),
-                              world > 1 ? gen : Gen{}, rt->row_cap, tables, status, stream))
-      return rc;
-    RouteRows rows{at<int>(S, rt->sl.local_offset), at<int>(S, rt->sl.dst_rank),
-                   at<int>(S, rt->sl.dst_row), at<int>(S, rt->sl.dst_prow)};
-    if (int rc = route_rows(shape, routes, gates, tokens, local, at<int>(S, rt->sl.chunk_hist),
-                            tables, rows, meta_origin, meta_prob, rt->row_cap, status, stream))
-      return rc;
-    if (world > 1)
-      if (int rc = route_primary(shape, tokens, local, rows, meta_primary, nullptr, rt->row_cap, status, stream))
+    SmallPlan plan{};
+    plan.shape = shape;
+    plan.routes = routes;
+    plan.gates = gates;
+    plan.tokens = tokens;
+    plan.local = local;
+    plan.rows = rows;
+    plan.tables = tables;
+    plan.local_count = at<int>(S, rt->sl.local_count);
+    plan.count_matrix = counts;
+    plan.my_count_matrix = at<int>(rt->arena, rt->al.counts);
+    plan.meta_origin = meta_origin;
+    plan.meta_prob = meta_prob;
+    plan.meta_primary = meta_primary;
+    plan.want_primary = world > 1;
+    plan.global_part = 1;
+    plan.exchange = world > 1;
+    plan.flag_counts = flag_group(rt, kCounts);
+    plan.my_flag_counts = my_flags(rt, kCounts);
+    plan.flag_ready = flag_group(rt, kReady);
+    plan.my_flag_ready = my_flags(rt, kReady);
+    plan.generation = world > 1 ? gen : Gen{};
+    plan.row_capacity = rt->row_cap;
+    plan.status = status;
+    plan.chunks = rt->chunks;
+    if (int rc = route_plan_small(plan, stream)) return rc;
+  } else {
+    {
+      StageScope scope(timing, kStagePlan, stream);
+      if (int rc = route_local(shape, routes, tokens, local, at<int>(S, rt->sl.chunk_hist),
+                               at<int>(S, rt->sl.local_count), counts, stream))
         return rc;
-  }
-  if (world > 1) {
-    StageScope scope(timing, kStageSyncReady, stream);
-    if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
-    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, tables.split, stream)) return rc;
+      if (world > 1)
+        if (int rc = signal_peers(flag_group(rt, kCounts), world, c.rank, gen, stream)) return rc;
+      if (int rc = route_global(shape, at<int>(rt->arena, rt->al.counts), my_flags(rt, kCounts),
+                                world > 1 ? gen : Gen{}, rt->row_cap, tables, status, rt->chunks, stream))
+        return rc;
+      if (int rc = route_rows(shape, routes, gates, tokens, local, at<int>(S, rt->sl.chunk_hist),
+                              tables, rows, meta_origin, meta_prob, rt->row_cap, status, stream))
+        return rc;
+      if (world > 1)
+        if (int rc = route_primary(shape, tokens, local, rows, meta_primary, nullptr, rt->row_cap, status, stream))
+          return rc;
+    }
+    if (world > 1) {
+      StageScope scope(timing, kStageSyncReady, stream);
+      if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
+      if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, tables.split, stream)) return rc;
+    }
   }
   // 3. owner side: pull rows, then the two grouped GEMMs; FC2 pushes into the sources' mailboxes.
-  //    world > 1: the rows are split at an expert boundary; the second half is pulled on the side
-  //    stream while FC1/FC2 of the first half run (inbound NVLink beside compute and pushes).
-  const bool halves = world > 1;
-  auto owner_rows = [&](int half) {
-    return OwnerRows{tables.padded_start, tables.tile_group, split_range(tables.split, 2, half),
+  //    world > 1: the rows are cut at expert boundaries into rt->chunks chunks.  Chunk 0 is pulled on
+  //    this stream with every SM; the later chunks are pulled on the side stream while FC1 / FC2 of the
+  //    chunks before them run (inbound NVLink beside compute and pushes), so only the first pull is
+  //    exposed.
+  const int chunks = world > 1 ? rt->chunks : 1;
+  auto owner_rows = [&](int chunk) {
+    return OwnerRows{tables.padded_start, tables.tile_group, split_range(tables.split, 2, chunk),
                      tables.expert_total};
   };
-  auto pull = [&](int half, cudaStream_t st) -> int {
+  auto pull = [&](int chunk, cudaStream_t st) -> int {
     const int ctas = st == rt->side ? rt->sms * 2 : rt->sms * 8;  // the side stream copies beside a GEMM
-    if (int rc = gather_rows(owner_rows(half), c.rank, rt->e_local, world, rt->row_cap, c.max_tokens, c.top_k,
+    if (int rc = gather_rows(owner_rows(chunk), c.rank, rt->e_local, world, rt->row_cap, c.max_tokens, c.top_k,
                              c.hidden, stage,
                              at<int>(rt->arena, rt->al.meta_origin), at<float>(rt->arena, rt->al.meta_prob),
                              primary ? at<int>(rt->arena, rt->al.meta_primary) : nullptr, xrows, origin,
                              prob, primary, ctas, st))
       return rc;
-    return primary ? copy_duplicate_rows(split_range(tables.split, 2, half), primary, c.hidden, xrows, ctas, st)
+    return primary ? copy_duplicate_rows(split_range(tables.split, 2, chunk), primary, c.hidden, xrows, ctas, st)
                    : 0;
   };
-  auto schedule_of = [&](int half) {
+  auto schedule_of = [&](int chunk) {
     return Schedule{tables.split, tables.tile_group, tables.padded_start, rt->e_local, rt->row_cap,
-                    tables.pair_tiles, false, half};
+                    tables.pair_tiles, many_rows, chunk};
   };
-  auto fc1 = [&](int half, int stage_id, int sms) -> int {
-    StageScope scope(timing, stage_id, stream);
-    return launch_fc1(schedule_of(half), xrows, static_cast<const __nv_bfloat16*>(w1), u, ab, prob, c.hidden,
+  auto fc1 = [&](int chunk, int sms) -> int {
+    StageScope scope(timing, chunk <= 0 ? kStageFc1 : kStageFc1B, stream, chunk < 0 ? 0 : chunk);
+    return launch_fc1(schedule_of(chunk), xrows, static_cast<const __nv_bfloat16*>(w1), u, ab, prob, c.hidden,
                       c.intermediate, status, sms, stream);
   };
-  auto fc2 = [&](int half, int stage_id, int sms, cudaStream_t st) -> int {
-    StageScope scope(timing, stage_id, st);
-    return launch_mgrouped_nt(schedule_of(half), u, static_cast<const __nv_bfloat16*>(w2), nullptr, &push,
+  auto fc2 = [&](int chunk, int sms, cudaStream_t st) -> int {
+    StageScope scope(timing, chunk <= 0 ? kStageFc2 : kStageFc2B, st, chunk < 0 ? 0 : chunk);
+    return launch_mgrouped_nt(schedule_of(chunk), u, static_cast<const __nv_bfloat16*>(w2), nullptr, &push,
                               c.hidden, c.intermediate, status, sms, st);
   };
-  auto compute = [&](int half, int stage_fc1, int stage_fc2) -> int {
-    if (int rc = fc1(half, stage_fc1, rt->sms)) return rc;
-    return fc2(half, stage_fc2, rt->sms, stream);
-  };
-  if (!halves) {
+  if (chunks == 1) {
     {
       StageScope scope(timing, kStageGather, stream);
       if (int rc = pull(kWhole, stream)) return rc;
     }
-    if (int rc = compute(kWhole, kStageFc1, kStageFc2)) return rc;
+    if (int rc = fc1(kWhole, rt->sms)) return rc;
+    if (int rc = fc2(kWhole, rt->sms, stream)) return rc;
   } else {
     {
       StageScope scope(timing, kStageGather, stream);
-      if (int rc = pull(kFirstHalf, stream)) return rc;
+      if (int rc = pull(0, stream)) return rc;
     }
-    WM_CUDA(cudaEventRecord(rt->ev_first_pulled, stream));
-    WM_CUDA(cudaStreamWaitEvent(rt->side, rt->ev_first_pulled, 0));
-    {
-      StageScope scope(timing, kStageGatherB, rt->side);
-      if (int rc = pull(kSecondHalf, rt->side)) return rc;
+    WM_CUDA(cudaEventRecord(rt->ev_pulled[0], stream));
+    WM_CUDA(cudaStreamWaitEvent(rt->side, rt->ev_pulled[0], 0));
+    for (int k = 1; k < chunks; ++k) {
+      {
+        StageScope scope(timing, kStageGatherB, rt->side, k);
+        if (int rc = pull(k, rt->side)) return rc;
+      }
+      WM_CUDA(cudaEventRecord(rt->ev_pulled[k], rt->side));
     }
-    WM_CUDA(cudaEventRecord(rt->ev_second_pulled, rt->side));
-    if (rt->push_sms == 0) {
-      if (int rc = compute(kFirstHalf, kStageFc1, kStageFc2)) return rc;
-      WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_second_pulled, 0));
-      if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
-      if (int rc = compute(kSecondHalf, kStageFc1B, kStageFc2B)) return rc;
-    } else {
-      // FC2 of the first half pushes over NVLink from a few SMs while FC1 of the second half computes.
-      if (int rc = fc1(kFirstHalf, kStageFc1, rt->sms)) return rc;
-      WM_CUDA(cudaEventRecord(rt->ev_half_ready, stream));
-      WM_CUDA(cudaStreamWaitEvent(rt->push_stream, rt->ev_half_ready, 0));
-      if (int rc = fc2(kFirstHalf, kStageFc2, rt->push_sms, rt->push_stream)) return rc;
-      WM_CUDA(cudaEventRecord(rt->ev_half_pushed, rt->push_stream));
-      WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_second_pulled, 0));
-      if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
-      if (int rc = fc1(kSecondHalf, kStageFc1B, rt->sms - rt->push_sms)) return rc;
-      WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_half_pushed, 0));
-      if (int rc = fc2(kSecondHalf, kStageFc2B, rt->sms, stream)) return rc;
+    // With push_sms > 0, FC2 of chunk k (bound by its NVLink pushes) runs on push_sms SMs of a third
+    // stream beside FC1 of chunk k + 1 on the other SMs; the last chunk's FC2 gets every SM again.
+    const bool beside = rt->push_sms > 0;
+    for (int k = 0; k < chunks; ++k) {
+      if (k > 0) WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_pulled[k], 0));
+      if (k == chunks - 1)  // every row of this call has been read from the sources' staging buffers
+        if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
+      if (int rc = fc1(k, beside && k > 0 ? rt->sms - rt->push_sms : rt->sms)) return rc;
+      if (beside && k < chunks - 1) {
+        WM_CUDA(cudaEventRecord(rt->ev_ready[k], stream));
+        WM_CUDA(cudaStreamWaitEvent(rt->push_stream, rt->ev_ready[k], 0));
+        if (int rc = fc2(k, rt->push_sms, rt->push_stream)) return rc;
+        WM_CUDA(cudaEventRecord(rt->ev_pushed, rt->push_stream));
+      } else {
+        if (beside) WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_pushed, 0));
+        if (int rc = fc2(k, rt->sms, stream)) return rc;
+      }
     }
   }
   if (world > 1) {
@@ -789,17 +871,17 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
   // Rows per local expert if routing were uniform: tokens * K * world / E.
   const bool many_rows = 1ll * tokens * c.top_k * world >= 1024ll * c.experts;
   const int* split = reinterpret_cast<const int*>(tp(rt->tl.split));
-  const bool halves = world > 1;
+  const int chunks = world > 1 ? rt->chunks : 1;
   const int* primary = world == 1 ? nullptr : reinterpret_cast<const int*>(tp(rt->tl.primary));
-  auto pull = [&](int half, cudaStream_t st) -> int {
+  auto pull = [&](int chunk, cudaStream_t st) -> int {
     const int ctas = st == rt->side ? rt->sms * 2 : rt->sms * 8;  // the side stream copies beside a GEMM
-    if (int rc = gather_by_origin(split_range(split, 2, half), origin, primary, world, c.max_tokens, c.top_k,
+    if (int rc = gather_by_origin(split_range(split, 2, chunk), origin, primary, world, c.max_tokens, c.top_k,
                                   c.hidden, stage, recv, ctas, st))
       return rc;
-    return primary ? copy_duplicate_rows(split_range(split, 2, half), primary, c.hidden, recv, ctas, st) : 0;
+    return primary ? copy_duplicate_rows(split_range(split, 2, chunk), primary, c.hidden, recv, ctas, st) : 0;
   };
-  auto schedule = [&](int half) {
-    return Schedule{split, tile_group, padded_start, rt->e_local, rt->row_cap, pair_tiles, many_rows, half};
+  auto schedule = [&](int chunk) {
+    return Schedule{split, tile_group, padded_start, rt->e_local, rt->row_cap, pair_tiles, many_rows, chunk};
   };
   // dU with the SwiGLU backward in its epilogue (no dU buffer, no separate elementwise pass) where the
   // one-CTA kernel runs dU and I is a multiple of 256; WM_FUSED_DU=0 keeps the two-kernel form.
@@ -808,78 +890,80 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
     return !(v && v[0] == '0');
   }();
   auto* dprob_part = at<float>(S, rt->sl.dprob_part);
-  auto du_and_swiglu = [&](int half, int stage_du, int stage_sw, int sms) -> int {
+  auto du_and_swiglu = [&](int chunk, int sms) -> int {
+    const int slot = chunk < 0 ? 0 : chunk;
+    const int stage_du = chunk <= 0 ? kStageDu : kStageDuB, stage_sw = chunk <= 0 ? kStageSwigluBwd : kStageSwigluBwdB;
     if (fused_allowed) {
       int rc;
       {
-        StageScope scope(timing, stage_du, stream);
-        rc = launch_du_swiglu_backward(schedule(half), recv, static_cast<const __nv_bfloat16*>(w2), ab, prob, u,
+        StageScope scope(timing, stage_du, stream, slot);
+        rc = launch_du_swiglu_backward(schedule(chunk), recv, static_cast<const __nv_bfloat16*>(w2), ab, prob, u,
                                        dab, dprob_part, c.intermediate, c.hidden, status, sms, stream);
       }
       if (rc > 0) return rc;
       if (rc == 0) {
-        StageScope scope(timing, stage_sw, stream);
-        return dprob_finish(split_range(split, 2, half), dprob_part, c.intermediate / 128, rt->row_cap, origin,
+        StageScope scope(timing, stage_sw, stream, slot);
+        return dprob_finish(split_range(split, 2, chunk), dprob_part, c.intermediate / 128, rt->row_cap, origin,
                             c.max_tokens, c.top_k, dgate_box, stream);
       }
     }
     {
-      StageScope scope(timing, stage_du, stream);
-      if (int rc = launch_mgrouped_nn(schedule(half), recv, static_cast<const __nv_bfloat16*>(w2), du, nullptr,
+      StageScope scope(timing, stage_du, stream, slot);
+      if (int rc = launch_mgrouped_nn(schedule(chunk), recv, static_cast<const __nv_bfloat16*>(w2), du, nullptr,
                                       c.intermediate, c.hidden, status, sms, stream))
         return rc;
     }
-    StageScope scope(timing, stage_sw, stream);
-    return swiglu_backward(split_range(split, 2, half), ab, du, prob, origin, c.intermediate, c.max_tokens,
+    StageScope scope(timing, stage_sw, stream, slot);
+    return swiglu_backward(split_range(split, 2, chunk), ab, du, prob, origin, c.intermediate, c.max_tokens,
                            c.top_k, u, dab, dgate_box, rt->sms, stream);
   };
-  auto dx_push = [&](int half, int stage_dx, int sms, cudaStream_t st) -> int {
-    StageScope scope(timing, stage_dx, st);
-    return launch_mgrouped_nn(schedule(half), dab, static_cast<const __nv_bfloat16*>(w1), nullptr, &push,
+  auto dx_push = [&](int chunk, int sms, cudaStream_t st) -> int {
+    StageScope scope(timing, chunk <= 0 ? kStageDx : kStageDxB, st, chunk < 0 ? 0 : chunk);
+    return launch_mgrouped_nn(schedule(chunk), dab, static_cast<const __nv_bfloat16*>(w1), nullptr, &push,
                               c.hidden, 2 * c.intermediate, status, sms, st);
   };
-  auto compute = [&](int half, int stage_du, int stage_sw, int stage_dx) -> int {
-    if (int rc = du_and_swiglu(half, stage_du, stage_sw, rt->sms)) return rc;
-    return dx_push(half, stage_dx, rt->sms, stream);
-  };
-  if (!halves) {
+  if (chunks == 1) {
     {
       StageScope scope(timing, kStageGatherDy, stream);
       if (int rc = pull(kWhole, stream)) return rc;
     }
-    if (int rc = compute(kWhole, kStageDu, kStageSwigluBwd, kStageDx)) return rc;
+    if (int rc = du_and_swiglu(kWhole, rt->sms)) return rc;
+    if (int rc = dx_push(kWhole, rt->sms, stream)) return rc;
   } else {
     {
       StageScope scope(timing, kStageGatherDy, stream);
-      if (int rc = pull(kFirstHalf, stream)) return rc;
+      if (int rc = pull(0, stream)) return rc;
     }
-    WM_CUDA(cudaEventRecord(rt->ev_first_pulled, stream));
-    WM_CUDA(cudaStreamWaitEvent(rt->side, rt->ev_first_pulled, 0));
-    {
-      StageScope scope(timing, kStageGatherDyB, rt->side);
-      if (int rc = pull(kSecondHalf, rt->side)) return rc;
+    WM_CUDA(cudaEventRecord(rt->ev_pulled[0], stream));
+    WM_CUDA(cudaStreamWaitEvent(rt->side, rt->ev_pulled[0], 0));
+    for (int k = 1; k < chunks; ++k) {
+      {
+        StageScope scope(timing, kStageGatherDyB, rt->side, k);
+        if (int rc = pull(k, rt->side)) return rc;
+      }
+      WM_CUDA(cudaEventRecord(rt->ev_pulled[k], rt->side));
     }
-    WM_CUDA(cudaEventRecord(rt->ev_second_pulled, rt->side));
-    if (rt->push_sms_bwd == 0) {
-      if (int rc = compute(kFirstHalf, kStageDu, kStageSwigluBwd, kStageDx)) return rc;
-      WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_second_pulled, 0));
-      if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
-      if (int rc = compute(kSecondHalf, kStageDuB, kStageSwigluBwdB, kStageDxB)) return rc;
-    } else {
-      // dX of the first half pushes from a few SMs while dU and SwiGLU of the second half compute.
-      if (int rc = du_and_swiglu(kFirstHalf, kStageDu, kStageSwigluBwd, rt->sms)) return rc;
-      WM_CUDA(cudaEventRecord(rt->ev_half_ready, stream));
-      WM_CUDA(cudaStreamWaitEvent(rt->push_stream, rt->ev_half_ready, 0));
-      if (int rc = dx_push(kFirstHalf, kStageDx, rt->push_sms_bwd, rt->push_stream)) return rc;
-      WM_CUDA(cudaEventRecord(rt->ev_half_pushed, rt->push_stream));
-      WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_second_pulled, 0));
-      if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
-      if (int rc = du_and_swiglu(kSecondHalf, kStageDuB, kStageSwigluBwdB, rt->sms - rt->push_sms_bwd)) return rc;
-      WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_half_pushed, 0));
-      if (int rc = dx_push(kSecondHalf, kStageDxB, rt->sms, stream)) return rc;
+    // With push_sms_bwd > 0, dX of chunk k pushes from a few SMs on a third stream while dU and the SwiGLU
+    // backward of chunk k + 1 compute on the others.
+    const bool beside = rt->push_sms_bwd > 0;
+    for (int k = 0; k < chunks; ++k) {
+      if (k > 0) WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_pulled[k], 0));
+      if (k == chunks - 1)
+        if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
+      if (int rc = du_and_swiglu(k, beside && k > 0 ? rt->sms - rt->push_sms_bwd : rt->sms)) return rc;
+      if (beside && k < chunks - 1) {
+        WM_CUDA(cudaEventRecord(rt->ev_ready[k], stream));
+        WM_CUDA(cudaStreamWaitEvent(rt->push_stream, rt->ev_ready[k], 0));
+        if (int rc = dx_push(k, rt->push_sms_bwd, rt->push_stream)) return rc;
+        WM_CUDA(cudaEventRecord(rt->ev_pushed, rt->push_stream));
+      } else {
+        if (beside) WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_pushed, 0));
+        if (int rc = dx_push(k, rt->sms, stream)) return rc;
+      }
     }
   }
-  const Schedule sched = schedule(kWhole);
+  Schedule sched = schedule(kWhole);
+  sched.group_live_rows = reinterpret_cast<const int*>(tp(rt->tl.live_rows));
   if (world > 1)
     if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
   // 4. weight gradients: reductions over each expert's rows in the saved (fixed) order.
@@ -1006,22 +1090,49 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
     }
   }
   // 2. route plan (as wm_forward).
-  if (int rc = route_local(shape, routes, tokens, local, at<int>(S, rt->sl.chunk_hist),
-                           at<int>(S, rt->sl.local_count), counts, stream))
-    return rc;
-  if (world > 1)
-    if (int rc = signal_peers(flag_group(rt, kCounts), world, c.rank, gen, stream)) return rc;
-  if (int rc = route_global(shape, at<int>(rt->arena, rt->al.counts), my_flags(rt, kCounts),
-                            world > 1 ? gen : Gen{}, rt->row_cap, tables, status, stream))
-    return rc;
   RouteRows rows{at<int>(S, rt->sl.local_offset), at<int>(S, rt->sl.dst_rank), at<int>(S, rt->sl.dst_row),
                  at<int>(S, rt->sl.dst_prow)};
-  if (int rc = route_rows(shape, routes, gates, tokens, local, at<int>(S, rt->sl.chunk_hist), tables, rows,
-                          meta_origin, meta_prob, rt->row_cap, status, stream))
-    return rc;
-  if (world > 1) {
-    if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
-    if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, tables.split, stream)) return rc;
+  if (small_plan_allowed(1ll * tokens * c.top_k)) {
+    SmallPlan plan{};
+    plan.shape = shape;
+    plan.routes = routes;
+    plan.gates = gates;
+    plan.tokens = tokens;
+    plan.local = local;
+    plan.rows = rows;
+    plan.tables = tables;
+    plan.local_count = at<int>(S, rt->sl.local_count);
+    plan.count_matrix = counts;
+    plan.my_count_matrix = at<int>(rt->arena, rt->al.counts);
+    plan.meta_origin = meta_origin;
+    plan.meta_prob = meta_prob;
+    plan.global_part = 1;
+    plan.exchange = world > 1;
+    plan.flag_counts = flag_group(rt, kCounts);
+    plan.my_flag_counts = my_flags(rt, kCounts);
+    plan.flag_ready = flag_group(rt, kReady);
+    plan.my_flag_ready = my_flags(rt, kReady);
+    plan.generation = world > 1 ? gen : Gen{};
+    plan.row_capacity = rt->row_cap;
+    plan.status = status;
+    plan.chunks = 1;
+    if (int rc = route_plan_small(plan, stream)) return rc;
+  } else {
+    if (int rc = route_local(shape, routes, tokens, local, at<int>(S, rt->sl.chunk_hist),
+                             at<int>(S, rt->sl.local_count), counts, stream))
+      return rc;
+    if (world > 1)
+      if (int rc = signal_peers(flag_group(rt, kCounts), world, c.rank, gen, stream)) return rc;
+    if (int rc = route_global(shape, at<int>(rt->arena, rt->al.counts), my_flags(rt, kCounts),
+                              world > 1 ? gen : Gen{}, rt->row_cap, tables, status, 1, stream))
+      return rc;
+    if (int rc = route_rows(shape, routes, gates, tokens, local, at<int>(S, rt->sl.chunk_hist), tables, rows,
+                            meta_origin, meta_prob, rt->row_cap, status, stream))
+      return rc;
+    if (world > 1) {
+      if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
+      if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, tables.split, stream)) return rc;
+    }
   }
   // 3. owner side: pull quantised rows + scale factors, FC1, SwiGLU + re-quantisation, FC2 -> mailboxes.
   OwnerRows owner{tables.padded_start, tables.tile_group, split_range(tables.split, 2, kWhole),
@@ -1416,27 +1527,49 @@ extern "C" int wm_route_plan(int32_t phase, int32_t world, int32_t rank, int32_t
     RouteLocal local{out->sorted_slot, out->sorted_expert, at<int>(tmp, o_pos)};
     PeerInts counts{};
     for (int r = 0; r < world; ++r) counts.p[r] = count_matrix;  // every "rank" shares one matrix
-    if (int rc = route_local(shape, routes, tokens, local, at<int>(tmp, o_hist), at<int>(tmp, o_cnt), counts,
-                             stream))
-      return rc;
-    if (phase != 1) return 0;
     PlanTables t{out->expert_total, at<int>(tmp, o_before), out->expert_base, out->expert_pbase,
                  out->padded_start, out->tile_group, out->num_tiles, out->padded_rows,
                  at<int>(tmp, o_pairs) + 1, at<int>(tmp, o_pairs)};
-    // No exchange to wait for: generation 0 is satisfied by the zeroed flag words.
-    if (int rc = route_global(shape, count_matrix, at<int>(tmp, o_flags), Gen{}, row_capacity, t,
-                              at<int>(tmp, o_status), stream))
-      return rc;
     RouteRows rows{out->local_offset, out->dst_rank, out->dst_row, out->dst_prow};
-    PeerInts no_origin{};
-    PeerFloats no_prob{};
-    if (int rc = route_rows(shape, routes, nullptr, tokens, local, at<int>(tmp, o_hist), t, rows, no_origin,
-                            no_prob, row_capacity, at<int>(tmp, o_status), stream))
-      return rc;
-    if (out->dst_primary)
-      if (int rc = route_primary(shape, tokens, local, rows, no_origin, out->dst_primary, row_capacity,
-                                 at<int>(tmp, o_status), stream))
+    if (small_plan_allowed(static_cast<long long>(n))) {
+      // the single-launch planner of small calls, so that the tests of this entry cover it too
+      SmallPlan plan{};
+      plan.shape = shape;
+      plan.routes = routes;
+      plan.tokens = tokens;
+      plan.local = local;
+      plan.rows = rows;
+      plan.tables = t;
+      plan.local_count = at<int>(tmp, o_cnt);
+      plan.count_matrix = counts;
+      plan.my_count_matrix = count_matrix;
+      plan.per_route_primary = out->dst_primary;
+      plan.want_primary = out->dst_primary != nullptr;
+      plan.global_part = phase == 1;
+      plan.row_capacity = row_capacity;
+      plan.status = at<int>(tmp, o_status);
+      plan.chunks = 1;
+      if (int rc = route_plan_small(plan, stream)) return rc;
+      if (phase != 1) return 0;
+    } else {
+      if (int rc = route_local(shape, routes, tokens, local, at<int>(tmp, o_hist), at<int>(tmp, o_cnt), counts,
+                               stream))
         return rc;
+      if (phase != 1) return 0;
+      // No exchange to wait for: generation 0 is satisfied by the zeroed flag words.
+      if (int rc = route_global(shape, count_matrix, at<int>(tmp, o_flags), Gen{}, row_capacity, t,
+                                at<int>(tmp, o_status), 1, stream))
+        return rc;
+      PeerInts no_origin{};
+      PeerFloats no_prob{};
+      if (int rc = route_rows(shape, routes, nullptr, tokens, local, at<int>(tmp, o_hist), t, rows, no_origin,
+                              no_prob, row_capacity, at<int>(tmp, o_status), stream))
+        return rc;
+      if (out->dst_primary)
+        if (int rc = route_primary(shape, tokens, local, rows, no_origin, out->dst_primary, row_capacity,
+                                   at<int>(tmp, o_status), stream))
+          return rc;
+    }
     WM_CUDA(cudaMemcpyAsync(&device_code, tmp + o_status, sizeof(int), cudaMemcpyDeviceToHost, stream));
     return 0;
   };
@@ -1481,14 +1614,7 @@ extern "C" const char* wm_stage_name(int stage) {
 
 extern "C" int wm_runtime_enable_timing(wm_runtime* rt, int enable) {
   if (int rc = check_ready(rt, "wm_runtime_enable_timing")) return rc;
-  if (enable && rt->slots.empty()) {
-    rt->slots.resize(kTimingRing);
-    for (auto& slot : rt->slots)
-      for (int k = 0; k < kStageCount; ++k) {
-        WM_CUDA(cudaEventCreate(&slot.start[k]));
-        WM_CUDA(cudaEventCreate(&slot.stop[k]));
-      }
-  }
+  if (enable && rt->slots.empty()) rt->slots.resize(kTimingRing);  // events are created at first use
   rt->timing = enable != 0;
   return WM_OK;
 }
