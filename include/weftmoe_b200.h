@@ -115,6 +115,12 @@ typedef struct wm_quant_weights {
   const void* w2_sf;
   float x_scale, w1_scale, u_scale, w2_scale; /* NVFP4 layer scales; ignored for FP8 */
   float dy_scale, dab_scale;                   /* NVFP4 backward only: layer scales of dY and d(gate,up) */
+  /* Blockwise FP8 only, optional (NULL = quantise the BF16 source online): the source rows already
+   * quantised 1 x 128 by wm_fp8_quantize (E4M3 bytes [tokens][H] and FP32 scales [tokens][H/128]); x in
+   * wm_forward_quantized, dY in wm_backward_quantized.  The BF16 pointer is then ignored and the result has
+   * the bits of the online path (reference: FP8Tensor sources, tests/torchrun_fp8.py:133-157). */
+  const void* source_q;
+  const float* source_scales;
 } wm_quant_weights;
 WM_API int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t* routes, const float* gates,
                                 const wm_quant_weights* weights, int32_t tokens, void* y, void* tape,
@@ -248,6 +254,21 @@ WM_API int wm_route_plan_noalloc(int32_t phase, int32_t world, int32_t rank, int
                                  int32_t top_k, int32_t tokens, int32_t cap, int32_t row_capacity,
                                  const int32_t* routes, int32_t* count_matrix, const wm_route_out* out,
                                  void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Serving-adapter helpers (reference: the SGLang staging kernels sanitize_routes / stage_inputs /
+ * scatter_output, weftmoe/_sglang_kernels.py:21-99).  Every rank holds the same [tokens][hidden] BF16
+ * activations and [tokens][top_k] ids / FP32 weights; rank r works on rows [start, start + valid_rows).
+ * wm_stage_inputs: staged_x[local_rows][hidden], routes[local_rows][top_k] int32, gates FP32 = that slice,
+ *   padded with zero rows whose routes are -1; negative ids stay -1 ("no route") and get gate 0.  Strides
+ *   are in elements; ids are int32 or (ids_are_int64) int64.
+ * wm_scatter_output: result[tokens][hidden] = zeros with rows [start, start + valid_rows) = output[0..). */
+WM_API int wm_stage_inputs(const void* x, int64_t x_row_stride, const void* ids, int32_t ids_are_int64,
+                           int64_t id_row_stride, const float* weights, int64_t weight_row_stride,
+                           int32_t start, int32_t valid_rows, int32_t local_rows, int32_t hidden,
+                           int32_t top_k, void* staged_x, int32_t* routes, float* gates, void* stream);
+WM_API int wm_scatter_output(const void* output, int32_t tokens, int32_t start, int32_t valid_rows,
+                             int32_t hidden, void* result, void* stream);
 
 /* Diagnostic: one grouped GEMM on caller buffers (synchronises `stream`).
  * kind 0: out[rows,n]   = a[rows,k] * b[g][n,k]^T          (FC2 form)

@@ -66,3 +66,29 @@ def test_megatron_adapter_forward_backward(fp8):
     adapter.suspend()
     assert adapter.runtime is None
     adapter.close()
+
+
+def test_sglang_staging_and_scatter_kernels_match_their_torch_definitions():
+    """wm_stage_inputs / wm_scatter_output (the jobs of the reference's Triton staging kernels,
+    weftmoe/_sglang_kernels.py:21-99) against the torch expressions that define them, bit for bit, for int32
+    and int64 ids, masked (-1) entries, a strided input, every rank's slice incl. an empty one."""
+    from weftmoe_b200 import sglang
+    torch.manual_seed(11)
+    tokens, hidden, k, world = 37, 512, 6, 4
+    wide = torch.randn(tokens, hidden + 64, device="cuda").bfloat16()
+    hidden_states = wide[:, :hidden]                                  # row stride hidden + 64 elements
+    weights = torch.rand(tokens, k, device="cuda")
+    for dtype in (torch.int32, torch.int64):
+        ids = torch.randint(-1, 16, (tokens, k), device="cuda", dtype=dtype)
+        for rank in range(world + 1):                                 # the last one is past the end: valid = 0
+            local, start, valid = sglang.row_shard(tokens, world, min(rank, world - 1) if rank < world else world - 1)
+            if rank == world:
+                start, valid = tokens, 0
+            mine = sglang.stage_inputs(hidden_states, ids, weights, start, valid, local)
+            ref = sglang.stage_inputs(hidden_states.cpu(), ids.cpu(), weights.cpu(), start, valid, local)
+            for a, b in zip(mine, ref):
+                assert a.dtype == b.dtype and torch.equal(a.cpu().view(torch.uint8), b.view(torch.uint8)), (dtype, rank)
+            out = torch.randn(local, hidden, device="cuda").bfloat16()
+            scattered = sglang.scatter_output(out, tokens, min(start, tokens), valid)
+            expect = sglang.scatter_output(out.cpu(), tokens, min(start, tokens), valid)
+            assert torch.equal(scattered.cpu().view(torch.int16), expect.view(torch.int16))

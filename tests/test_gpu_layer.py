@@ -220,6 +220,22 @@ def test_decode_under_cuda_graph_replays_and_matches_eager_bits():
     ref = O.moe_layer(b["x"].cpu(), b["routes"].cpu(), b["gates"].cpu(), a["w1"].cpu(), a["w2"].cpu())[0]
     assert rel_l2(y, ref) < TOL_ROUNDED_ORACLE
     del graph
+    # the (layer, tokens) plan contract of the reference (src/python/runtime.cpp:554-616): a prepared layer
+    # must be replayed with the addresses it was prepared with, until the layer is invalidated; a layer
+    # that was never warmed cannot be captured
+    moved = x.clone()
+    with pytest.raises(RuntimeError, match="addresses changed"):
+        rt.inference(0, moved, routes, gates, a["w1"], a["w2"])
+    with pytest.raises(RuntimeError, match="Expert addresses changed"):
+        rt.inference(0, x, routes, gates, a["w1"].clone(), a["w2"])
+    rt.invalidate_inference_layer(0)
+    assert torch.equal(bits(rt.inference(0, moved, routes, gates, a["w1"], a["w2"])), bits(eager_b))
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with pytest.raises(RuntimeError, match="Warm every inference layer"):
+            with torch.cuda.graph(torch.cuda.CUDAGraph(), stream=side):
+                rt.inference(7, moved, routes, gates, a["w1"], a["w2"])
+    torch.cuda.synchronize()
     rt.close()
 
 

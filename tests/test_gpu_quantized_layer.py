@@ -137,6 +137,37 @@ def test_fp8_training_forward_backward_meets_the_reference_acceptance(cfg):
     rt.close()
 
 
+def test_fp8_prequantised_sources_reproduce_the_online_bits():
+    """FP8Tensor x and dY (quantised 1 x 128 by quantize_fp8 beforehand) give exactly the bits of the BF16
+    sources that the layer quantises online (reference: tests/torchrun_fp8.py:133-157)."""
+    from weftmoe_b200.fp8 import quantize_fp8
+    cfg = dict(experts=16, top_k=4, hidden=512, intermediate=256, tokens=200)
+    d, g = inputs(cfg, 41, 1.0, 0.02)
+    rt = TensorRuntime(group=SingleRankGroup(), experts=cfg["experts"], top_k=cfg["top_k"], hidden=cfg["hidden"],
+                       intermediate=cfg["intermediate"], max_tokens=cfg["tokens"],
+                       max_rows=cfg["tokens"] * cfg["top_k"], training=True, precision="fp8", max_saved=2)
+    weights = prepare_fp8_weights(g["w1"], g["w2"], training=True)
+    online = rt.forward_fp8(g["x"], g["routes"], g["gates"], weights, weight_grad_dtype=torch.bfloat16)
+    online_grads = rt.backward(online, g["dy"])
+    xq, dyq = quantize_fp8(g["x"]), quantize_fp8(g["dy"])
+    tape = rt.forward_fp8(xq, g["routes"], g["gates"], weights, weight_grad_dtype=torch.bfloat16)
+    assert torch.equal(tape.output.view(torch.int16), online.output.view(torch.int16))
+    grads = rt.backward(tape, dyq)
+    for a, b in zip(grads, online_grads):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    with pytest.raises(ValueError):
+        rt.forward_fp8(quantize_fp8(g["x"], block_rows=128), g["routes"], g["gates"], weights)   # not 1 x 128 rows
+    rt.close()
+    bf16 = TensorRuntime(group=SingleRankGroup(), experts=cfg["experts"], top_k=cfg["top_k"], hidden=cfg["hidden"],
+                         intermediate=cfg["intermediate"], max_tokens=cfg["tokens"],
+                         max_rows=cfg["tokens"] * cfg["top_k"], training=True)
+    t = bf16.forward(g["x"], g["routes"], g["gates"], g["w1"], g["w2"])
+    with pytest.raises(ValueError):
+        bf16.backward(t, dyq)                                     # FP8 sources need an FP8 runtime
+    bf16.backward(t, g["dy"])
+    bf16.close()
+
+
 def test_fp8_weight_gradients_in_fp8_meet_the_same_acceptance():
     """WM_FP8_WGRAD=1 switches the two weight-gradient contractions to the reference's recipe (operands
     re-quantised 1 x 128 along the rows, blockwise-FP8 K-grouped GEMM; docs/usage.md:122-125).  The

@@ -43,3 +43,14 @@ def test_forward_is_refused_where_the_precision_has_its_own_entry_point(monkeypa
         make("fp8", True, intermediate=256).forward_async(*args)
     with pytest.raises(ValueError, match="inference_nvfp4"):
         make("nvfp4", False).forward_async(*args)
+
+
+def test_decode_only_runtimes_are_inference_only_and_bounded():
+    """decode_only is honoured, not ignored: a decode runtime (reference: the DT runtime, docs/usage.md:104-112)
+    refuses training and keeps every call within the single-launch route planner."""
+    assert make("bf16", False, decode_only=True).decode_only
+    with pytest.raises(ValueError, match="inference-only"):
+        make("bf16", True, decode_only=True)
+    with pytest.raises(ValueError, match="at most 4096 routes"):
+        TensorRuntime(group=SingleRankGroup(), experts=8, top_k=2, hidden=256, intermediate=256, max_tokens=4096,
+                      max_rows=64, training=False, stream=object(), decode_only=True, _native_factory=FakeNative)

@@ -29,7 +29,8 @@ class WmSizes(Structure):
 class WmQuantWeights(Structure):
     _fields_ = [("w1", c_void_p), ("w1_sf", c_void_p), ("w2", c_void_p), ("w2_sf", c_void_p),
                 ("x_scale", c_float), ("w1_scale", c_float), ("u_scale", c_float), ("w2_scale", c_float),
-                ("dy_scale", c_float), ("dab_scale", c_float)]
+                ("dy_scale", c_float), ("dab_scale", c_float),
+                ("source_q", c_void_p), ("source_scales", c_void_p)]
 
 
 class WmRouteOut(Structure):
@@ -71,6 +72,9 @@ SIGNATURES = {
     "wm_nvfp4_quantize": (c_int, [c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p, c_int32, c_void_p]),
     "wm_nvfp4_gemm": (c_int, [c_void_p] * 5 + [c_int32] * 3 + [c_float, c_int32, c_void_p]),
     "wm_route_plan_noalloc": (c_int, [c_int32] * 8 + [c_void_p, c_void_p, POINTER(WmRouteOut), c_void_p]),
+    "wm_stage_inputs": (c_int, [c_void_p, c_int64, c_void_p, c_int32, c_int64, c_void_p, c_int64] + [c_int32] * 5
+                        + [c_void_p, c_void_p, c_void_p, c_void_p]),
+    "wm_scatter_output": (c_int, [c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
     "wm_debug_force_gemm_pairs": (None, [c_int]),
     "wm_debug_set_wait_budget": (c_int, [ctypes.c_longlong]),
     "wm_debug_wait_flag": (c_int, [c_void_p, c_void_p, c_int32, c_void_p]),

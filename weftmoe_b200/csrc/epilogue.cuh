@@ -101,7 +101,6 @@ template <int BLOCK_N>
 struct EpilogueStoreTma {
   alignas(64) CUtensorMap tmap;
   int rows_per_group;  // K-grouped: M (rows of one expert's output); 0 for M-grouped
-  int debug_skip;      // diagnostics (WM_DEBUG_EPILOGUE): 1 = pack but issue no store, 2 = read TMEM only
 
   __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane,
                                              bool zero, uint8_t* stage) const {
@@ -127,10 +126,6 @@ struct EpilogueStoreTma {
         if (unit + 1 < kUnits) tmem_ld_32x64(taddr + (unit + 1) * 64, v);
       }
       uint8_t* box = stage + (unit & 1) * 4096;
-      if (debug_skip == 2) {
-        if (w[0] == 0x7fc07fc1u) box[lane] = 1;  // keeps the read-out alive; never true for packed sums
-        continue;
-      }
       if (lane == 0) bulk_wait_group_read<1>();  // the store issued from this box two units ago
       __syncwarp();
 #pragma unroll
@@ -139,7 +134,7 @@ struct EpilogueStoreTma {
             make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0 && debug_skip == 0) {
+      if (lane == 0) {
         tma_store_2d(&tmap, box, col0 + unit * 64, row0);
         bulk_commit_group();
       }

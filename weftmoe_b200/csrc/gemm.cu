@@ -331,7 +331,6 @@ static int launch_mgrouped(const Schedule& s, const __nv_bfloat16* a_ptr, const 
     EpilogueStoreTma<256> epi{};
     if (int rc = make_tmap_2d(&epi.tmap, out, 2, n, s.row_capacity, (uint64_t)n * 2, 64, 32)) return rc;
     epi.rows_per_group = 0;
-    epi.debug_skip = 0;
     return launch<256, false, B_MN, false, false>(pair, ta, tb, a, s, epi, sms, stream);
   }
   if (bn == 256) {
@@ -390,8 +389,6 @@ int launch_kgrouped_tn(const Schedule& s, const __nv_bfloat16* a_ptr, const __nv
     EpilogueStoreTma<256> epi{};
     if (int rc = make_tmap_2d(&epi.tmap, out, 2, n, (uint64_t)s.groups * m, (uint64_t)n * 2, 64, 32)) return rc;
     epi.rows_per_group = m;
-    static const int debug_skip = [] { const char* v = std::getenv("WM_DEBUG_EPILOGUE"); return v ? std::atoi(v) : 0; }();
-    epi.debug_skip = debug_skip;
     return launch<256, true, true, false, true>(pair, ta, tb, a, s, epi, sms, stream);
   }
   if (bn == 256) {

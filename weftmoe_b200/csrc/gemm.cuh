@@ -202,6 +202,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      // Issues the loads of one k block of a tile.
+      auto issue = [&](const TileCoord& t, int kb, uint8_t* sa, uint64_t* bar) {
+        uint8_t* sb = sa + S::kABytes;
+        const int k0 = kb * kBlockK;
+        auto box = [&](uint8_t* dst, const CUtensorMap* map, int x, int y) { tma_load_2d(dst, map, bar, x, y); };
+        if constexpr (!A_MN) {
+          box(sa, &tmap_a, k0, t.m_tile * kBlockM);
+        } else {
+#pragma unroll
+          for (int j = 0; j < kBlockM / 64; ++j)
+            box(sa + j * (kBlockK * 128), &tmap_a, t.m_tile * kBlockM + j * 64, t.row0 + k0);
+        }
+        if constexpr (GATE_UP) {
+          const int r = t.group * args.b_group_rows + t.n_tile * 128;
+          box(sb, &tmap_b, k0, r);
+          box(sb + 128 * kBlockK * 2, &tmap_b, k0, r + args.gate_up_half);
+        } else if constexpr (!B_MN) {
+          box(sb, &tmap_b, k0, t.group * args.b_group_rows + t.n_tile * BLOCK_N);
+        } else {
+          const int krow = K_GROUPED ? (t.row0 + k0) : (t.group * args.b_group_rows + k0);
+#pragma unroll
+          for (int j = 0; j < BLOCK_N / 64; ++j)
+            box(sb + j * (kBlockK * 128), &tmap_b, t.n_tile * BLOCK_N + j * 64, krow);
+        }
+      };
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -218,33 +243,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (!ok) break;
           if (stamp && kb == 0) tl[2] = global_timer_ns();
           if (stamp && kb == t.num_kb - 1) tl[3] = global_timer_ns();
-          uint8_t* sa = smem + stage * S::kStageBytes;
-          uint8_t* sb = sa + S::kABytes;
           mbar_expect_tx(full_bar + stage, S::kStageBytes);
-          const int k0 = kb * kBlockK;
-          if constexpr (!A_MN) {
-            tma_load_2d(sa, &tmap_a, full_bar + stage, k0, t.m_tile * kBlockM);
-          } else {
-#pragma unroll
-            for (int j = 0; j < kBlockM / 64; ++j)
-              tma_load_2d(sa + j * (kBlockK * 128), &tmap_a, full_bar + stage,
-                          t.m_tile * kBlockM + j * 64, t.row0 + k0);
-          }
-          if constexpr (GATE_UP) {
-            const int r = t.group * args.b_group_rows + t.n_tile * 128;
-            tma_load_2d(sb, &tmap_b, full_bar + stage, k0, r);
-            tma_load_2d(sb + 128 * kBlockK * 2, &tmap_b, full_bar + stage, k0,
-                        r + args.gate_up_half);
-          } else if constexpr (!B_MN) {
-            tma_load_2d(sb, &tmap_b, full_bar + stage, k0,
-                        t.group * args.b_group_rows + t.n_tile * BLOCK_N);
-          } else {
-            const int krow = K_GROUPED ? (t.row0 + k0) : (t.group * args.b_group_rows + k0);
-#pragma unroll
-            for (int j = 0; j < BLOCK_N / 64; ++j)
-              tma_load_2d(sb + j * (kBlockK * 128), &tmap_b, full_bar + stage,
-                          t.n_tile * BLOCK_N + j * 64, krow);
-          }
+          issue(t, kb, smem + stage * S::kStageBytes, full_bar + stage);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }

@@ -1007,8 +1007,14 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
     set_error("Activation shape exceeds prepared capacity (%d tokens, capacity %d)", tokens, c.max_tokens);
     return WM_ERR_CAPACITY;
   }
+  const bool prequantised = weights && weights->source_q != nullptr;
+  if (prequantised && (c.reserved != 1 || !weights->source_scales || !aligned16(weights->source_q) ||
+                       !aligned16(weights->source_scales))) {
+    set_error("wm_forward_quantized: a prequantised source needs an FP8 runtime and 16-byte aligned bytes and scales");
+    return WM_ERR_INVALID;
+  }
   if (!weights || !weights->w1 || !weights->w1_sf || !weights->w2 || !weights->w2_sf ||
-      (tokens > 0 && (!x || !routes || !gates || !y)) || !aligned16(x) || !aligned16(y) ||
+      (tokens > 0 && ((!x && !prequantised) || !routes || !gates || !y)) || !aligned16(x) || !aligned16(y) ||
       !aligned16(weights->w1) || !aligned16(weights->w2) || !aligned16(weights->w1_sf) ||
       !aligned16(weights->w2_sf)) {
     set_error("wm_forward_quantized: null or misaligned tensor (16-byte alignment required)");
@@ -1080,7 +1086,13 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
     if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, nullptr, stream)) return rc;
   uint8_t* my_stage = rt->arena + rt->al.stage;
   if (tokens > 0) {
-    if (kind == kKindFp8) {
+    if (prequantised) {  // the caller's bytes and scales are what the online quantiser would have written
+      WM_CUDA(cudaMemcpyAsync(my_stage, weights->source_q, static_cast<size_t>(tokens) * H,
+                              cudaMemcpyDeviceToDevice, stream));
+      WM_CUDA(cudaMemcpyAsync(my_stage + sf_offset, weights->source_scales,
+                              static_cast<size_t>(tokens) * (H / 128) * sizeof(float), cudaMemcpyDeviceToDevice,
+                              stream));
+    } else if (kind == kKindFp8) {
       if (int rc = fp8_quantize_rows(x, tokens, H, my_stage, reinterpret_cast<float*>(my_stage + sf_offset),
                                      rt->sms, stream))
         return rc;
@@ -1337,8 +1349,14 @@ extern "C" int wm_backward_quantized(wm_runtime* rt, const void* tape, const voi
     set_error("Backward token count %d exceeds capacity %d", tokens, c.max_tokens);
     return WM_ERR_CAPACITY;
   }
+  const bool prequantised = transposed && transposed->source_q != nullptr;
+  if (prequantised && (!transposed->source_scales || !aligned16(transposed->source_q) ||
+                       !aligned16(transposed->source_scales))) {
+    set_error("wm_backward_quantized: a prequantised dY needs 16-byte aligned bytes and scales");
+    return WM_ERR_INVALID;
+  }
   if (!tape || !transposed || !transposed->w1 || !transposed->w1_sf || !transposed->w2 || !transposed->w2_sf ||
-      !dw1 || !dw2 || (tokens > 0 && (!dy || !dx || !dgates)) || !aligned16(tape) || !aligned16(dy) ||
+      !dw1 || !dw2 || (tokens > 0 && ((!dy && !prequantised) || !dx || !dgates)) || !aligned16(tape) || !aligned16(dy) ||
       !aligned16(dx) || !aligned16(dw1) || !aligned16(dw2)) {
     set_error("wm_backward_quantized: null or misaligned tensor (16-byte alignment required)");
     return WM_ERR_INVALID;
@@ -1393,10 +1411,17 @@ extern "C" int wm_backward_quantized(wm_runtime* rt, const void* tape, const voi
   if (world > 1)
     if (int rc = wait_flags(my_flags(rt, kPulled), world, gen - 1, status, nullptr, stream)) return rc;
   uint8_t* my_stage = rt->arena + rt->al.stage;
-  if (tokens > 0)
+  if (tokens > 0 && prequantised) {
+    WM_CUDA(cudaMemcpyAsync(my_stage, transposed->source_q, static_cast<size_t>(tokens) * H,
+                            cudaMemcpyDeviceToDevice, stream));
+    WM_CUDA(cudaMemcpyAsync(my_stage + sf_offset, transposed->source_scales,
+                            static_cast<size_t>(tokens) * (H / 128) * sizeof(float), cudaMemcpyDeviceToDevice,
+                            stream));
+  } else if (tokens > 0) {
     if (int rc = fp8_quantize_rows(dy, tokens, H, my_stage, reinterpret_cast<float*>(my_stage + sf_offset),
                                    rt->sms, stream))
       return rc;
+  }
   if (world > 1) {
     if (int rc = signal_peers(flag_group(rt, kReady), world, c.rank, gen, stream)) return rc;
     if (int rc = wait_flags(my_flags(rt, kReady), world, gen, status, const_cast<int*>(split), stream)) return rc;

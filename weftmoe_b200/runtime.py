@@ -23,6 +23,11 @@ import torch.distributed as dist
 from . import _lib
 
 
+# Routes (tokens * top_k) per rank that the single-launch planner of libweftmoe_b200 handles
+# (kSmallPlanRoutes in csrc/route.h); a decode_only runtime never exceeds it.
+DECODE_MAX_ROUTES = 4096
+
+
 class SingleRankGroup:
     """Stand-in for a one-rank process group, so EP1 needs no torch.distributed initialisation.
 
@@ -107,6 +112,7 @@ class NativeRuntime:
                        else stream)
         self.training, self.max_saved = training, max_saved
         self.tapes = weakref.WeakSet()
+        self.plans = {}          # (layer, tokens) -> addresses a replayable inference was prepared with
         self.shape = (experts, top_k, hidden, intermediate)
         self.local_experts = experts // collectives.world
         config = _lib.WmConfig(rank=collectives.rank, world=collectives.world, experts=experts,
@@ -183,15 +189,21 @@ class NativeRuntime:
 
     # ------------------------------------------------------------------ quantised inference
     def _run_quantized(self, x, routes, gates, packed, save=False):
-        """packed: (w1 data, w1 scale chunks, w2 data, w2 scale chunks, x_scale, w1_scale, u_scale, w2_scale)."""
+        """packed: (w1 data, w1 scale chunks, w2 data, w2 scale chunks, x_scale, w1_scale, u_scale, w2_scale).
+        x: BF16 [T, H], or (FP8 only) an FP8Tensor of that shape quantised 1 x 128, whose bytes and scales
+        are used as they are."""
         self._require()
+        from .fp8 import FP8Tensor
+        source = x if isinstance(x, FP8Tensor) else None
+        if source is not None:
+            x = source.data
         caller = torch.cuda.current_stream()
         if caller.device != self.stream.device or x.device != self.stream.device:
             raise ValueError("Workspace and tensors must share the current device")
         if caller != self.stream:
             self.stream.wait_stream(caller)
         with torch.cuda.stream(self.stream):
-            y = torch.empty_like(x)
+            y = torch.empty(tuple(x.shape), dtype=torch.bfloat16, device=x.device)
             blob = None
             if save:
                 if len(self.tapes) >= self.max_saved:
@@ -200,11 +212,15 @@ class NativeRuntime:
             w1, w1_sf, w2, w2_sf, sx, s1, su, s2 = packed
             weights = _lib.WmQuantWeights(w1=w1.data_ptr(), w1_sf=w1_sf.data_ptr(), w2=w2.data_ptr(),
                                           w2_sf=w2_sf.data_ptr(), x_scale=sx, w1_scale=s1, u_scale=su, w2_scale=s2)
-            _lib.check(self.lib.wm_forward_quantized(self.handle, _lib.ptr(x), _lib.ptr(routes), _lib.ptr(gates),
+            if source is not None:
+                weights.source_q, weights.source_scales = source.data.data_ptr(), source.scales.data_ptr()
+            _lib.check(self.lib.wm_forward_quantized(self.handle, None if source is not None else _lib.ptr(x),
+                                                     _lib.ptr(routes), _lib.ptr(gates),
                                                      ctypes.byref(weights), x.shape[0], _lib.ptr(y),
                                                      _lib.ptr(blob), self.stream.cuda_stream))
             if caller != self.stream:
-                for tensor in (x, routes, gates, w1, w1_sf, w2, w2_sf):
+                held = (x, routes, gates, w1, w1_sf, w2, w2_sf) + ((source.scales,) if source is not None else ())
+                for tensor in held:
                     tensor.record_stream(self.stream)
                 y.record_stream(caller)
         if caller != self.stream:
@@ -253,20 +269,29 @@ class NativeRuntime:
         return tape
 
     def _backward_fp8(self, tape, dy):
+        from .fp8 import FP8Tensor
         blob, weights, fp32_wgrad, tokens, _ = tape.state
-        if dy.dtype != torch.bfloat16 or dy.shape != tape.output.shape or dy.device != blob.device:
+        source = dy if isinstance(dy, FP8Tensor) else None
+        if source is not None:
+            if tuple(source.shape) != tuple(tape.output.shape) or source.data.device != blob.device:
+                raise ValueError("Backward requires dY matching the forward output")
+            dy = source.data
+        elif dy.dtype != torch.bfloat16 or dy.shape != tape.output.shape or dy.device != blob.device:
             raise ValueError("Backward requires BF16 dY matching the forward output")
         weights._validate_version(training=True)
         w1t, w1t_sf, w2t, w2t_sf = self._fp8_packed_transposed(weights)
         e, k = self.local_experts, self.shape[1]
         _, _, hidden, inter = self.shape
-        dx = torch.empty_like(dy)
+        dx = torch.empty(tuple(dy.shape), dtype=torch.bfloat16, device=dy.device)
         dgates = torch.empty((tokens, k), dtype=torch.float32, device=dy.device)
         dw1 = torch.empty((e, 2 * inter, hidden), dtype=torch.bfloat16, device=dy.device)
         dw2 = torch.empty((e, hidden, inter), dtype=torch.bfloat16, device=dy.device)
         packed = _lib.WmQuantWeights(w1=w1t.data_ptr(), w1_sf=w1t_sf.data_ptr(), w2=w2t.data_ptr(),
                                      w2_sf=w2t_sf.data_ptr(), x_scale=1.0, w1_scale=1.0, u_scale=1.0, w2_scale=1.0)
-        _lib.check(self.lib.wm_backward_quantized(self.handle, _lib.ptr(blob), _lib.ptr(dy), ctypes.byref(packed),
+        if source is not None:
+            packed.source_q, packed.source_scales = source.data.data_ptr(), source.scales.data_ptr()
+        _lib.check(self.lib.wm_backward_quantized(self.handle, _lib.ptr(blob),
+                                                  None if source is not None else _lib.ptr(dy), ctypes.byref(packed),
                                                   tokens, _lib.ptr(dx), _lib.ptr(dgates), _lib.ptr(dw1),
                                                   _lib.ptr(dw2), self.stream.cuda_stream))
         tape.state = None
@@ -292,10 +317,24 @@ class NativeRuntime:
     # NVFP4 training (reference: NVFP4Runtime.forward / weftmoe/nvfp4_backward.py): BF16 master weights are
     # quantised block-16 along the reduction axis of each contraction, forward layout in the forward
     # pass and transposed in the backward pass, with the runtime's layer scales.
+    def _nvfp4_weight_version(self, w1, w2):
+        """Identity of one version of the BF16 master weights, or None when it cannot be tracked (inference
+        tensors carry no in-place version counter).  The quantised forward and transposed layouts are kept
+        per version, so the masters are quantised once per optimizer step, not once per call."""
+        if w1.is_inference() or w2.is_inference():
+            return None
+        return (w1.data_ptr(), w1._version, w2.data_ptr(), w2._version, tuple(self.scales))
+
     def _forward_nvfp4(self, x, routes, gates, w1, w2, retain):
         from .nvfp4 import prepare_nvfp4_weights
         s = self.scales
-        q = prepare_nvfp4_weights(w1, w2, weight_scales=(s.w1, s.w2))
+        version = self._nvfp4_weight_version(w1, w2)
+        cache = getattr(self, "_nvfp4_cache", None)
+        if version is None or cache is None or cache["version"] != version:
+            cache = dict(version=version, forward=prepare_nvfp4_weights(w1, w2, weight_scales=(s.w1, s.w2)),
+                         transposed=None)
+            self._nvfp4_cache = cache
+        q = cache["forward"]
         packed = (q.fc1[0], q.fc1[1], q.fc2[0], q.fc2[1], s.x, s.w1, s.intermediate, s.w2)
         if self.training and retain:
             y, blob = self._run_quantized(x, routes, gates, packed, save=True)
@@ -312,10 +351,17 @@ class NativeRuntime:
         s = self.scales
         e, k = self.local_experts, self.shape[1]
         _, _, hidden, inter = self.shape
-        w1t = w1.transpose(1, 2).contiguous().view(e * hidden, 2 * inter)     # [E*H, 2I]: reduce over 2I
-        w2t = w2.transpose(1, 2).contiguous().view(e * inter, hidden)         # [E*I, H]:  reduce over H
-        w1t_q, w1t_sf = quantize_nvfp4(w1t, s.w1, chunked=True)
-        w2t_q, w2t_sf = quantize_nvfp4(w2t, s.w2, chunked=True)
+        version = self._nvfp4_weight_version(w1, w2)
+        cache = getattr(self, "_nvfp4_cache", None)
+        if version is not None and cache is not None and cache["version"] == version and cache["transposed"]:
+            w1t_q, w1t_sf, w2t_q, w2t_sf = cache["transposed"]
+        else:
+            w1t = w1.transpose(1, 2).contiguous().view(e * hidden, 2 * inter)     # [E*H, 2I]: reduce over 2I
+            w2t = w2.transpose(1, 2).contiguous().view(e * inter, hidden)         # [E*I, H]:  reduce over H
+            w1t_q, w1t_sf = quantize_nvfp4(w1t, s.w1, chunked=True)
+            w2t_q, w2t_sf = quantize_nvfp4(w2t, s.w2, chunked=True)
+            if version is not None and cache is not None and cache["version"] == version:
+                cache["transposed"] = (w1t_q, w1t_sf, w2t_q, w2t_sf)
         dx = torch.empty_like(dy)
         dgates = torch.empty((tokens, k), dtype=torch.float32, device=dy.device)
         dw1, dw2 = torch.empty_like(w1), torch.empty_like(w2)
@@ -365,6 +411,32 @@ class NativeRuntime:
 
     # ------------------------------------------------------------------ inference
     def graph_forward(self, layer, x, routes, gates, w1, w2, caller_stream, fp8_weights=None):
+        """Replayable inference of one (layer, token count) "plan" (reference: Runtime::graph_forward,
+        src/python/runtime.cpp:554-616).  The forward itself enqueues only stream-ordered kernels, so a
+        caller's capture records it directly; what a plan keeps is the reference's contract around it:
+        the first call of a (layer, tokens) pair must come outside capture (warm-up), and later calls must
+        present the same input, route, gate and weight addresses, because a captured graph replays the
+        addresses it was captured with.  invalidate_inference_layer(layer) forgets the layer's plans."""
+        if self.training:
+            raise ValueError("graph_forward is inference-only")
+        source = getattr(x, "data", x)                     # BF16 tensor, or the bytes of an FP8Tensor
+        scales = x.scales.data_ptr() if source is not x else 0
+        key = (layer, source.shape[0])
+        record = (source.data_ptr(), scales, routes.data_ptr(), gates.data_ptr(), w1.data_ptr(), w2.data_ptr(),
+                  None if fp8_weights is None else id(fp8_weights))
+        plan = self.plans.get(key)
+        if plan is None:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("Warm every inference layer/token bucket before outer graph capture")
+            plan = self.plans[key] = record
+        if plan[:4] != record[:4]:
+            raise RuntimeError("Inference input addresses changed: use stable CUDA Graph buffers or call "
+                               "invalidate_inference_layer(layer) before re-preparation")
+        if plan[6] != record[6]:
+            raise RuntimeError("Weight format/version changed: invalidate inference layer before re-preparation")
+        if plan[4:6] != record[4:6]:
+            raise RuntimeError("Expert addresses changed: discard outer graphs and call "
+                               "invalidate_inference_layer(layer) before re-preparation")
         if fp8_weights is not None:
             return self._run_quantized(x, routes, gates, self._fp8_packed(fp8_weights))
         return self._run(x, routes, gates, w1, w2)
@@ -378,7 +450,11 @@ class NativeRuntime:
         return output
 
     def invalidate_inference_layer(self, layer, caller_stream):
+        """Forget the plans of `layer` (its buffers or weights are about to change); graphs captured with
+        them must be discarded by the caller.  Waits for the layer's work in flight first."""
         self.stream.synchronize()
+        for key in [k for k in self.plans if k[0] == layer]:
+            del self.plans[key]
 
     # ------------------------------------------------------------------ lifecycle
     def drain_eager_inference(self):
@@ -504,6 +580,15 @@ class TensorRuntime:
             _validate_scales(self.nvfp4_scales)
         if hidden > 4096 and hidden % 512:
             raise ValueError("Blackwell combine requires hidden divisible by 512 when hidden > 4096")
+        if decode_only:
+            # A decode runtime (reference: the DT runtime, docs/usage.md:104-112) serves inference only and
+            # keeps every call within the single-launch route planner, so that a decode step is the same
+            # short launch sequence whatever the batch.
+            if training:
+                raise ValueError("decode_only runtimes are inference-only (training=False)")
+            if max_tokens * top_k > DECODE_MAX_ROUTES:
+                raise ValueError(f"decode_only runtimes hold at most {DECODE_MAX_ROUTES} routes per rank "
+                                 f"(max_tokens * top_k = {max_tokens * top_k})")
         if (max_tokens < 0 or hidden < 256 or hidden % 256 or not 128 <= intermediate <= 4096
                 or intermediate % 128 or experts % self.world or not 1 <= top_k <= min(32, experts)
                 or experts > 2048 or experts // self.world > 512
@@ -554,7 +639,18 @@ class TensorRuntime:
         self._check(x, routes, gates, w1, w2)
         return self.native.forward_async(x, routes, gates, w1, w2, retain_backward_state)
 
+    def _check_fp8_source(self, source):
+        """A prequantised source (x or dY): rows quantised 1 x 128 by quantize_fp8, one row per token."""
+        if self.precision != "fp8":
+            raise ValueError("Source must be BF16 or FP8Tensor with explicit row scales")
+        if (len(source.shape) != 2 or source.block_rows != 1 or source.shape[1] != self.hidden
+                or source.shape[0] > self.max_tokens or source.data.device != self.stream.device):
+            raise ValueError("Source shape/device/layout does not match runtime")
+
     def _check_dy(self, dy):
+        from .fp8 import FP8Tensor
+        if isinstance(dy, FP8Tensor):
+            return self._check_fp8_source(dy)
         if not isinstance(dy, torch.Tensor) or dy.dtype != torch.bfloat16:
             raise ValueError("Source must be BF16 or FP8Tensor with explicit row scales")
         if (dy.ndim != 2 or dy.shape[1] != self.hidden or dy.shape[0] > self.max_tokens
@@ -578,9 +674,13 @@ class TensorRuntime:
         return self.native.backward_async(tape, dy)
 
     def _check_quantized(self, x, routes, gates):
+        from .fp8 import FP8Tensor
         if self.native is None:
             raise RuntimeError("WeftMoE runtime is closed")
-        if (not isinstance(x, torch.Tensor) or x.dtype != torch.bfloat16 or x.ndim != 2
+        if isinstance(x, FP8Tensor):
+            self._check_fp8_source(x)
+            x = x.data
+        elif (not isinstance(x, torch.Tensor) or x.dtype != torch.bfloat16 or x.ndim != 2
                 or x.shape[1] != self.hidden or x.shape[0] > self.max_tokens or not x.is_cuda
                 or not x.is_contiguous() or x.device != self.stream.device):
             raise ValueError("Source shape/device/layout does not match runtime")
@@ -604,7 +704,9 @@ class TensorRuntime:
 
         Prepare weights with weftmoe_b200.fp8.prepare_fp8_weights before this call (training=True when
         a backward pass will follow).  Backward runs dU and dX in FP8 and the two weight gradients in
-        BF16 on the dequantised saved rows.  Prequantised FP8Tensor inputs are not accepted yet."""
+        BF16 on the dequantised saved rows.  x (and dY in backward) may also be an FP8Tensor quantised
+        1 x 128 by quantize_fp8: its bytes and scales are used as they are and give the same result bits as
+        the BF16 source (reference: tests/torchrun_fp8.py:133-157)."""
         if weight_grad_dtype not in (torch.bfloat16, torch.float32):
             raise ValueError("weight_grad_dtype must be torch.bfloat16 or torch.float32")
         if self.precision != "fp8":
@@ -612,7 +714,7 @@ class TensorRuntime:
         if self.training and torch.cuda.current_stream() != self.stream:
             raise RuntimeError("Runtime must be invoked on its preparation stream")
         self._check_quantized(x, routes, gates)
-        self._check_fp8_weights(weights, x.device)
+        self._check_fp8_weights(weights, getattr(x, "data", x).device)   # x: BF16 tensor or FP8Tensor
         weights.wait(training=self.training and retain_backward_state)
         return self.native.forward_fp8(x, routes, gates, weights, synchronize, retain_backward_state,
                                        weight_grad_dtype == torch.float32)
@@ -622,7 +724,7 @@ class TensorRuntime:
         if self.training or self.precision != "fp8":
             raise ValueError("inference_fp8 requires an FP8 runtime with training=False")
         self._check_quantized(x, routes, gates)
-        self._check_fp8_weights(weights, x.device)
+        self._check_fp8_weights(weights, getattr(x, "data", x).device)
         if torch.cuda.is_current_stream_capturing():
             weights._validate_version()
         else:

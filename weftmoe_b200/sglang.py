@@ -1,8 +1,10 @@
 """SGLang `FusedMoE.forward` adapter over `TensorRuntime`.
 
 Entry point `install(batch_invariant=True)` follows the reference's `weftmoe/sglang.py:215`; the row
-sharding / staging / scatter helpers restate `weftmoe/_sglang_kernels.py:21-99` and the layout logic of
-`weftmoe/sglang.py:363-487` with torch ops.  SGLang is imported lazily: the helpers work without it.
+sharding / staging / scatter helpers do the jobs of `weftmoe/_sglang_kernels.py:21-99` and the layout logic
+of `weftmoe/sglang.py:363-487`.  On CUDA tensors staging and scatter are one kernel each of
+libweftmoe_b200.so (`wm_stage_inputs`, `wm_scatter_output`); the torch expressions below define the same
+results and serve host tensors.  SGLang is imported lazily: the helpers work without it.
 
 Differences from the reference that follow from this runtime: masked top-k entries (-1) are legal route
 ids here, so sanitisation only zeroes their gates instead of substituting unused experts; one runtime serves
@@ -29,6 +31,14 @@ def sanitize_routes(ids: torch.Tensor, weights: torch.Tensor):
     return routes, gates.contiguous()
 
 
+def _native_ok(hidden_states, ids, weights):
+    """The staging kernel reads BF16 rows in 16-byte words, int32/int64 ids and FP32 weights, unit column stride."""
+    return (hidden_states.dtype == torch.bfloat16 and hidden_states.stride(1) == 1 and hidden_states.stride(0) % 8 == 0
+            and hidden_states.shape[1] % 8 == 0 and hidden_states.data_ptr() % 16 == 0
+            and ids.dtype in (torch.int32, torch.int64) and ids.stride(1) == 1
+            and weights.dtype == torch.float32 and weights.stride(1) == 1)
+
+
 def row_shard(tokens: int, world: int, rank: int):
     """Replicated rows are split evenly across ranks: (rows per rank, first row, valid rows of this rank)."""
     local = (tokens + world - 1) // world
@@ -46,6 +56,15 @@ def stage_inputs(hidden_states, topk_ids, topk_weights, start, valid_rows, local
                torch.empty((local_rows, k), dtype=torch.int32, device=hidden_states.device),
                torch.empty((local_rows, k), dtype=torch.float32, device=hidden_states.device))
     x, routes, gates = out
+    if hidden_states.is_cuda and _native_ok(hidden_states, topk_ids, topk_weights):
+        from . import _lib
+        with torch.cuda.device(hidden_states.device):
+            _lib.check(_lib.load().wm_stage_inputs(
+                _lib.ptr(hidden_states), hidden_states.stride(0), _lib.ptr(topk_ids),
+                int(topk_ids.dtype == torch.int64), topk_ids.stride(0), _lib.ptr(topk_weights),
+                topk_weights.stride(0), start, valid_rows, local_rows, hidden, k, _lib.ptr(x), _lib.ptr(routes),
+                _lib.ptr(gates), torch.cuda.current_stream().cuda_stream))
+        return x, routes, gates
     x.zero_()
     routes.fill_(-1)
     gates.zero_()
@@ -60,6 +79,13 @@ def stage_inputs(hidden_states, topk_ids, topk_weights, start, valid_rows, local
 def scatter_output(output, tokens, start, valid_rows):
     """Place this rank's rows into a zero [tokens, H] tensor; the model's tensor-parallel reduction then
     reassembles every row (reference: weftmoe/sglang.py:470-482)."""
+    if output.is_cuda and output.dtype == torch.bfloat16 and output.is_contiguous() and output.shape[1] % 8 == 0:
+        from . import _lib
+        result = output.new_empty((tokens, output.shape[1]))
+        with torch.cuda.device(output.device):
+            _lib.check(_lib.load().wm_scatter_output(_lib.ptr(output), tokens, start, valid_rows, output.shape[1],
+                                                     _lib.ptr(result), torch.cuda.current_stream().cuda_stream))
+        return result
     result = output.new_zeros((tokens, output.shape[1]))
     result[start:start + valid_rows].copy_(output[:valid_rows])
     return result
