@@ -129,3 +129,32 @@ def test_device_timeline_diagnostic_prints_the_stamps(kernel_choice):
     assert rows, run.stderr   # CTA 1 handled one tile (4 tiles over the grid) and stamped it
     stamps = [int(v) for v in rows[0].replace("|", " ").split()[1:]]
     assert len(stamps) == 12 and stamps[3] >= stamps[2] >= 0   # producer: last stage after first stage
+
+
+def test_cta_pair_and_one_cta_kernels_give_the_same_bits():
+    """The kernel choice depends on the batch (pairs where experts average many rows), so the two kernels
+    must agree bit for bit for the forward contractions: same K order, same UMMA_K, a row's accumulator only
+    sees that row, whichever way the tile is split over CTAs."""
+    lib = _lib.load()
+    torch.manual_seed(5)
+    dev = torch.device("cuda")
+    rows, n, k = [384, 128, 256], 512, 1024
+    total = sum(rows)
+    a = torch.randn(total, k, device=dev).bfloat16()
+    results = {}
+    try:
+        for mode in (0, 1):
+            lib.wm_debug_force_gemm_pairs(mode)
+            b = torch.randn(len(rows), n, k, device=dev, generator=torch.Generator(device=dev).manual_seed(1)).bfloat16()
+            out = torch.empty(total, n, device=dev, dtype=torch.bfloat16)
+            grouped_gemm(0, a, b, out, rows, n, k)                                  # FC2 form
+            w1 = torch.randn(len(rows), 2 * 256, k, device=dev, generator=torch.Generator(device=dev).manual_seed(2)).bfloat16()
+            u = torch.empty(total, 256, device=dev, dtype=torch.bfloat16)
+            ab = torch.empty(total, 512, device=dev, dtype=torch.bfloat16)
+            prob = torch.rand(total, device=dev, generator=torch.Generator(device=dev).manual_seed(3))
+            grouped_gemm(3, a, w1, u, rows, 256, k, aux=ab, prob=prob)              # FC1 + SwiGLU form
+            results[mode] = (out, u, ab)
+    finally:
+        lib.wm_debug_force_gemm_pairs(-1)
+    for single, pair in zip(results[0], results[1]):
+        assert torch.equal(single.view(torch.int16), pair.view(torch.int16))

@@ -168,6 +168,32 @@ def test_fp8_prequantised_sources_reproduce_the_online_bits():
     bf16.close()
 
 
+def test_fp8_imported_weights_keep_their_bits_and_non_power_of_two_scales_are_refused():
+    """Imported (already quantised) weights are used as they are: scaling their block scales by a power of two
+    scales the layer's output by exactly that factor pair.  Block scales with a mantissa (the reference imports
+    them with x1.125 / x0.875, tests/torchrun_fp8.py:235-255) are refused with a message instead of being
+    rounded or quantised again: the scaling here happens inside the MMA as UE8M0."""
+    from weftmoe_b200.fp8 import FP8Tensor
+    cfg = dict(experts=8, top_k=2, hidden=512, intermediate=256, tokens=96)
+    d, g = inputs(cfg, 51, 1.0, 0.02)
+    rt = runtime(cfg, "fp8")
+    base = prepare_fp8_weights(g["w1"], g["w2"], training=False)
+    y = rt.inference_fp8(0, g["x"], g["routes"], g["gates"], base)
+    scaled = lambda q, f: FP8Tensor(q.data, q.scales * f, tuple(q.shape), 128)
+    imported = prepare_fp8_weights(scaled(base.w1, 2.0), scaled(base.w2, 0.5), training=True)
+    assert torch.equal(imported.w1.data.view(torch.uint8), base.w1.data.view(torch.uint8))     # bytes untouched
+    assert imported.w1_t is not None and torch.equal(imported.w1.scales, base.w1.scales * 2.0)
+    rt.invalidate_inference_layer(0)
+    y2 = rt.inference_fp8(0, g["x"], g["routes"], g["gates"], imported)
+    # silu(2a) * 2b * 0.5 is not 2 * 0.5 * silu(a) * b: compare against the oracle on the dequantised weights
+    ref = O.quantized_layer(d["x"], d["routes"], d["gates"], imported.w1.dequantize().cpu().bfloat16(),
+                            imported.w2.dequantize().cpu().bfloat16(), kind="fp8")
+    assert rel_l2(y2, ref) < 2e-3 and not torch.equal(y2, y)
+    with pytest.raises(ValueError, match="powers of two"):
+        prepare_fp8_weights(scaled(base.w1, 1.125), scaled(base.w2, 0.875), training=False)
+    rt.close()
+
+
 def test_fp8_weight_gradients_in_fp8_meet_the_same_acceptance():
     """WM_FP8_WGRAD=1 switches the two weight-gradient contractions to the reference's recipe (operands
     re-quantised 1 x 128 along the rows, blockwise-FP8 K-grouped GEMM; docs/usage.md:122-125).  The

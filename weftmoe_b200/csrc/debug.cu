@@ -40,7 +40,7 @@ extern "C" int wm_debug_grouped_gemm(int kind, const void* a, const void* b, voi
   tile_group.push_back(0);
   int *d_num = nullptr, *d_tiles = nullptr, *d_starts = nullptr, *d_pairs = nullptr;
   int split[kSplitWords];
-  fill_whole_split(split, num_tiles, num_pairs, rows);
+  fill_whole_split(split, num_tiles, num_pairs, rows, groups);
   WM_CUDA(cudaMalloc(&d_pairs, pairs.size() * sizeof(int)));
   WM_CUDA(cudaMemcpyAsync(d_pairs, pairs.data(), pairs.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
   WM_CUDA(cudaMalloc(&d_num, sizeof(split)));

@@ -200,11 +200,8 @@ int launch_tile(const void* x, int batches, int rows, int cols, int mode, void* 
                 float* st, cudaStream_t stream) {
   if (batches == 0 || rows == 0 || cols == 0) return WM_OK;
   constexpr int smem = 128 * 129 * sizeof(float);
-  static bool configured = false;
-  if (!configured) {
-    WM_CUDA(cudaFuncSetAttribute(quantize_tile_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
-  }
+  static PerDeviceOnce configured;  // one table per template instantiation
+  if (int rc = opt_in_dynamic_smem(quantize_tile_kernel<T>, smem, configured)) return rc;
   dim3 grid((cols + 127) / 128, (rows + 127) / 128, batches);
   quantize_tile_kernel<T><<<grid, 256, smem, stream>>>(static_cast<const T*>(x), rows, cols, mode,
                                                        static_cast<unsigned char*>(q), s,

@@ -137,12 +137,15 @@ static int forced_pairs() {
   }
   return value;
 }
-// Per-contraction overrides for A/B runs: WM_PAIR_FWD (FC1 / FC2), WM_PAIR_DGRAD (dU / dX), WM_PAIR_WGRAD
-// (dW1 / dW2) = 0 / 1; unset = the measured default below.
-enum Contraction { kForward = 0, kDgrad = 1, kWgrad = 2 };
+// Per-contraction overrides for A/B runs: WM_PAIR_FC1, WM_PAIR_FC2, WM_PAIR_DGRAD (dU / dX), WM_PAIR_WGRAD
+// (dW1 / dW2) = 0 / 1; unset = the measured default below: with about 2048 rows per expert FC1 gains 3 - 8 %
+// on the pair kernel (its long K loop hides the cross-CTA hops), FC2 (K = I, a store-heavy epilogue) loses
+// 15 %.  The two kernels give the same bits (tests/test_gpu_gemm.py), so the choice may follow the batch.
+enum Contraction { kFc1 = 0, kFc2 = 1, kDgrad = 2, kWgrad = 3 };
 static int contraction_override(Contraction c) {
-  static const int values[3] = {
-      [] { const char* v = std::getenv("WM_PAIR_FWD"); return v ? (v[0] != '0') : -1; }(),
+  static const int values[4] = {
+      [] { const char* v = std::getenv("WM_PAIR_FC1"); return v ? (v[0] != '0') : -1; }(),
+      [] { const char* v = std::getenv("WM_PAIR_FC2"); return v ? (v[0] != '0') : -1; }(),
       [] { const char* v = std::getenv("WM_PAIR_DGRAD"); return v ? (v[0] != '0') : -1; }(),
       [] { const char* v = std::getenv("WM_PAIR_WGRAD"); return v ? (v[0] != '0') : -1; }()};
   return values[c];
@@ -152,7 +155,7 @@ static bool use_pairs(const Schedule& s, Contraction c) {
   if (forced >= 0) return forced == 1;
   const int override = contraction_override(c);
   if (override >= 0) return override == 1;
-  return c != kForward && s.many_rows_per_expert;
+  return c != kFc2 && s.many_rows_per_expert;
 }
 
 template <int BLOCK_N, bool A_MN, bool B_MN, bool GATE_UP, bool K_GROUPED, class Epi, int EPI_WARPS = 4>
@@ -160,11 +163,8 @@ static int launch_single(const CUtensorMap& ta, const CUtensorMap& tb, const Gem
                          const Epi& epi, int sms, cudaStream_t stream) {
   auto kernel = gemm_kernel<BLOCK_N, A_MN, B_MN, GATE_UP, K_GROUPED, Epi, EPI_WARPS>;
   constexpr int smem = GemmSmem<BLOCK_N>::kTotal;
-  static bool configured = false;  // one flag per template instantiation
-  if (!configured) {
-    WM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
-  }
+  static PerDeviceOnce configured;  // one table per template instantiation
+  if (int rc = opt_in_dynamic_smem(kernel, smem, configured)) return rc;
   kernel<<<sms, 64 + 32 * EPI_WARPS, smem, stream>>>(ta, tb, args, epi);
   WM_CUDA(cudaGetLastError());
   count_launch();
@@ -176,11 +176,8 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
                        const Schedule& s, const Epi& epi, int sms, cudaStream_t stream) {
   auto kernel = gemm2_kernel<BLOCK_N, A_MN, B_MN, GATE_UP, K_GROUPED, Epi>;
   constexpr int smem = Gemm2Smem<BLOCK_N>::kTotal;
-  static bool configured = false;
-  if (!configured) {
-    WM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
-  }
+  static PerDeviceOnce configured;  // one table per template instantiation
+  if (int rc = opt_in_dynamic_smem(kernel, smem, configured)) return rc;
   const DeviceRange pairs = split_range(s.split, 1, s.chunk);
   Gemm2Args a2{args, pairs.begin, pairs.end, s.pair_tiles};
   kernel<<<sms & ~1, kGemmThreads, smem, stream>>>(ta, tb, a2, epi);  // clusters of two CTAs
@@ -268,6 +265,7 @@ static GemmArgs base_args(const Schedule& s, int* status) {
   a.tile_group = s.tile_group;
   a.group_row_start = s.group_row_start;
   a.group_live_rows = s.group_live_rows;
+  a.group_order = s.group_order;
   a.groups = s.groups;
   a.status = status;
   return a;
@@ -287,7 +285,7 @@ int launch_fc1(const Schedule& s, const __nv_bfloat16* x, const __nv_bfloat16* w
   a.gate_up_half = inter;
   EpilogueSwiglu epi{u, ab, row_prob, inter};
   TimelineScope timeline("fc1", a);
-  return launch<256, false, false, true, false>(use_pairs(s, kForward), ta, tb, a, s, epi, sms, stream);
+  return launch<256, false, false, true, false>(use_pairs(s, kFc1), ta, tb, a, s, epi, sms, stream);
 }
 
 template <bool B_MN>
@@ -301,7 +299,7 @@ static int launch_mgrouped(const Schedule& s, const __nv_bfloat16* a_ptr, const 
     set_error("grouped GEMM needs N %% 128 == 0, got %d", n);
     return 2;
   }
-  const bool pair = use_pairs(s, B_MN ? kDgrad : kForward);  // B MN-major = dU / dX
+  const bool pair = use_pairs(s, B_MN ? kDgrad : kFc2);  // B MN-major = dU / dX
   if (B_MN) {
     if (int rc = make_tmap_2d(&tb, b_ptr, 2, n, (uint64_t)s.groups * k, (uint64_t)n * 2, 64, 64)) return rc;
   } else {
@@ -384,6 +382,11 @@ int launch_kgrouped_tn(const Schedule& s, const __nv_bfloat16* a_ptr, const __nv
   GemmArgs a = base_args(s, status);
   a.m_tiles_per_group = m / 128;
   a.n_tiles = n / bn;
+  if (s.split != nullptr && s.chunk >= 0) {  // the experts of one chunk only
+    const DeviceRange experts = split_range(s.split, 3, s.chunk);
+    a.group_begin = experts.begin;
+    a.group_end = experts.end;
+  }
   TimelineScope timeline("wgrad", a);
   if (bn == 256 && tma_epilogue()) {
     EpilogueStoreTma<256> epi{};

@@ -37,7 +37,10 @@ struct GemmArgs {
   const int* tile_group;       // M-grouped: expert of each 128-row tile
   const int* group_row_start;  // K-grouped: [groups + 1] padded row offsets (multiples of 64)
   const int* group_live_rows;  // K-grouped, optional: [groups] rows that are not padding (the rest are zero)
+  const int* group_order;      // K-grouped, optional: [groups] experts in descending order of rows (tile walk order)
   int groups;                  // K-grouped: number of experts
+  const int* group_begin;      // K-grouped, optional device scalars: range of expert slots to process
+  const int* group_end;        //   (null = all `groups`)
   int m_tiles_per_group;       // K-grouped: M_total / 128
   int n_tiles;                 // N_total / BLOCK_N  (gate/up pair: I / 128)
   int k_total;                 // M-grouped: reduction extent in elements
@@ -96,8 +99,10 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& a, int tile) {
     t.num_kb = a.k_total / kBlockK;
   } else {
     const int per_group = a.m_tiles_per_group * a.n_tiles;
-    t.group = tile / per_group;
-    const int rem = tile - t.group * per_group;
+    const int local_slot = tile / per_group;
+    const int slot = local_slot + (a.group_begin != nullptr ? __ldg(a.group_begin) : 0);
+    t.group = a.group_order != nullptr ? __ldg(a.group_order + slot) : slot;
+    const int rem = tile - local_slot * per_group;
     t.m_tile = rem / a.n_tiles;
     t.n_tile = rem - t.m_tile * a.n_tiles;
     t.row0 = __ldg(a.group_row_start + t.group);
@@ -193,7 +198,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   int total_tiles, first_tile = 0;
   if constexpr (K_GROUPED) {
-    total_tiles = args.groups * args.m_tiles_per_group * args.n_tiles;
+    const int slots = args.group_begin != nullptr ? __ldg(args.group_end) - __ldg(args.group_begin) : args.groups;
+    total_tiles = slots * args.m_tiles_per_group * args.n_tiles;
   } else {
     first_tile = __ldg(args.tile_begin) * args.n_tiles;
     total_tiles = __ldg(args.tile_end) * args.n_tiles;

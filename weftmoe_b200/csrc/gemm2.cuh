@@ -65,8 +65,10 @@ __device__ __forceinline__ PairTile decode_pair(const Gemm2Args& a, int work, in
   } else {
     const int m_pairs = g.m_tiles_per_group / 2;
     const int per_group = m_pairs * g.n_tiles;
-    p.t.group = work / per_group;
-    const int rem = work - p.t.group * per_group;
+    const int local_slot = work / per_group;
+    const int slot = local_slot + (g.group_begin != nullptr ? __ldg(g.group_begin) : 0);
+    p.t.group = g.group_order != nullptr ? __ldg(g.group_order + slot) : slot;
+    const int rem = work - local_slot * per_group;
     const int mp = rem / g.n_tiles;
     p.t.n_tile = rem - mp * g.n_tiles;
     p.t.m_tile = mp * 2 + cta;
@@ -135,7 +137,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
 
   int total_work, first_work = 0;
   if constexpr (K_GROUPED) {
-    total_work = args.groups * (args.m_tiles_per_group / 2) * args.n_tiles;
+    const int slots = args.group_begin != nullptr ? __ldg(args.group_end) - __ldg(args.group_begin) : args.groups;
+    total_work = slots * (args.m_tiles_per_group / 2) * args.n_tiles;
   } else {
     first_work = __ldg(args2.pair_begin) * args.n_tiles;
     total_work = __ldg(args2.pair_end) * args.n_tiles;

@@ -278,11 +278,8 @@ int launch_bs(const CUtensorMap& ta, const CUtensorMap& tb, const BsArgs& args, 
               cudaStream_t stream) {
   auto kernel = gemm_bs_kernel<KIND, K_GROUPED, Epi>;
   constexpr int smem = BsConfig<KIND>::kTotal;
-  static bool configured = false;
-  if (!configured) {
-    WM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
-  }
+  static PerDeviceOnce configured;  // one table per template instantiation
+  if (int rc = opt_in_dynamic_smem(kernel, smem, configured)) return rc;
   kernel<<<sms, kGemmThreads, smem, stream>>>(ta, tb, args, epi);
   WM_CUDA(cudaGetLastError());
   count_launch();

@@ -32,6 +32,22 @@ void force_gemm_pairs(int mode);
     }                                                                                 \
   } while (0)
 
+// Function attributes belong to a device: opt a kernel in to `bytes` of dynamic shared memory once per
+// device of this process (`done` is one static table per kernel instantiation).
+struct PerDeviceOnce {
+  bool done[64] = {};
+};
+template <class Kernel>
+inline int opt_in_dynamic_smem(Kernel kernel, int bytes, PerDeviceOnce& once) {
+  int device = 0;
+  WM_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= 64 || !once.done[device]) {
+    WM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    if (device >= 0 && device < 64) once.done[device] = true;
+  }
+  return 0;
+}
+
 // ------------------------------------------------------------------ tensor maps
 // 2-D BF16 (elem_bytes = 2) or 8-bit (elem_bytes = 1) row-major tensor, 128-byte swizzle.
 // box_inner * elem_bytes must be 128.  Returns 0 on success.
@@ -49,6 +65,7 @@ struct Schedule {
   bool many_rows_per_expert;   // host estimate: experts average >= 1024 rows (long K loops, few odd tiles)
   int chunk;                   // which chunk of the M-grouped work to run (kWhole = all of it)
   const int* group_live_rows = nullptr;  // device [groups], optional: unpadded rows per expert (K-grouped)
+  const int* group_order = nullptr;      // device [groups], optional: experts by descending rows (K-grouped walk)
 };
 
 struct PushTarget {

@@ -96,12 +96,21 @@ __device__ void publish_empty_schedule(const PlanTables& t, int e_local) {
   for (int l = threadIdx.x; l <= e_local; l += blockDim.x) t.padded_start[l] = 0;
   if (t.live_rows != nullptr)
     for (int l = threadIdx.x; l < e_local; l += blockDim.x) t.live_rows[l] = 0;
+  if (t.group_order != nullptr)
+    for (int l = threadIdx.x; l < e_local; l += blockDim.x) t.group_order[l] = l;
   if (threadIdx.x == 0) {
     *t.num_tiles = 0;
     *t.padded_rows = 0;
     *t.num_pairs = 0;
   }
-  if (t.split != nullptr && threadIdx.x < kSplitWords) t.split[threadIdx.x] = 0;
+  if (t.split != nullptr) {
+    // no tiles, pairs or rows in any chunk; chunk 0 still names every local expert, so that the weight
+    // gradients of an empty call are written as zeros
+    for (int i = threadIdx.x; i < kSplitWords; i += blockDim.x) {
+      const int row = i / kSplitStride, c = i - row * kSplitStride;
+      t.split[i] = (row == 3 && c >= 1) ? e_local : 0;
+    }
+  }
 }
 
 // The plan itself, for one CTA whose threads have all seen every count row (callers wait for the COUNTS
@@ -168,7 +177,8 @@ __device__ void global_plan_body(const int* __restrict__ count_matrix, int world
       int* tiles_b = t.split;
       int* pairs_b = t.split + kSplitStride;
       int* rows_b = t.split + 2 * kSplitStride;
-      tiles_b[0] = pairs_b[0] = rows_b[0] = 0;
+      int* experts_b = t.split + 3 * kSplitStride;
+      tiles_b[0] = pairs_b[0] = rows_b[0] = experts_b[0] = 0;
       int rows = 0, l = 0;
       for (int c = 1; c <= kMaxChunks; ++c) {
         if (c < chunks) {
@@ -177,12 +187,15 @@ __device__ void global_plan_body(const int* __restrict__ count_matrix, int world
           tiles_b[c] = rows / 128;
           pairs_b[c] = l < e_local ? pair_first[l] : p;
           rows_b[c] = rows;
+          experts_b[c] = l;
         } else {
           tiles_b[c] = total_rows / 128;
           pairs_b[c] = p;
           rows_b[c] = total_rows;
+          experts_b[c] = e_local;
         }
       }
+
     }
   }
   __syncthreads();
@@ -192,6 +205,25 @@ __device__ void global_plan_body(const int* __restrict__ count_matrix, int world
     const int tiles = padded[e] / 128;
     t.padded_start[l] = start;
     if (t.live_rows != nullptr) t.live_rows[l] = total[e];
+    if (t.group_order != nullptr) {
+      // position of expert l when the experts of ITS CHUNK are sorted by rows, largest first (counting
+      // sort by comparison: at most 512 local experts); without a split all experts form one chunk
+      int first = 0, last = e_local;
+      if (t.split != nullptr) {
+        const int* experts_b = t.split + 3 * kSplitStride;
+        for (int c = 0; c < kMaxChunks; ++c)
+          if (l >= experts_b[c] && l < experts_b[c + 1]) {
+            first = experts_b[c];
+            last = experts_b[c + 1];
+          }
+      }
+      int before = 0;
+      for (int j = first; j < last; ++j) {
+        const int other = total[rank * e_local + j];
+        before += (other > total[e]) || (other == total[e] && j < l);
+      }
+      t.group_order[first + before] = l;
+    }
     for (int k = 0; k < tiles; ++k) t.tile_group[start / 128 + k] = l;
     for (int j = 0; j < (tiles + 1) / 2; ++j) {
       t.pair_tiles[2 * (pair_first[l] + j)] = start / 128 + 2 * j;
@@ -441,7 +473,8 @@ __global__ void __launch_bounds__(1024, 1) plan_small_kernel(const SmallPlan a) 
     }
     if (threadIdx.x < 32) {
       const bool failed = __any_sync(0xffffffffu, !arrived) || *reinterpret_cast<volatile int*>(a.status) != 0;
-      if (failed && a.tables.split != nullptr && threadIdx.x < kSplitWords) a.tables.split[threadIdx.x] = 0;
+      if (failed && a.tables.split != nullptr)
+        for (int i = threadIdx.x; i < kSplitWords; i += 32) a.tables.split[i] = 0;
     }
   }
 }

@@ -55,18 +55,22 @@ struct PlanTables {
   int* pair_tiles;     // [2 * pairs] two 128-row tiles of one expert per CTA pair, -1 = none
   int* num_pairs;      // scalar
   // Optional [kSplitWords]: the owner's work cut at expert boundaries into up to kMaxChunks chunks, so
-  // that a later chunk's transfers overlap an earlier chunk's compute.  Three rows of kMaxChunks + 1
-  // boundaries (tiles, CTA pairs, padded rows): chunk c is [b[c], b[c + 1]); b[0] = 0 and every
-  // boundary from the chunk count on equals the total, so unused chunks are empty.
+  // that a later chunk's transfers overlap an earlier chunk's compute.  Four rows of kMaxChunks + 1
+  // boundaries (tiles, CTA pairs, padded rows, local experts): chunk c is [b[c], b[c + 1]); b[0] = 0 and
+  // every boundary from the chunk count on equals the total, so unused chunks are empty.
   int* split;
   // Optional [experts/world]: unpadded rows of each local expert of this rank (the K-grouped weight
   // gradients stop their reduction at the last 64-row block that holds a live row).
   int* live_rows;
+  // Optional [experts/world]: this rank's local experts, chunk by chunk, inside a chunk in descending order
+  // of their rows (ties by index).  The K-grouped weight gradients walk their tiles in this order, so that
+  // the round-robin deal of tiles to CTAs gives every CTA nearly the same amount of reduction work.
+  int* group_order;
 };
 
 constexpr int kMaxChunks = 8;
 constexpr int kSplitStride = kMaxChunks + 1;
-constexpr int kSplitWords = 3 * kSplitStride;
+constexpr int kSplitWords = 4 * kSplitStride;
 
 // A [begin, end) range held in device memory (two pointers into PlanTables::split).
 struct DeviceRange {
@@ -74,14 +78,14 @@ struct DeviceRange {
   const int* end;
 };
 constexpr int kWhole = -1;  // "chunk" argument: all of the owner's work
-inline DeviceRange split_range(const int* split, int what /*0 tiles, 1 pairs, 2 rows*/, int chunk) {
+inline DeviceRange split_range(const int* split, int what /*0 tiles, 1 pairs, 2 rows, 3 experts*/, int chunk) {
   const int* b = split + what * kSplitStride;
   return chunk < 0 ? DeviceRange{b, b + kMaxChunks} : DeviceRange{b + chunk, b + chunk + 1};
 }
 // Host-side image of a split that has one chunk holding everything.
-inline void fill_whole_split(int* words, int tiles, int pairs, int rows) {
-  const int totals[3] = {tiles, pairs, rows};
-  for (int what = 0; what < 3; ++what) {
+inline void fill_whole_split(int* words, int tiles, int pairs, int rows, int experts) {
+  const int totals[4] = {tiles, pairs, rows, experts};
+  for (int what = 0; what < 4; ++what) {
     words[what * kSplitStride] = 0;
     for (int c = 1; c <= kMaxChunks; ++c) words[what * kSplitStride + c] = totals[what];
   }

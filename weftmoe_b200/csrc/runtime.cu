@@ -77,7 +77,7 @@ struct ScratchLayout {
 };
 // Training cache carved out of the caller's tape buffer.
 struct TapeLayout {
-  size_t sorted_slot, sorted_expert, padded_start, live_rows, tile_group, num_tiles, padded_rows, pair_tiles,
+  size_t sorted_slot, sorted_expert, padded_start, live_rows, group_order, tile_group, num_tiles, padded_rows, pair_tiles,
       num_pairs, split, origin, prob, primary, xrows, ab, total;
 };
 
@@ -211,6 +211,7 @@ TapeLayout tape_layout(const wm_config& c, int row_cap) {
   t.sorted_expert = k.take(sizeof(int) * routes);
   t.padded_start = k.take(sizeof(int) * (e_local + 1));
   t.live_rows = k.take(sizeof(int) * e_local);
+  t.group_order = k.take(sizeof(int) * e_local);
   t.tile_group = k.take(sizeof(int) * (row_cap / 128 + 1));
   t.num_tiles = k.take(sizeof(int));
   t.padded_rows = k.take(sizeof(int));
@@ -406,15 +407,21 @@ extern "C" int wm_runtime_create(const wm_config* config, wm_runtime** out) {
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&rt->push_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&rt->ev_pushed, cudaEventDisableTiming);
     // Chunks of the owner's rows: only the first chunk's pull is exposed, every later pull runs on the side
-    // stream beside the GEMMs of the chunks before it (WM_CHUNKS = 2..8).
-    rt->chunks = config->world == 8 ? 4 : 2;
+    // stream beside the GEMMs of the chunks before it (WM_CHUNKS = 2..8).  Measured at 2 and 4 ranks on the
+    // headline shape: 2 chunks 2.20 / 2.43 ms per step, 3 chunks 2.49 ms (4 ranks), 4 chunks 2.35 / 2.57 ms:
+    // smaller GEMM launches and more copy kernels beside them cost more than the shorter first pull saves.
+    rt->chunks = 2;
     if (const char* v = std::getenv("WM_CHUNKS")) {
       const int n = std::atoi(v);
       if (n >= 2 && n <= kMaxChunks) rt->chunks = n;
     }
-    // Measured on 8 x B200 (35B-A3B-like shape, skewed routing): 72 SMs for the pushes gives
-    // 2.98 ms per step against 3.08 ms without the overlap; 48 SMs gives 3.06 ms.  Off below 8 ranks.
-    rt->push_sms = rt->push_sms_bwd = config->world == 8 ? 72 : 0;
+    // SMs of the push GEMM when it runs beside the next chunk's compute (forward) or beside the chunk's own
+    // weight gradients (backward).  Measured on the headline shape with skewed routing: forward at 8 ranks
+    // 72 SMs 2.98 ms per step, none 3.08 ms, 48 SMs 3.06 ms; at 2 ranks 48 SMs 2.15 ms against 2.22 ms with
+    // none; backward (beside the weight gradients) at 2 / 4 ranks: 48 SMs 2.22 / 2.34 ms, 74 SMs 2.38 / 2.42 ms,
+    // 32 SMs 2.43 ms (2 ranks), 96 SMs 2.63 ms (4 ranks), weight gradients at the end 2.29 / 2.43 ms.
+    rt->push_sms = config->world == 8 ? 72 : 48;
+    rt->push_sms_bwd = 48;
     auto knob = [&](const char* name, int* value) {
       if (const char* v = std::getenv(name)) {
         const int n = std::atoi(v);
@@ -422,7 +429,6 @@ extern "C" int wm_runtime_create(const wm_config* config, wm_runtime** out) {
       }
     };
     knob("WM_PUSH_SMS", &rt->push_sms);
-    rt->push_sms_bwd = rt->push_sms;
     knob("WM_PUSH_SMS_BWD", &rt->push_sms_bwd);
     if (e != cudaSuccess) {
       set_error("side stream creation failed: %s", cudaGetErrorString(e));
@@ -561,15 +567,6 @@ static bool small_plan_allowed(long long routes) {
   return on && routes <= kSmallPlanRoutes;
 }
 
-// WM_PAIR_FWD=1 lets FC1 / FC2 take the CTA-pair kernel where experts average >= 1024 rows.
-static bool pairs_in_forward() {
-  static const bool on = [] {
-    const char* v = std::getenv("WM_PAIR_FWD");
-    return v && v[0] == '1';
-  }();
-  return on;
-}
-
 extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, const float* gates,
                           const void* w1, const void* w2, int32_t tokens, void* y, void* tape,
                           void* stream_) {
@@ -613,6 +610,7 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
   tables.num_pairs = tape ? at<int>(T, rt->tl.num_pairs) : at<int>(S, rt->sl.num_pairs);
   tables.split = tape ? at<int>(T, rt->tl.split) : at<int>(S, rt->sl.split);
   tables.live_rows = tape ? at<int>(T, rt->tl.live_rows) : nullptr;
+  tables.group_order = tape ? at<int>(T, rt->tl.group_order) : nullptr;
   int* origin = tape ? at<int>(T, rt->tl.origin) : at<int>(S, rt->sl.origin);
   float* prob = tape ? at<float>(T, rt->tl.prob) : at<float>(S, rt->sl.prob);
   // world > 1: row a duplicate of a token is copied from (the token crosses NVLink once per owner).
@@ -639,7 +637,7 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
   push.top_k = c.top_k;
 
   // Rows per local expert if routing were uniform: tokens * K * world / E (kernel choice only).
-  const bool many_rows = pairs_in_forward() && 1ll * tokens * c.top_k * world >= 1024ll * c.experts;
+  const bool many_rows = 1ll * tokens * c.top_k * world >= 1024ll * c.experts;
   // 1. staging buffer free?  then stage x and plan locally; counts go to every rank.
   TimingSlot* timing = begin_timing(rt, stream);
   if (world == 1) {
@@ -922,6 +920,29 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
     return launch_mgrouped_nn(schedule(chunk), dab, static_cast<const __nv_bfloat16*>(w1), nullptr, &push,
                               c.hidden, 2 * c.intermediate, status, sms, st);
   };
+  static const bool ordered_wgrad = [] {  // WM_WGRAD_ORDER=0: walk the experts in index order (A/B runs)
+    const char* v = std::getenv("WM_WGRAD_ORDER");
+    return !(v && v[0] == '0');
+  }();
+  static const bool interleave_wgrad = [] {  // WM_WGRAD_INTERLEAVE=0: all weight gradients after the last chunk
+    const char* v = std::getenv("WM_WGRAD_INTERLEAVE");
+    return !(v && v[0] == '0');
+  }();
+  auto weight_gradients = [&](int chunk, int sms) -> int {
+    Schedule sched = schedule(chunk);
+    sched.group_live_rows = reinterpret_cast<const int*>(tp(rt->tl.live_rows));
+    if (ordered_wgrad) sched.group_order = reinterpret_cast<const int*>(tp(rt->tl.group_order));
+    const int slot = chunk < 0 ? 0 : chunk;
+    {
+      StageScope scope(timing, kStageDw1, stream, slot);
+      if (int rc = launch_kgrouped_tn(sched, dab, xrows, static_cast<__nv_bfloat16*>(dw1), 2 * c.intermediate,
+                                      c.hidden, status, sms, stream))
+        return rc;
+    }
+    StageScope scope(timing, kStageDw2, stream, slot);
+    return launch_kgrouped_tn(sched, recv, u, static_cast<__nv_bfloat16*>(dw2), c.hidden, c.intermediate, status,
+                              sms, stream);
+  };
   if (chunks == 1) {
     {
       StageScope scope(timing, kStageGatherDy, stream);
@@ -943,41 +964,53 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
       }
       WM_CUDA(cudaEventRecord(rt->ev_pulled[k], rt->side));
     }
-    // With push_sms_bwd > 0, dX of chunk k pushes from a few SMs on a third stream while dU and the SwiGLU
-    // backward of chunk k + 1 compute on the others.
-    const bool beside = rt->push_sms_bwd > 0;
-    for (int k = 0; k < chunks; ++k) {
-      if (k > 0) WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_pulled[k], 0));
-      if (k == chunks - 1)
-        if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
-      if (int rc = du_and_swiglu(k, beside && k > 0 ? rt->sms - rt->push_sms_bwd : rt->sms)) return rc;
-      if (beside && k < chunks - 1) {
+    if (!interleave_wgrad) {
+      // With push_sms_bwd > 0, dX of chunk k pushes from a few SMs on a third stream while dU and the SwiGLU
+      // backward of chunk k + 1 compute on the others.
+      const bool beside = rt->push_sms_bwd > 0;
+      for (int k = 0; k < chunks; ++k) {
+        if (k > 0) WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_pulled[k], 0));
+        if (k == chunks - 1)
+          if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
+        if (int rc = du_and_swiglu(k, beside && k > 0 ? rt->sms - rt->push_sms_bwd : rt->sms)) return rc;
+        if (beside && k < chunks - 1) {
+          WM_CUDA(cudaEventRecord(rt->ev_ready[k], stream));
+          WM_CUDA(cudaStreamWaitEvent(rt->push_stream, rt->ev_ready[k], 0));
+          if (int rc = dx_push(k, rt->push_sms_bwd, rt->push_stream)) return rc;
+          WM_CUDA(cudaEventRecord(rt->ev_pushed, rt->push_stream));
+        } else {
+          if (beside) WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_pushed, 0));
+          if (int rc = dx_push(k, rt->sms, stream)) return rc;
+        }
+      }
+    } else {
+      // Chunk by chunk: dU + SwiGLU backward on every SM, then the chunk's dX GEMM (bound by its NVLink
+      // pushes) on `push` SMs of the third stream WHILE this stream computes the chunk's weight gradients
+      // (no communication, pure tensor work) on the other SMs.  The weight gradients of a chunk only need
+      // that chunk's rows, so they fill the time the link is the limit instead of running at the very end.
+      const int push = rt->push_sms_bwd > 0 ? rt->push_sms_bwd : (rt->sms / 2) & ~1;
+      for (int k = 0; k < chunks; ++k) {
+        if (k > 0) WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_pulled[k], 0));
+        if (k == chunks - 1)
+          if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
+        if (int rc = du_and_swiglu(k, rt->sms)) return rc;
         WM_CUDA(cudaEventRecord(rt->ev_ready[k], stream));
         WM_CUDA(cudaStreamWaitEvent(rt->push_stream, rt->ev_ready[k], 0));
-        if (int rc = dx_push(k, rt->push_sms_bwd, rt->push_stream)) return rc;
+        if (int rc = dx_push(k, push, rt->push_stream)) return rc;
+        if (k == chunks - 1)  // every result row of this call is on its way: tell the sources from that stream
+          if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, rt->push_stream)) return rc;
         WM_CUDA(cudaEventRecord(rt->ev_pushed, rt->push_stream));
-      } else {
-        if (beside) WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_pushed, 0));
-        if (int rc = dx_push(k, rt->sms, stream)) return rc;
+        if (int rc = weight_gradients(k, rt->sms - push)) return rc;
       }
+      WM_CUDA(cudaStreamWaitEvent(stream, rt->ev_pushed, 0));
     }
   }
-  Schedule sched = schedule(kWhole);
-  sched.group_live_rows = reinterpret_cast<const int*>(tp(rt->tl.live_rows));
-  if (world > 1)
-    if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
-  // 4. weight gradients: reductions over each expert's rows in the saved (fixed) order.
-  {
-    StageScope scope(timing, kStageDw1, stream);
-    if (int rc = launch_kgrouped_tn(sched, dab, xrows, static_cast<__nv_bfloat16*>(dw1),
-                                    2 * c.intermediate, c.hidden, status, rt->sms, stream))
-      return rc;
-  }
-  {
-    StageScope scope(timing, kStageDw2, stream);
-    if (int rc = launch_kgrouped_tn(sched, recv, u, static_cast<__nv_bfloat16*>(dw2), c.hidden,
-                                    c.intermediate, status, rt->sms, stream))
-      return rc;
+  // 4. weight gradients: reductions over each expert's rows in the saved (fixed) order (chunk by chunk above
+  //    when they are interleaved with the pushes).
+  if (!(chunks > 1 && interleave_wgrad)) {
+    if (world > 1)
+      if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
+    if (int rc = weight_gradients(kWhole, rt->sms)) return rc;
   }
   // 5. source side: ordered combine of dX, dprob back to the original slots.
   if (world > 1) {

@@ -25,7 +25,8 @@ __global__ void wait_flags_kernel(const int* flags, int world, Gen generation, i
   // empty the owner schedule's ranges so that no later kernel of the call follows indices that may
   // never have arrived.
   const bool failed = __any_sync(0xffffffffu, !ok) || *status != 0;
-  if (failed && split_on_fail != nullptr && threadIdx.x < kSplitWords) split_on_fail[threadIdx.x] = 0;
+  if (failed && split_on_fail != nullptr)
+    for (int i = threadIdx.x; i < kSplitWords; i += blockDim.x) split_on_fail[i] = 0;
 }
 __global__ void signal_peers_kernel(PeerInts group, int world, int slot, Gen gen) {
   const int generation = gen.value();

@@ -253,15 +253,25 @@ def _import_quantised(weight: FP8Tensor) -> FP8Tensor:
 
 
 def _check_imported(weights):
-    """Imported bytes must be finite E4M3 and their scales finite and positive (one host sync)."""
+    """Imported bytes must be finite E4M3 and their scales finite, positive powers of two (one host sync).
+
+    The block-scaled tensor-core kernels of this library apply the scales INSIDE the MMA as UE8M0 (power-of-two)
+    factors; a scale with a mantissa, as some checkpoints carry, would need the per-K128 FP32 promotion of the
+    reference's Hopper kernel (src/cuda/fp8/gemm.cuh:68-70), which is not built here.  Such weights are refused
+    rather than silently rounded or quantised again."""
     if not weights:
         return
-    verdicts = []
+    healthy, pow2 = [], []
     for w in weights:
-        verdicts.append((w.scales > 0).logical_and(torch.isfinite(w.scales)).all())
-        verdicts.append((w.data.view(torch.uint8).bitwise_and(0x7F) != 0x7F).all())   # 0x7f / 0xff = NaN
-    if not bool(torch.stack(verdicts).all()):
+        healthy.append((w.scales > 0).logical_and(torch.isfinite(w.scales)).all())
+        healthy.append((w.data.view(torch.uint8).bitwise_and(0x7F) != 0x7F).all())   # 0x7f / 0xff = NaN
+        pow2.append((w.scales.view(torch.int32).bitwise_and(0x007FFFFF) == 0).all())  # FP32 mantissa field empty
+    verdict = torch.stack([torch.stack(healthy).all(), torch.stack(pow2).all()]).tolist()
+    if not verdict[0]:
         raise ValueError("FP8 weights must be finite and scales finite and positive")
+    if not verdict[1]:
+        raise ValueError("Imported FP8 block scales must be powers of two: this library scales inside the MMA "
+                         "(UE8M0) and does not re-quantise imported weights")
 
 
 @torch.inference_mode(False)

@@ -419,8 +419,10 @@ class NativeRuntime:
         addresses it was captured with.  invalidate_inference_layer(layer) forgets the layer's plans."""
         if self.training:
             raise ValueError("graph_forward is inference-only")
-        source = getattr(x, "data", x)                     # BF16 tensor, or the bytes of an FP8Tensor
-        scales = x.scales.data_ptr() if source is not x else 0
+        from .fp8 import FP8Tensor
+        prequantised = isinstance(x, FP8Tensor)
+        source = x.data if prequantised else x             # BF16 tensor, or the bytes of an FP8Tensor
+        scales = x.scales.data_ptr() if prequantised else 0
         key = (layer, source.shape[0])
         record = (source.data_ptr(), scales, routes.data_ptr(), gates.data_ptr(), w1.data_ptr(), w2.data_ptr(),
                   None if fp8_weights is None else id(fp8_weights))
