@@ -1,6 +1,6 @@
 """TEST INFRASTRUCTURE ONLY — access to the reference's own torch layer, `verify_step`
 (benchmarks/training_reference.py:15-79), when `make -C oracle ref` byte-compiled it into
-oracle/_ref/training_reference.pyc.  Nothing of it is copied or restated here.
+oracle/_ref/training_reference.bytecode.  Nothing of it is copied or restated here.
 
 Only tests/ and bench.py's CPU legs (`--impl reference`, `cpu_baseline`) may import this module.
 `verify_step(runtime, x, routes, gates, w1, w2, dy)` runs the layer expert by expert on the host
@@ -12,7 +12,7 @@ import importlib.machinery
 import importlib.util
 from pathlib import Path
 
-COMPILED = Path(__file__).resolve().parent / "_ref" / "training_reference.pyc"
+COMPILED = Path(__file__).resolve().parent / "_ref" / "training_reference.bytecode"
 
 
 def load_verify_step():

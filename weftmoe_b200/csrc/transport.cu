@@ -51,21 +51,39 @@ int signal_peers(const PeerInts& group, int world, int slot, Gen generation, cud
 }
 
 // ------------------------------------------------------------------ row copies
-// One warp copies one row of `vecs` uint4 (16 B) words; up to four loads in flight per lane.
-__device__ __forceinline__ void copy_row(const uint4* __restrict__ src, uint4* __restrict__ dst,
-                                         int vecs, int lane) {
-  for (int c = lane; c < vecs; c += 128) {
-    uint4 v[4];
+// What a warp does with one row: copy `src` to `dst`, write zeros (src == nullptr), or nothing
+// (dst == nullptr).
+struct RowJob {
+  const uint4* src;
+  uint4* dst;
+};
+// One warp serves two rows at a time: every lane first issues all its loads of both rows (up to eight
+// 16-byte loads per lane: what covers the latency of a peer's memory over NVLink), then stores them.
+__device__ __forceinline__ void run_row_jobs(const RowJob& a, const RowJob& b, int vecs, int lane) {
+  constexpr int kDepth = 4;
+  for (int c = lane; c < vecs; c += 32 * kDepth) {
+    uint4 va[kDepth], vb[kDepth];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (c + 32 * j < vecs) v[j] = src[c + 32 * j];
+    for (int j = 0; j < kDepth; ++j) {
+      const int i = c + 32 * j;
+      va[j] = (a.src != nullptr && i < vecs) ? a.src[i] : make_uint4(0, 0, 0, 0);
+      vb[j] = (b.src != nullptr && i < vecs) ? b.src[i] : make_uint4(0, 0, 0, 0);
+    }
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (c + 32 * j < vecs) dst[c + 32 * j] = v[j];
+    for (int j = 0; j < kDepth; ++j) {
+      const int i = c + 32 * j;
+      if (a.dst != nullptr && i < vecs) a.dst[i] = va[j];
+      if (b.dst != nullptr && i < vecs) b.dst[i] = vb[j];
+    }
   }
 }
-__device__ __forceinline__ void zero_row(uint4* __restrict__ dst, int vecs, int lane) {
-  for (int c = lane; c < vecs; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+
+// The source row of a routed row: origin = src_rank * cap * top_k + token * top_k + sorted_slot.
+__device__ __forceinline__ const uint4* source_row(const PeerConstRows& stage, int org, int cap, int top_k,
+                                                   int hidden) {
+  const int src = org / (cap * top_k);
+  const int token = (org - src * cap * top_k) / top_k;
+  return reinterpret_cast<const uint4*>(stage.p[src] + static_cast<size_t>(token) * hidden);
 }
 
 __global__ void gather_rows_kernel(OwnerRows o, int rank, int e_local, int world, int row_capacity,
@@ -80,7 +98,9 @@ __global__ void gather_rows_kernel(OwnerRows o, int rank, int e_local, int world
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const int vecs = hidden / 8;
-  for (int r = *o.rows.begin + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += warps) {
+  // Looks row r up, writes its origin / prob / primary words and says what to copy.
+  auto job_of = [&](int r) -> RowJob {
+    if (r >= rows) return RowJob{nullptr, nullptr};
     const int l = o.tile_group[r >> 7];
     const int within = r - o.padded_start[l];
     const bool live = within < o.expert_total[rank * e_local + l];
@@ -91,26 +111,23 @@ __global__ void gather_rows_kernel(OwnerRows o, int rank, int e_local, int world
     if (live && org >= 0 && org < world * cap * top_k) {
       int first = meta_primary ? meta_primary[r] : r;
       if (first < 0 || first >= row_capacity) first = r;
-      if (first == r) {  // duplicates of a token inside this rank are copied locally afterwards
-        const int src = org / (cap * top_k);
-        const int token = (org - src * cap * top_k) / top_k;
-        copy_row(reinterpret_cast<const uint4*>(stage.p[src] + static_cast<size_t>(token) * hidden),
-                 dst, vecs, lane);
-      }
       if (lane == 0) {
         origin_out[r] = org;
         prob_out[r] = meta_prob[r];
         if (primary_out) primary_out[r] = first;
       }
-    } else {
-      zero_row(dst, vecs, lane);
-      if (lane == 0) {
-        origin_out[r] = -1;
-        prob_out[r] = 0.0f;
-        if (primary_out) primary_out[r] = r;
-      }
+      // duplicates of a token inside this rank are copied locally afterwards
+      return first == r ? RowJob{source_row(stage, org, cap, top_k, hidden), dst} : RowJob{nullptr, nullptr};
     }
-  }
+    if (lane == 0) {
+      origin_out[r] = -1;
+      prob_out[r] = 0.0f;
+      if (primary_out) primary_out[r] = r;
+    }
+    return RowJob{nullptr, dst};
+  };
+  for (int r = *o.rows.begin + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += 2 * warps)
+    run_row_jobs(job_of(r), job_of(r + warps), vecs, lane);
 }
 
 __global__ void gather_by_origin_kernel(DeviceRange range, const int* __restrict__ origin,
@@ -121,19 +138,16 @@ __global__ void gather_by_origin_kernel(DeviceRange range, const int* __restrict
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const int vecs = hidden / 8;
-  for (int r = *range.begin + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += warps) {
+  auto job_of = [&](int r) -> RowJob {
+    if (r >= rows) return RowJob{nullptr, nullptr};
     const int org = origin[r];
     uint4* dst = reinterpret_cast<uint4*>(rows_out + static_cast<size_t>(r) * hidden);
-    if (org >= 0 && org < world * cap * top_k) {
-      if (primary != nullptr && primary[r] != r) continue;  // copied locally afterwards
-      const int src = org / (cap * top_k);
-      const int token = (org - src * cap * top_k) / top_k;
-      copy_row(reinterpret_cast<const uint4*>(stage.p[src] + static_cast<size_t>(token) * hidden),
-               dst, vecs, lane);
-    } else {
-      zero_row(dst, vecs, lane);
-    }
-  }
+    if (org < 0 || org >= world * cap * top_k) return RowJob{nullptr, dst};      // padding: zeros
+    if (primary != nullptr && primary[r] != r) return RowJob{nullptr, nullptr};  // copied locally afterwards
+    return RowJob{source_row(stage, org, cap, top_k, hidden), dst};
+  };
+  for (int r = *range.begin + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += 2 * warps)
+    run_row_jobs(job_of(r), job_of(r + warps), vecs, lane);
 }
 
 __global__ void copy_duplicate_rows_kernel(DeviceRange range, const int* __restrict__ primary,
@@ -142,12 +156,15 @@ __global__ void copy_duplicate_rows_kernel(DeviceRange range, const int* __restr
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const int vecs = hidden / 8;
-  for (int r = *range.begin + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += warps) {
+  auto job_of = [&](int r) -> RowJob {
+    if (r >= rows) return RowJob{nullptr, nullptr};
     const int first = primary[r];
-    if (first == r || first < 0) continue;
-    copy_row(reinterpret_cast<const uint4*>(rows_out + static_cast<size_t>(first) * hidden),
-             reinterpret_cast<uint4*>(rows_out + static_cast<size_t>(r) * hidden), vecs, lane);
-  }
+    if (first == r || first < 0) return RowJob{nullptr, nullptr};
+    return RowJob{reinterpret_cast<const uint4*>(rows_out + static_cast<size_t>(first) * hidden),
+                  reinterpret_cast<uint4*>(rows_out + static_cast<size_t>(r) * hidden)};
+  };
+  for (int r = *range.begin + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += 2 * warps)
+    run_row_jobs(job_of(r), job_of(r + warps), vecs, lane);
 }
 
 int gather_rows(const OwnerRows& o, int rank, int e_local, int world, int row_capacity, int cap, int top_k,
