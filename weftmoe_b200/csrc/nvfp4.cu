@@ -83,6 +83,54 @@ __global__ void nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ x, int r
   }
 }
 
+// BF16 [rows][cols] -> NVFP4 of the TRANSPOSE: packed codes [cols][rows / 2] with block 16 along the
+// rows, scales in the chunked layout of a [cols][rows] operand (the weight-gradient operands of the
+// NVFP4 backward, reference: src/cuda/blackwell/nvfp4_quantize.cuh:48-51).  A warp serves 64 rows x 64
+// columns: lane l holds columns 2l and 2l+1, so every load instruction of the warp is one 128-byte row
+// segment, and a lane ends up with 64 consecutive codes of each of its two output rows (32 bytes, one
+// sector) plus their four scale bytes (one word of the chunk).  Same values as transposing first and
+// quantising the rows after (the blocks are the same 16 consecutive rows), without the two extra passes.
+__global__ void nvfp4_quantize_cols_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols, float six_s,
+                                           float s, uint8_t* __restrict__ data, uint8_t* __restrict__ sf) {
+  const int lane = threadIdx.x & 31;
+  const int col_blocks = cols / 64, k64 = rows / 64;
+  const long long units = static_cast<long long>(k64) * col_blocks;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long unit = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; unit < units;
+       unit += warps) {
+    const int rb = static_cast<int>(unit / col_blocks), cb = static_cast<int>(unit - static_cast<long long>(rb) * col_blocks);
+    const int r0 = rb * 64, c = cb * 64 + 2 * lane;
+    const unsigned* src = reinterpret_cast<const unsigned*>(x + static_cast<size_t>(r0) * cols + c);
+    const size_t pitch = static_cast<size_t>(cols) / 2;  // words per input row
+    uint2 codes[2][4];
+    unsigned scale_word[2] = {0u, 0u};
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      unsigned w[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) w[i] = src[(16 * g + i) * pitch];
+      float lo[16], hi[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        lo[i] = __uint_as_float(w[i] << 16);
+        hi[i] = __uint_as_float(w[i] & 0xffff0000u);
+      }
+      unsigned char sb;
+      codes[0][g] = nvfp4_encode16(lo, six_s, s, &sb);
+      scale_word[0] |= static_cast<unsigned>(sb) << (8 * g);
+      codes[1][g] = nvfp4_encode16(hi, six_s, s, &sb);
+      scale_word[1] |= static_cast<unsigned>(sb) << (8 * g);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint4* dst = reinterpret_cast<uint4*>(data + static_cast<size_t>(c + h) * (rows / 2) + r0 / 2);
+      dst[0] = make_uint4(codes[h][0].x, codes[h][0].y, codes[h][1].x, codes[h][1].y);
+      dst[1] = make_uint4(codes[h][2].x, codes[h][2].y, codes[h][3].x, codes[h][3].y);
+      *reinterpret_cast<unsigned*>(sf + nvfp4_sf_chunk_offset(c + h, 4 * rb, k64)) = scale_word[h];
+    }
+  }
+}
+
 // Row-major scale bytes [rows][k/16] -> chunked layout (rows beyond `rows` and groups beyond k get 0).
 __global__ void nvfp4_pack_scales_kernel(const unsigned char* __restrict__ sf, int rows, int groups, int k64,
                                          unsigned char* __restrict__ out, int tiles) {
@@ -111,6 +159,22 @@ int nvfp4_quantize_rows(const void* x, int rows, int cols, float layer_scale, vo
                                                   static_cast<float>(6.0 * static_cast<double>(layer_scale)),
                                                   layer_scale, static_cast<uint2*>(data),
                                                   static_cast<unsigned char*>(scales), chunked);
+  WM_CUDA(cudaGetLastError());
+  count_launch();
+  return 0;
+}
+int nvfp4_quantize_cols(const __nv_bfloat16* x, int rows, int cols, float layer_scale, uint8_t* data,
+                        uint8_t* scales, int sms, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return 0;
+  if (rows % 64 || cols % 64) {
+    set_error("nvfp4_quantize_cols: rows and columns must be multiples of 64");
+    return WM_ERR_INVALID;
+  }
+  if (cols % 128)  // the last 128-row tile of the output is half empty: its scale words must read as zero
+    WM_CUDA(cudaMemsetAsync(scales, 0, static_cast<size_t>((cols + 127) / 128) * (rows / 64) * 512, stream));
+  nvfp4_quantize_cols_kernel<<<sms * 8, 256, 0, stream>>>(x, rows, cols,
+                                                          static_cast<float>(6.0 * static_cast<double>(layer_scale)),
+                                                          layer_scale, data, scales);
   WM_CUDA(cudaGetLastError());
   count_launch();
   return 0;

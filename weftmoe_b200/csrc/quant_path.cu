@@ -412,20 +412,6 @@ int fp8_dequantize_rows(DeviceRange rows, const uint8_t* q, const uint32_t* sfa,
   return 0;
 }
 
-// BF16 [rows][cols] -> [cols][rows] (both row-major), 32 x 32 tiles through shared memory.
-__global__ void transpose_bf16_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols,
-                                      __nv_bfloat16* __restrict__ xt) {
-  __shared__ __nv_bfloat16 tile[32][33];
-  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
-  for (int j = threadIdx.y; j < 32; j += blockDim.y)
-    if (r0 + j < rows && c0 + threadIdx.x < cols)
-      tile[j][threadIdx.x] = x[static_cast<size_t>(r0 + j) * cols + c0 + threadIdx.x];
-  __syncthreads();
-  for (int j = threadIdx.y; j < 32; j += blockDim.y)
-    if (c0 + j < cols && r0 + threadIdx.x < rows)
-      xt[static_cast<size_t>(c0 + j) * rows + r0 + threadIdx.x] = tile[threadIdx.x][j];
-}
-
 // Packed E2M1 rows + chunked E4M3 scales -> BF16 rows: value = code * block scale * layer scale.
 __global__ void nvfp4_dequantize_rows_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ sf,
                                              int rows, int cols, float layer_scale,
@@ -458,14 +444,6 @@ __global__ void nvfp4_dequantize_rows_kernel(const uint8_t* __restrict__ data, c
     dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
     dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
   }
-}
-
-int transpose_bf16(const __nv_bfloat16* x, int rows, int cols, __nv_bfloat16* xt, cudaStream_t stream) {
-  if (rows == 0 || cols == 0) return 0;
-  transpose_bf16_kernel<<<dim3((cols + 31) / 32, (rows + 31) / 32), dim3(32, 8), 0, stream>>>(x, rows, cols, xt);
-  WM_CUDA(cudaGetLastError());
-  count_launch();
-  return 0;
 }
 
 int nvfp4_dequantize_rows(const uint8_t* data, const uint8_t* sf_chunks, int rows, int cols, float layer_scale,

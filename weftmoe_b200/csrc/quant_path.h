@@ -24,6 +24,9 @@ int fp8_quantize_rows(const void* x, long long rows, int cols, void* q, float* s
                       cudaStream_t stream);
 int nvfp4_quantize_rows(const void* x, int rows, int cols, float layer_scale, void* data, void* scales,
                         int chunked, cudaStream_t stream);
+// BF16 [rows][cols] -> NVFP4 of the transpose ([cols][rows / 2] codes, block 16 along the rows, chunked scales).
+int nvfp4_quantize_cols(const __nv_bfloat16* x, int rows, int cols, float layer_scale, uint8_t* data,
+                        uint8_t* scales, int sms, cudaStream_t stream);
 int pack_fp8_scales(const float* scales, int rows, int kblocks, int block_rows, void* out,
                     cudaStream_t stream);
 
@@ -45,8 +48,7 @@ int fp8_quantize_cols_chunked(DeviceRange rows, const __nv_bfloat16* x, int cols
 int launch_block_scaled_kgrouped(int kind, const Schedule& s, const void* a, const SfLayout& sfa, const void* b,
                                  const SfLayout& sfb, __nv_bfloat16* out, int m, int n, float alpha,
                                  int* status, int sms, cudaStream_t stream);
-// NVFP4 backward helpers: a plain BF16 transpose, and packed rows + chunked scales back to BF16.
-int transpose_bf16(const __nv_bfloat16* x, int rows, int cols, __nv_bfloat16* xt, cudaStream_t stream);
+// NVFP4 backward helper: packed rows + chunked scales back to BF16.
 int nvfp4_dequantize_rows(const uint8_t* data, const uint8_t* sf_chunks, int rows, int cols, float layer_scale,
                           __nv_bfloat16* out, int sms, cudaStream_t stream);
 int swiglu_quantize(DeviceRange rows, const __nv_bfloat16* ab, const float* prob, int inter, int kind,

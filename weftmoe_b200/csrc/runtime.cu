@@ -73,7 +73,7 @@ struct ScratchLayout {
   size_t status, sorted_slot, sorted_expert, slot_pos, local_offset, dst_rank, dst_row, dst_prow,
       chunk_hist, local_count, expert_total, expert_before, expert_base, expert_pbase, padded_start,
       tile_group, num_tiles, padded_rows, pair_tiles, num_pairs, split, origin, prob, xrows, u, recv, du,
-      dab, abq, sfa_x, sfa_u, primary, wq_a, wq_b, wsf_a, wsf_b, wt, dprob_part, gen, total;
+      dab, abq, sfa_x, sfa_u, primary, wq_a, wq_b, wsf_a, wsf_b, dprob_part, gen, total;
 };
 // Training cache carved out of the caller's tape buffer.
 struct TapeLayout {
@@ -189,10 +189,9 @@ ScratchLayout scratch_layout(const wm_config& c, int row_cap) {
     s.wsf_b = k.take((static_cast<size_t>(c.hidden) / 128) * (row_cap / 128) * 512 + 4 * 512);
   }
   if (c.training && c.reserved == 2) {
-    // NVFP4 weight gradients: a BF16 transpose of one operand at a time, then both operands of the
-    // contraction quantised block-16 along the rows ([features][row_cap / 2] bytes) with their chunks.
+    // NVFP4 weight gradients: both operands of the contraction quantised block-16 along the rows and
+    // stored transposed ([features][row_cap / 2] bytes) with their scale chunks.
     const size_t wide = c.hidden > 2 * c.intermediate ? c.hidden : 2 * c.intermediate;
-    s.wt = k.take(2ull * row_cap * wide);
     s.wq_a = k.take(static_cast<size_t>(row_cap) / 2 * wide);
     s.wq_b = k.take(static_cast<size_t>(row_cap) / 2 * wide);
     s.wsf_a = k.take((wide / 128) * (row_cap / 64) * 512 + 4 * 512);
@@ -1274,7 +1273,6 @@ static int backward_nvfp4(wm_runtime* rt, const void* tape, const void* dy, cons
   uint8_t* qrows = at<uint8_t>(S, rt->sl.abq);       // row-quantised dY, then dAB (<= row_cap * 4I bytes)
   uint8_t* sf_dy = at<uint8_t>(S, rt->sl.sfa_x);     // H / 64 chunks per row tile
   uint8_t* sf_dab = at<uint8_t>(S, rt->sl.sfa_u);    // 2I / 64 chunks per row tile
-  auto* wt = at<__nv_bfloat16>(S, rt->sl.wt);
   uint8_t* qa = at<uint8_t>(S, rt->sl.wq_a);
   uint8_t* qb = at<uint8_t>(S, rt->sl.wq_b);
   uint8_t* sa = at<uint8_t>(S, rt->sl.wsf_a);
@@ -1339,8 +1337,7 @@ static int backward_nvfp4(wm_runtime* rt, const void* tape, const void* dy, cons
   const long long per_tile = static_cast<long long>(R / 64) * chunk;
   const SfLayout la{sa, 0, per_tile, 4 * chunk, chunk}, lb{sb, 0, per_tile, 4 * chunk, chunk};
   auto along_rows = [&](const __nv_bfloat16* rows_in, int cols, float scale, uint8_t* q, uint8_t* sf) -> int {
-    if (int rc = transpose_bf16(rows_in, R, cols, wt, stream)) return rc;
-    return nvfp4_quantize_rows(wt, cols, R, scale, q, sf, 1, stream);
+    return nvfp4_quantize_cols(rows_in, R, cols, scale, q, sf, rt->sms, stream);
   };
   if (int rc = nvfp4_dequantize_rows(xq, sf_x, R, H, w->x_scale, x_bf16, rt->sms, stream)) return rc;
   if (int rc = along_rows(dab, 2 * I, w->dab_scale, qa, sa)) return rc;
