@@ -62,7 +62,8 @@ namespace {
 // One lane per 16-element block; a warp covers 512 consecutive columns of one row.
 __global__ void nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols, float six_s,
                                       float s, uint2* __restrict__ data, unsigned char* __restrict__ sf,
-                                      int chunked) {
+                                      int chunked, const int* __restrict__ live_rows) {
+  if (live_rows != nullptr) rows = min(rows, *live_rows);  // rows behind the live ones are never read
   const int groups = cols / 16;
   const long long total = static_cast<long long>(rows) * groups;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
@@ -83,51 +84,110 @@ __global__ void nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ x, int r
   }
 }
 
-// BF16 [rows][cols] -> NVFP4 of the TRANSPOSE: packed codes [cols][rows / 2] with block 16 along the
+// [rows][cols] values -> NVFP4 of the TRANSPOSE: packed codes [cols][rows / 2] with block 16 along the
 // rows, scales in the chunked layout of a [cols][rows] operand (the weight-gradient operands of the
 // NVFP4 backward, reference: src/cuda/blackwell/nvfp4_quantize.cuh:48-51).  A warp serves 64 rows x 64
-// columns: lane l holds columns 2l and 2l+1, so every load instruction of the warp is one 128-byte row
-// segment, and a lane ends up with 64 consecutive codes of each of its two output rows (32 bytes, one
-// sector) plus their four scale bytes (one word of the chunk).  Same values as transposing first and
-// quantising the rows after (the blocks are the same 16 consecutive rows), without the two extra passes.
+// columns: lane l holds columns c = 2l and 2l+1 and ends up with 64 consecutive codes of each of its two
+// output rows (32 bytes, one sector) plus their four scale bytes (one word of the chunk).  Same values as
+// transposing first and quantising the rows after (the blocks are the same 16 consecutive rows), without
+// the two extra passes.  `word_at(i)` returns the BF16 pair (columns c, c + 1) of row r0 + i.
+template <class WordAt>
+__device__ __forceinline__ void nvfp4_encode_columns(WordAt word_at, int r0, int c, int rows, float six_s, float s,
+                                                     uint8_t* __restrict__ data, uint8_t* __restrict__ sf) {
+  uint2 codes[2][4];
+  unsigned scale_word[2] = {0u, 0u};
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float lo[16], hi[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const unsigned w = word_at(16 * g + i);
+      lo[i] = __uint_as_float(w << 16);
+      hi[i] = __uint_as_float(w & 0xffff0000u);
+    }
+    unsigned char sb;
+    codes[0][g] = nvfp4_encode16(lo, six_s, s, &sb);
+    scale_word[0] |= static_cast<unsigned>(sb) << (8 * g);
+    codes[1][g] = nvfp4_encode16(hi, six_s, s, &sb);
+    scale_word[1] |= static_cast<unsigned>(sb) << (8 * g);
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint4* dst = reinterpret_cast<uint4*>(data + static_cast<size_t>(c + h) * (rows / 2) + r0 / 2);
+    dst[0] = make_uint4(codes[h][0].x, codes[h][0].y, codes[h][1].x, codes[h][1].y);
+    dst[1] = make_uint4(codes[h][2].x, codes[h][2].y, codes[h][3].x, codes[h][3].y);
+    *reinterpret_cast<unsigned*>(sf + nvfp4_sf_chunk_offset(c + h, r0 / 16, rows / 64)) = scale_word[h];
+  }
+}
+
+// Source = BF16 [rows][cols]: every load instruction of the warp is one 128-byte row segment.
 __global__ void nvfp4_quantize_cols_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols, float six_s,
-                                           float s, uint8_t* __restrict__ data, uint8_t* __restrict__ sf) {
+                                           float s, uint8_t* __restrict__ data, uint8_t* __restrict__ sf,
+                                           const int* __restrict__ live_rows) {
   const int lane = threadIdx.x & 31;
-  const int col_blocks = cols / 64, k64 = rows / 64;
-  const long long units = static_cast<long long>(k64) * col_blocks;
+  const int col_blocks = cols / 64;
+  // rows behind the live ones (a multiple of 64) are never read by the contraction: left out
+  const long long units = static_cast<long long>((live_rows ? min(rows, *live_rows) : rows) / 64) * col_blocks;
   const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const size_t pitch = static_cast<size_t>(cols) / 2;  // words per input row
   for (long long unit = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; unit < units;
        unit += warps) {
     const int rb = static_cast<int>(unit / col_blocks), cb = static_cast<int>(unit - static_cast<long long>(rb) * col_blocks);
     const int r0 = rb * 64, c = cb * 64 + 2 * lane;
     const unsigned* src = reinterpret_cast<const unsigned*>(x + static_cast<size_t>(r0) * cols + c);
-    const size_t pitch = static_cast<size_t>(cols) / 2;  // words per input row
-    uint2 codes[2][4];
-    unsigned scale_word[2] = {0u, 0u};
+    nvfp4_encode_columns([&](int i) { return src[i * pitch]; }, r0, c, rows, six_s, s, data, sf);
+  }
+}
+
+// Source = rows stored as NVFP4 (packed E2M1 [rows][cols / 2] + chunked E4M3 scales, layer scale s_in): the
+// values a dequantisation to BF16 rows would hold (code * block scale * s_in, rounded to BF16), without
+// that copy.  Lane l first decodes rows l and 32 + l of the warp's 64 x 64 block (32 bytes of codes and
+// one scale word each) into the warp's shared-memory tile (33-word row pitch: conflict-free both ways),
+// then the lanes read the tile column-wise as above.
+constexpr int kRequantWarps = 4;
+__global__ void __launch_bounds__(32 * kRequantWarps)
+nvfp4_requantize_cols_kernel(const uint8_t* __restrict__ xq, const uint8_t* __restrict__ xsf, float s_in, int rows,
+                             int cols, float six_s, float s, uint8_t* __restrict__ data,
+                             uint8_t* __restrict__ sf, const int* __restrict__ live_rows) {
+  __shared__ unsigned tiles[kRequantWarps][64 * 33];
+  __shared__ float e2m1[16];  // value of each code: sign bit 3, magnitudes 0, 0.5, 1, 1.5, 2, 3, 4, 6
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x < 16) {
+    const unsigned mag = threadIdx.x & 7u;
+    const float m = mag < 2 ? 0.5f * mag : (mag & 1 ? 1.5f : 1.0f) * static_cast<float>(1 << ((mag >> 1) - 1));
+    e2m1[threadIdx.x] = threadIdx.x & 8u ? -m : m;
+  }
+  __syncthreads();
+  unsigned* tile = tiles[threadIdx.x >> 5];
+  const int col_blocks = cols / 64;
+  const long long units = static_cast<long long>((live_rows ? min(rows, *live_rows) : rows) / 64) * col_blocks;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long unit = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; unit < units;
+       unit += warps) {
+    const int rb = static_cast<int>(unit / col_blocks), cb = static_cast<int>(unit - static_cast<long long>(rb) * col_blocks);
+    const int r0 = rb * 64, c0 = cb * 64;
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      unsigned w[16];
+    for (int half = 0; half < 2; ++half) {
+      const int row = r0 + 32 * half + lane;
+      const uint4* src = reinterpret_cast<const uint4*>(xq + static_cast<size_t>(row) * (cols / 2) + c0 / 2);
+      const uint4 d0 = src[0], d1 = src[1];
+      const unsigned scales = *reinterpret_cast<const unsigned*>(xsf + nvfp4_sf_chunk_offset(row, c0 / 16, cols / 64));
+      const unsigned words[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+      unsigned* out = tile + (32 * half + lane) * 33;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) w[i] = src[(16 * g + i) * pitch];
-      float lo[16], hi[16];
+      for (int g = 0; g < 4; ++g) {  // 16 columns = 8 bytes = words 2g, 2g+1
+        const unsigned char sb = static_cast<unsigned char>(scales >> (8 * g));
+        const float scale = __half2float(__half(__nv_cvt_fp8_to_halfraw(sb, __NV_E4M3))) * s_in;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        lo[i] = __uint_as_float(w[i] << 16);
-        hi[i] = __uint_as_float(w[i] & 0xffff0000u);
+        for (int j = 0; j < 8; ++j) {
+          const unsigned byte = (words[2 * g + (j >> 2)] >> (8 * (j & 3))) & 0xffu;
+          out[8 * g + j] = pack_bf16x2(e2m1[byte & 0xfu] * scale, e2m1[byte >> 4] * scale);
+        }
       }
-      unsigned char sb;
-      codes[0][g] = nvfp4_encode16(lo, six_s, s, &sb);
-      scale_word[0] |= static_cast<unsigned>(sb) << (8 * g);
-      codes[1][g] = nvfp4_encode16(hi, six_s, s, &sb);
-      scale_word[1] |= static_cast<unsigned>(sb) << (8 * g);
     }
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      uint4* dst = reinterpret_cast<uint4*>(data + static_cast<size_t>(c + h) * (rows / 2) + r0 / 2);
-      dst[0] = make_uint4(codes[h][0].x, codes[h][0].y, codes[h][1].x, codes[h][1].y);
-      dst[1] = make_uint4(codes[h][2].x, codes[h][2].y, codes[h][3].x, codes[h][3].y);
-      *reinterpret_cast<unsigned*>(sf + nvfp4_sf_chunk_offset(c + h, 4 * rb, k64)) = scale_word[h];
-    }
+    __syncwarp();
+    nvfp4_encode_columns([&](int i) { return tile[i * 33 + lane]; }, r0, c0 + 2 * lane, rows, six_s, s, data, sf);
+    __syncwarp();
   }
 }
 
@@ -147,7 +207,7 @@ __global__ void nvfp4_pack_scales_kernel(const unsigned char* __restrict__ sf, i
 
 namespace wm {
 int nvfp4_quantize_rows(const void* x, int rows, int cols, float layer_scale, void* data, void* scales,
-                        int chunked, cudaStream_t stream) {
+                        int chunked, cudaStream_t stream, const int* live_rows) {
   const long long total = static_cast<long long>(rows) * (cols / 16);
   if (total == 0) return 0;
   if (chunked) {
@@ -158,23 +218,38 @@ int nvfp4_quantize_rows(const void* x, int rows, int cols, float layer_scale, vo
   nvfp4_quantize_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, cols,
                                                   static_cast<float>(6.0 * static_cast<double>(layer_scale)),
                                                   layer_scale, static_cast<uint2*>(data),
-                                                  static_cast<unsigned char*>(scales), chunked);
+                                                  static_cast<unsigned char*>(scales), chunked, live_rows);
   WM_CUDA(cudaGetLastError());
   count_launch();
   return 0;
 }
-int nvfp4_quantize_cols(const __nv_bfloat16* x, int rows, int cols, float layer_scale, uint8_t* data,
-                        uint8_t* scales, int sms, cudaStream_t stream) {
-  if (rows == 0 || cols == 0) return 0;
+static int check_cols_shape(int rows, int cols, uint8_t* scales, cudaStream_t stream) {
   if (rows % 64 || cols % 64) {
     set_error("nvfp4_quantize_cols: rows and columns must be multiples of 64");
     return WM_ERR_INVALID;
   }
   if (cols % 128)  // the last 128-row tile of the output is half empty: its scale words must read as zero
     WM_CUDA(cudaMemsetAsync(scales, 0, static_cast<size_t>((cols + 127) / 128) * (rows / 64) * 512, stream));
-  nvfp4_quantize_cols_kernel<<<sms * 8, 256, 0, stream>>>(x, rows, cols,
-                                                          static_cast<float>(6.0 * static_cast<double>(layer_scale)),
-                                                          layer_scale, data, scales);
+  return 0;
+}
+int nvfp4_quantize_cols(const __nv_bfloat16* x, int rows, int cols, float layer_scale, uint8_t* data,
+                        uint8_t* scales, const int* live_rows, int sms, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return 0;
+  if (int rc = check_cols_shape(rows, cols, scales, stream)) return rc;
+  nvfp4_quantize_cols_kernel<<<sms * 8, 256, 0, stream>>>(
+      x, rows, cols, static_cast<float>(6.0 * static_cast<double>(layer_scale)), layer_scale, data, scales,
+      live_rows);
+  WM_CUDA(cudaGetLastError());
+  count_launch();
+  return 0;
+}
+int nvfp4_requantize_cols(const uint8_t* xq, const uint8_t* sf_chunks, int rows, int cols, float layer_scale,
+                          uint8_t* data, uint8_t* scales, const int* live_rows, int sms, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return 0;
+  if (int rc = check_cols_shape(rows, cols, scales, stream)) return rc;
+  nvfp4_requantize_cols_kernel<<<sms * 6, 32 * kRequantWarps, 0, stream>>>(
+      xq, sf_chunks, layer_scale, rows, cols, static_cast<float>(6.0 * static_cast<double>(layer_scale)), layer_scale,
+      data, scales, live_rows);
   WM_CUDA(cudaGetLastError());
   count_launch();
   return 0;
@@ -195,7 +270,7 @@ extern "C" int wm_nvfp4_quantize(const void* x, int32_t rows, int32_t cols, floa
     return WM_ERR_INVALID;
   }
   return nvfp4_quantize_rows(x, rows, cols, layer_scale, data, scales, chunked,
-                             static_cast<cudaStream_t>(stream_));
+                             static_cast<cudaStream_t>(stream_), nullptr);
 }
 
 // Diagnostic: out[m,n] = alpha * (A[m,k] * B[n,k]^T) with NVFP4 operands; scales row-major bytes.

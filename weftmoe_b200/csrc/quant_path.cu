@@ -412,49 +412,6 @@ int fp8_dequantize_rows(DeviceRange rows, const uint8_t* q, const uint32_t* sfa,
   return 0;
 }
 
-// Packed E2M1 rows + chunked E4M3 scales -> BF16 rows: value = code * block scale * layer scale.
-__global__ void nvfp4_dequantize_rows_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ sf,
-                                             int rows, int cols, float layer_scale,
-                                             __nv_bfloat16* __restrict__ out) {
-  const int groups = cols / 16, k64 = cols / 64;
-  const long long total = static_cast<long long>(rows) * groups;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int r = static_cast<int>(i / groups), g = static_cast<int>(i - static_cast<long long>(r) * groups);
-    const uint2 packed = reinterpret_cast<const uint2*>(data)[i];
-    const uint8_t sb = sf[((static_cast<size_t>(r >> 7) * k64 + (g >> 2)) * 128 + chunk_word(r)) * 4 + (g & 3)];
-    const float scale = __half2float(__half(__nv_cvt_fp8_to_halfraw(sb, __NV_E4M3))) * layer_scale;
-    const unsigned words[2] = {packed.x, packed.y};
-    unsigned o[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const unsigned byte = (words[j >> 2] >> (8 * (j & 3))) & 0xffu;
-      float v[2];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const unsigned code = (byte >> (4 * h)) & 0xfu;
-        const unsigned mag = code & 7u;
-        // E2M1 magnitudes: 0, 0.5, 1, 1.5, 2, 3, 4, 6
-        const float m = mag < 2 ? 0.5f * mag : (mag & 1 ? 1.5f : 1.0f) * static_cast<float>(1 << ((mag >> 1) - 1));
-        v[h] = (code & 8u ? -m : m) * scale;
-      }
-      o[j] = pack_bf16x2(v[0], v[1]);
-    }
-    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * cols + g * 16);
-    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-  }
-}
-
-int nvfp4_dequantize_rows(const uint8_t* data, const uint8_t* sf_chunks, int rows, int cols, float layer_scale,
-                          __nv_bfloat16* out, int sms, cudaStream_t stream) {
-  if (rows == 0) return 0;
-  nvfp4_dequantize_rows_kernel<<<sms * 8, 256, 0, stream>>>(data, sf_chunks, rows, cols, layer_scale, out);
-  WM_CUDA(cudaGetLastError());
-  count_launch();
-  return 0;
-}
-
 int fp8_quantize_cols_chunked(DeviceRange rows, const __nv_bfloat16* x, int cols, int row_capacity,
                               uint8_t* qt, uint32_t* sf_out, int sms, cudaStream_t stream) {
   fp8_quantize_cols_chunked_kernel<<<sms * 8, 256, 0, stream>>>(rows, x, cols, row_capacity, qt, sf_out);

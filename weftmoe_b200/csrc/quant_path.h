@@ -22,11 +22,17 @@ struct PeerBytes { const uint8_t* p[kMaxWorld]; };
 // fp8.cu / nvfp4.cu / fp8_gemm.cu
 int fp8_quantize_rows(const void* x, long long rows, int cols, void* q, float* scales, int sms,
                       cudaStream_t stream);
+// `live_rows` (optional device scalar): only rows below it are quantised (the owner's padded rows; what lies
+// behind them in a row buffer is never read by a contraction).
 int nvfp4_quantize_rows(const void* x, int rows, int cols, float layer_scale, void* data, void* scales,
-                        int chunked, cudaStream_t stream);
+                        int chunked, cudaStream_t stream, const int* live_rows = nullptr);
 // BF16 [rows][cols] -> NVFP4 of the transpose ([cols][rows / 2] codes, block 16 along the rows, chunked scales).
 int nvfp4_quantize_cols(const __nv_bfloat16* x, int rows, int cols, float layer_scale, uint8_t* data,
-                        uint8_t* scales, int sms, cudaStream_t stream);
+                        uint8_t* scales, const int* live_rows, int sms, cudaStream_t stream);
+// The same for rows that are stored as NVFP4 (packed codes + chunked scales along the columns, the saved X
+// of the training cache): re-quantised along the rows without a BF16 copy in between.
+int nvfp4_requantize_cols(const uint8_t* xq, const uint8_t* sf_chunks, int rows, int cols, float layer_scale,
+                          uint8_t* data, uint8_t* scales, const int* live_rows, int sms, cudaStream_t stream);
 int pack_fp8_scales(const float* scales, int rows, int kblocks, int block_rows, void* out,
                     cudaStream_t stream);
 
@@ -48,9 +54,6 @@ int fp8_quantize_cols_chunked(DeviceRange rows, const __nv_bfloat16* x, int cols
 int launch_block_scaled_kgrouped(int kind, const Schedule& s, const void* a, const SfLayout& sfa, const void* b,
                                  const SfLayout& sfb, __nv_bfloat16* out, int m, int n, float alpha,
                                  int* status, int sms, cudaStream_t stream);
-// NVFP4 backward helper: packed rows + chunked scales back to BF16.
-int nvfp4_dequantize_rows(const uint8_t* data, const uint8_t* sf_chunks, int rows, int cols, float layer_scale,
-                          __nv_bfloat16* out, int sms, cudaStream_t stream);
 int swiglu_quantize(DeviceRange rows, const __nv_bfloat16* ab, const float* prob, int inter, int kind,
                     float layer_scale, uint8_t* uq, uint32_t* sfa_out, int sms, cudaStream_t stream);
 // out[rows, n] = alpha * A[rows, k] * B[e][n, k]^T with quantised operands; `push` != nullptr sends the

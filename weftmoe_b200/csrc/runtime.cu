@@ -1265,7 +1265,6 @@ static int backward_nvfp4(wm_runtime* rt, const void* tape, const void* dy, cons
   const uint8_t* xq = tp(rt->tl.xrows);
   const uint8_t* sf_x = tp(rt->tl.xrows) + align_up(static_cast<size_t>(rt->row_cap) * H);
   const auto* ab = reinterpret_cast<const __nv_bfloat16*>(tp(rt->tl.ab));
-  auto* x_bf16 = at<__nv_bfloat16>(S, rt->sl.xrows);
   auto* recv = at<__nv_bfloat16>(S, rt->sl.recv);
   auto* u = at<__nv_bfloat16>(S, rt->sl.u);
   auto* du = at<__nv_bfloat16>(S, rt->sl.du);
@@ -1312,7 +1311,7 @@ static int backward_nvfp4(wm_runtime* rt, const void* tape, const void* dy, cons
   const long long chunk = 512;
   const int kh = H / 64, ki2 = 2 * I / 64;
   // 2. dU = q(dY) W2: dY rows quantised along H against W2^T [I][H].
-  if (int rc = nvfp4_quantize_rows(recv, R, H, w->dy_scale, qrows, sf_dy, 1, stream)) return rc;
+  if (int rc = nvfp4_quantize_rows(recv, R, H, w->dy_scale, qrows, sf_dy, 1, stream, all_rows.end)) return rc;
   const SfLayout sfa_dy{sf_dy, 0, kh * chunk, 4 * chunk, chunk};
   const SfLayout sfb_w2t{static_cast<const uint8_t*>(w->w2_sf), (1ll * I / 128) * kh * chunk, kh * chunk, 4 * chunk,
                          chunk};
@@ -1324,7 +1323,7 @@ static int backward_nvfp4(wm_runtime* rt, const void* tape, const void* dy, cons
                                rt->sms, stream))
     return rc;
   // 4. dX = q(dAB) W1 -> sources' mailboxes: dAB rows quantised along 2I against W1^T [H][2I].
-  if (int rc = nvfp4_quantize_rows(dab, R, 2 * I, w->dab_scale, qrows, sf_dab, 1, stream)) return rc;
+  if (int rc = nvfp4_quantize_rows(dab, R, 2 * I, w->dab_scale, qrows, sf_dab, 1, stream, all_rows.end)) return rc;
   const SfLayout sfa_dab{sf_dab, 0, ki2 * chunk, 4 * chunk, chunk};
   const SfLayout sfb_w1t{static_cast<const uint8_t*>(w->w1_sf), (1ll * H / 128) * ki2 * chunk, ki2 * chunk,
                          4 * chunk, chunk};
@@ -1337,11 +1336,10 @@ static int backward_nvfp4(wm_runtime* rt, const void* tape, const void* dy, cons
   const long long per_tile = static_cast<long long>(R / 64) * chunk;
   const SfLayout la{sa, 0, per_tile, 4 * chunk, chunk}, lb{sb, 0, per_tile, 4 * chunk, chunk};
   auto along_rows = [&](const __nv_bfloat16* rows_in, int cols, float scale, uint8_t* q, uint8_t* sf) -> int {
-    return nvfp4_quantize_cols(rows_in, R, cols, scale, q, sf, rt->sms, stream);
+    return nvfp4_quantize_cols(rows_in, R, cols, scale, q, sf, all_rows.end, rt->sms, stream);
   };
-  if (int rc = nvfp4_dequantize_rows(xq, sf_x, R, H, w->x_scale, x_bf16, rt->sms, stream)) return rc;
   if (int rc = along_rows(dab, 2 * I, w->dab_scale, qa, sa)) return rc;
-  if (int rc = along_rows(x_bf16, H, w->x_scale, qb, sb)) return rc;
+  if (int rc = nvfp4_requantize_cols(xq, sf_x, R, H, w->x_scale, qb, sb, all_rows.end, rt->sms, stream)) return rc;
   if (int rc = launch_block_scaled_kgrouped(kKindNvfp4, sched, qa, la, qb, lb, static_cast<__nv_bfloat16*>(dw1),
                                             2 * I, H, w->dab_scale * w->x_scale, status, rt->sms, stream))
     return rc;

@@ -209,15 +209,25 @@ __global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ mailbox,
     float acc[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
-    for (int j = 0; j < top_k; ++j) {
-      if (sorted_expert[t * top_k + j] < 0) continue;
-      const uint4 v = *reinterpret_cast<const uint4*>(
-          mailbox + (static_cast<size_t>(j) * cap + t) * hidden + c * 8);
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    // Four contributions are loaded at a time (their latencies overlap) and then added one after the
+    // other; a slot without a contribution adds +0.0, which leaves every bit of the sum as it was.
+    for (int j0 = 0; j0 < top_k; j0 += 4) {
+      uint4 v[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        acc[2 * k] += __uint_as_float(w[k] << 16);
-        acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+      for (int i = 0; i < 4; ++i) {
+        const int j = j0 + i;
+        const bool live = j < top_k && sorted_expert[t * top_k + j] >= 0;
+        v[i] = live ? *reinterpret_cast<const uint4*>(mailbox + (static_cast<size_t>(j) * cap + t) * hidden + c * 8)
+                    : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          acc[2 * k] += __uint_as_float(w[k] << 16);
+          acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+        }
       }
     }
     uint4 r;
