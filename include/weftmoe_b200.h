@@ -121,6 +121,13 @@ typedef struct wm_quant_weights {
    * the bits of the online path (reference: FP8Tensor sources, tests/torchrun_fp8.py:133-157). */
   const void* source_q;
   const float* source_scales;
+  /* Blockwise FP8 only, optional (NULL = every block scale of that weight is a power of two): the FP32
+   * 128 x 128 block scales of w1 / w2 as given, [E_local * rows / 128][K / 128], for weights whose scales carry
+   * mantissas (imported checkpoints, reference: tests/torchrun_fp8.py:235-255).  The bytes are used as they
+   * are: the MMA applies each scale's exponent (the packed chunks) and the kernel promotes every K128 block
+   * in FP32 by the mantissas (reference: src/cuda/fp8/gemm.cuh:68-70). */
+  const float* w1_scales;
+  const float* w2_scales;
 } wm_quant_weights;
 WM_API int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t* routes, const float* gates,
                                 const wm_quant_weights* weights, int32_t tokens, void* y, void* tape,

@@ -138,3 +138,31 @@ def test_gemm(m, n, k, b_block_rows):
     fp8_gemm(aq, bq, dtype=torch.float32, out=out, accumulate=True)
     assert global_diff(out, expected + 0.5) < 1e-6
     assert torch.equal(fp8_gemm(aq, bq), actual.bfloat16())
+
+
+@pytest.mark.parametrize("m,n,k", [(65, 137, 259), (128, 256, 4096), (300, 640, 1024)])
+@pytest.mark.parametrize("a_block_rows", [1, 128])
+def test_gemm_with_scales_that_are_not_powers_of_two(m, n, k, a_block_rows):
+    """Scales with mantissas (imported checkpoints: the reference multiplies them by 1.125 / 0.875,
+    tests/torchrun_fp8.py:235-255) are neither rounded nor re-quantised: the product equals the dequantised
+    FP64 product of the same bytes and the scaled scales, and differs from the power-of-two result."""
+    from weftmoe_b200.fp8 import fp8_gemm
+    torch.manual_seed(4321)
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    aq, bq = quantize_fp8(a, block_rows=a_block_rows), quantize_fp8(b, block_rows=128)
+    # a different mantissa per block, so that a wrong (row, K block) index shows
+    fa = 1.0 + torch.rand_like(aq.scales) * 0.9
+    fb = 1.0 + torch.rand_like(bq.scales) * 0.9
+    aq2 = FP8Tensor(aq.data, (aq.scales * fa).contiguous(), tuple(aq.shape), a_block_rows)
+    bq2 = FP8Tensor(bq.data, (bq.scales * fb).contiguous(), tuple(bq.shape), 128)
+    for left, right in ((aq, bq2), (aq2, bq2), (aq2, bq)):
+        expected = left.dequantize().double() @ right.dequantize().double().T
+        actual = fp8_gemm(left, right, dtype=torch.float32)
+        assert global_diff(actual, expected) < 1e-6
+        out = torch.full((m, n), 0.5, device="cuda", dtype=torch.float32)
+        fp8_gemm(left, right, dtype=torch.float32, out=out, accumulate=True)
+        assert global_diff(out, expected + 0.5) < 1e-6
+    assert global_diff(fp8_gemm(aq, bq2, dtype=torch.float32), fp8_gemm(aq, bq, dtype=torch.float32)) > 1e-3
+    with pytest.raises(ValueError, match="128 x 128"):
+        fp8_gemm(aq, FP8Tensor(quantize_fp8(b).data, quantize_fp8(b).scales * 1.125, tuple(b.shape), 1))

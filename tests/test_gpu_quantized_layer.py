@@ -168,29 +168,42 @@ def test_fp8_prequantised_sources_reproduce_the_online_bits():
     bf16.close()
 
 
-def test_fp8_imported_weights_keep_their_bits_and_non_power_of_two_scales_are_refused():
-    """Imported (already quantised) weights are used as they are: scaling their block scales by a power of two
-    scales the layer's output by exactly that factor pair.  Block scales with a mantissa (the reference imports
-    them with x1.125 / x0.875, tests/torchrun_fp8.py:235-255) are refused with a message instead of being
-    rounded or quantised again: the scaling here happens inside the MMA as UE8M0."""
+def test_fp8_imported_weights_keep_their_bits_also_with_scales_that_are_not_powers_of_two():
+    """Imported (already quantised) weights are used as they are, never rounded or quantised again
+    (reference: tests/torchrun_fp8.py:235-255, which imports with scales x1.125 / x0.875 and runs forward and
+    backward).  Power-of-two factors stay on the plain block-scaled kernel; scales with mantissas take the
+    kernel that promotes every K128 block in FP32.  Both are held to the layer on the DEQUANTISED weights."""
     from weftmoe_b200.fp8 import FP8Tensor
     cfg = dict(experts=8, top_k=2, hidden=512, intermediate=256, tokens=96)
     d, g = inputs(cfg, 51, 1.0, 0.02)
-    rt = runtime(cfg, "fp8")
-    base = prepare_fp8_weights(g["w1"], g["w2"], training=False)
-    y = rt.inference_fp8(0, g["x"], g["routes"], g["gates"], base)
+    rt = TensorRuntime(group=SingleRankGroup(), experts=cfg["experts"], top_k=cfg["top_k"], hidden=cfg["hidden"],
+                       intermediate=cfg["intermediate"], max_tokens=cfg["tokens"],
+                       max_rows=cfg["tokens"] * cfg["top_k"], training=True, precision="fp8", max_saved=2)
+    base = prepare_fp8_weights(g["w1"], g["w2"], training=True)
+    assert not base.scale_mantissas
+    y = rt.forward_fp8(g["x"], g["routes"], g["gates"], base, retain_backward_state=False).output
     scaled = lambda q, f: FP8Tensor(q.data, q.scales * f, tuple(q.shape), 128)
-    imported = prepare_fp8_weights(scaled(base.w1, 2.0), scaled(base.w2, 0.5), training=True)
-    assert torch.equal(imported.w1.data.view(torch.uint8), base.w1.data.view(torch.uint8))     # bytes untouched
-    assert imported.w1_t is not None and torch.equal(imported.w1.scales, base.w1.scales * 2.0)
-    rt.invalidate_inference_layer(0)
-    y2 = rt.inference_fp8(0, g["x"], g["routes"], g["gates"], imported)
-    # silu(2a) * 2b * 0.5 is not 2 * 0.5 * silu(a) * b: compare against the oracle on the dequantised weights
-    ref = O.quantized_layer(d["x"], d["routes"], d["gates"], imported.w1.dequantize().cpu().bfloat16(),
-                            imported.w2.dequantize().cpu().bfloat16(), kind="fp8")
-    assert rel_l2(y2, ref) < 2e-3 and not torch.equal(y2, y)
-    with pytest.raises(ValueError, match="powers of two"):
-        prepare_fp8_weights(scaled(base.w1, 1.125), scaled(base.w2, 0.875), training=False)
+    for f1, f2, mantissas in ((2.0, 0.5, False), (1.125, 0.875, True)):
+        imported = prepare_fp8_weights(scaled(base.w1, f1), scaled(base.w2, f2), training=True)
+        assert imported.scale_mantissas == mantissas
+        assert torch.equal(imported.w1.data.view(torch.uint8), base.w1.data.view(torch.uint8))     # bytes untouched
+        assert torch.equal(imported.w1.scales, base.w1.scales * f1)                                 # scales as given
+        assert imported.w1_t is not None and torch.equal(imported.w2_t.scales, base.w2_t.scales * f2)
+        w1, w2 = imported.w1.dequantize().cpu().bfloat16(), imported.w2.dequantize().cpu().bfloat16()
+        ref = O.moe_layer(d["x"], d["routes"], d["gates"], w1, w2, d["dy"], precision="bf16")
+        tape = rt.forward_fp8(g["x"], g["routes"], g["gates"], imported, weight_grad_dtype=torch.bfloat16)
+        y2, dx, dg, dw1, dw2 = (tape.output, *rt.backward(tape, g["dy"]))
+        assert not torch.equal(y2, y)
+        assert global_diff(y2, ref[0]) < 5e-3 and global_diff(dx, ref[1]) < 5e-3, (f1, global_diff(y2, ref[0]))
+        assert torch.isfinite(dg).all() and rel_l2(dg, ref[2]) < 0.1
+        live = [e for e in range(cfg["experts"]) if (d["routes"] == e).any()]
+        for e in live:
+            assert global_diff(dw1[e], ref[3][e]) < 5e-3 and global_diff(dw2[e], ref[4][e]) < 5e-3
+        # inference entry point: same bits as the training forward
+        rt_inf = runtime(cfg, "fp8")
+        assert torch.equal(rt_inf.inference_fp8(0, g["x"], g["routes"], g["gates"], imported).view(torch.int16),
+                           y2.view(torch.int16))
+        rt_inf.close()
     rt.close()
 
 

@@ -30,7 +30,8 @@ class WmQuantWeights(Structure):
     _fields_ = [("w1", c_void_p), ("w1_sf", c_void_p), ("w2", c_void_p), ("w2_sf", c_void_p),
                 ("x_scale", c_float), ("w1_scale", c_float), ("u_scale", c_float), ("w2_scale", c_float),
                 ("dy_scale", c_float), ("dab_scale", c_float),
-                ("source_q", c_void_p), ("source_scales", c_void_p)]
+                ("source_q", c_void_p), ("source_scales", c_void_p),
+                ("w1_scales", c_void_p), ("w2_scales", c_void_p)]
 
 
 class WmRouteOut(Structure):

@@ -34,6 +34,15 @@ __global__ void pack_fp8_scales_kernel(const float* __restrict__ scales, int row
   }
 }
 
+// flag |= 1 when any of the n scales has a non-empty mantissa field (is not a power of two).
+__global__ void scales_have_mantissa_kernel(const float* __restrict__ scales, long long n, int* __restrict__ flag) {
+  bool any = false;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    any |= (__float_as_uint(scales[i]) & 0x007fffffu) != 0;
+  if (any) atomicOr(flag, 1);
+}
+
 }  // namespace
 
 namespace wm {
@@ -93,6 +102,25 @@ extern "C" int wm_fp8_gemm(const void* aq, const float* as, const void* bq, cons
   int rc = 0;
   cudaError_t e = cudaMemcpyAsync(sched, host.data(), sched_bytes, cudaMemcpyHostToDevice, stream);
   if (e != cudaSuccess) rc = WM_ERR_CUDA;
+  // Scales with mantissas (imported checkpoints) take the promotion form of the kernel; words 4 and 5 of
+  // the schedule block are free and hold the two findings.
+  const int a_scale_rows = (m + a_block_rows - 1) / a_block_rows, b_scale_rows = (n + b_block_rows - 1) / b_block_rows;
+  int mantissa[2] = {0, 0};
+  if (!rc) {
+    scales_have_mantissa_kernel<<<64, 256, 0, stream>>>(as, static_cast<long long>(a_scale_rows) * kblocks, sched + 4);
+    scales_have_mantissa_kernel<<<64, 256, 0, stream>>>(bs, static_cast<long long>(b_scale_rows) * kblocks, sched + 5);
+    count_launch(2);
+    if (cudaGetLastError() != cudaSuccess ||
+        cudaMemcpyAsync(mantissa, sched + 4, sizeof(mantissa), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+        cudaStreamSynchronize(stream) != cudaSuccess)
+      rc = WM_ERR_CUDA;
+  }
+  const bool promote = mantissa[0] || mantissa[1];
+  if (!rc && promote && b_block_rows != 128) {
+    cudaFree(tmp);
+    set_error("wm_fp8_gemm: scales that are not powers of two need 128 x 128 blocks on the second operand");
+    return WM_ERR_INVALID;
+  }
   if (!rc) rc = pack_fp8_scales(as, m, kblocks, a_block_rows, sfa, stream);
   if (!rc) rc = pack_fp8_scales(bs, n, kblocks, b_block_rows, sfb, stream);
   CUtensorMap ta, tb;
@@ -113,8 +141,13 @@ extern "C" int wm_fp8_gemm(const void* aq, const float* as, const void* bq, cons
     args.base.status = sched + 7;
     args.sfa = SfLayout{sfa, 0, 512ll * kblocks, 512, 512};
     args.sfb = SfLayout{sfb, 0, 512ll * kblocks, 512, 512};
+    args.a_scales = as;
+    args.a_block_rows = a_block_rows;
+    args.a_scale_rows = a_scale_rows;
+    args.b_scales = bs;
     EpilogueBounded epi{out, m, n, n, out_is_f32, accumulate, 1.0f};
-    rc = launch_bs<kKindFp8>(ta, tb, args, epi, sms, stream);
+    rc = promote ? launch_bs<kKindFp8, false, true>(ta, tb, args, epi, sms, stream)
+                 : launch_bs<kKindFp8>(ta, tb, args, epi, sms, stream);
   }
   int status = 0;
   if (!rc && cudaMemcpyAsync(&status, sched + 7, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess)

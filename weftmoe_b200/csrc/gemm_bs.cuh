@@ -10,6 +10,12 @@
 //   kind NVFP4: packed E2M1 operands, `kind::mxf4nvf4.block_scale.scale_vec::4X`, one UE4M3 scale per
 //               16 elements (reference: src/cuda/blackwell/fused/ptx/tcgen05.cuh:89-108).
 //
+// FP8 scales that are NOT powers of two (imported checkpoints; reference: tests/torchrun_fp8.py:235-255) take
+// the PROMOTE form of the kernel: the MMA applies the power-of-two part of every scale as before, each K128
+// block is accumulated into a fresh TMEM buffer, and the epilogue warps add it into FP32 registers times the
+// mantissas of the block's scales -- the per-K128 FP32 promotion of the reference's kernel
+// (src/cuda/fp8/gemm.cuh:68-70) with the exponents already applied.  The quantised bytes are used as they are.
+//
 // Per stage a CTA loads 128 rows x 128 bytes of A, 128 rows x 128 bytes of B (TMA, 128-byte swizzle)
 // and the scale-factor chunks of both (1-D bulk copies of 512 bytes: 128 rows x 4 bytes in the
 // 4 x 32 order that `tcgen05.cp.32x128b.warpx4` expects: word (r%32)*4 + r/32 holds row r).  The MMA
@@ -36,6 +42,7 @@ struct BsConfig {
   static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + 256 + 1024;
   static constexpr uint32_t kTmemSfa = 2 * kBlockN;              // first scale-factor column
   static constexpr uint32_t kTmemSfb = kTmemSfa + 4 * kSfChunks;
+  static constexpr uint32_t kTmemResult = 384;                   // PROMOTE: the finished sums, 128 columns
   static constexpr uint32_t kTmemCols = 512;
 };
 
@@ -43,18 +50,31 @@ struct BsArgs {
   GemmArgs base;   // M-grouped schedule; k_total in ELEMENTS; b_group_rows = N_total
   SfLayout sfa;    // tile = 128-row tile of A (group_stride unused)
   SfLayout sfb;    // group = expert, tile = 128-row tile of that expert's B
+  // PROMOTE only: the FP32 scales themselves, [scale rows][K / 128]; their mantissas are applied per K128
+  // block by the epilogue warps.  a_scales may be null (activations quantised online have power-of-two
+  // scales); one scale row covers a_block_rows (1 or 128) rows of A, and 128 rows of B.
+  const float* a_scales;
+  int a_block_rows;
+  int a_scale_rows;
+  const float* b_scales;
 };
+
+// The factor of an FP32 scale that its biased exponent (the UE8M0 code the MMA applies) leaves out.
+__device__ __forceinline__ float scale_mantissa(float s) {
+  return __uint_as_float((__float_as_uint(s) & 0x007fffffu) | 0x3f800000u);
+}
 
 // K_GROUPED (weight gradients): out[e] = A[:, rows_e]  x  B[:, rows_e]^T with both operands stored
 // K-major over the rank's padded rows (A [M, row_capacity], B [N, row_capacity]); expert e reduces over
 // its own row segment [row0_e, row0_e + rows_e), rows_e a multiple of 128.  An NVFP4 stage spans 256
 // rows: when only 128 remain, half of the stage's MMAs are issued.
-template <int KIND, bool K_GROUPED, class Epilogue>
+template <int KIND, bool K_GROUPED, class Epilogue, bool PROMOTE = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const BsArgs bs, const Epilogue epilogue) {
   using C = BsConfig<KIND>;
   constexpr int kStages = C::kStages;
+  static_assert(!PROMOTE || (KIND == kKindFp8 && !K_GROUPED), "promotion is the FP8 M-grouped form");
   const GemmArgs& args = bs.base;
 
   extern __shared__ uint8_t smem_raw[];
@@ -159,11 +179,18 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           k_groups = (args.k_total + kElemsPerMma - 1) / kElemsPerMma;
         }
         const int k_stages = (k_groups + 3) / 4;
-        ok = mbar_wait(tmem_empty + acc, acc_phase ^ 1, abort_flag, args.status, kStatusTimeoutTmemEmpty);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * C::kBlockN;
+        if constexpr (!PROMOTE) {
+          ok = mbar_wait(tmem_empty + acc, acc_phase ^ 1, abort_flag, args.status, kStatusTimeoutTmemEmpty);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        uint32_t tmem_d = tmem_base + acc * C::kBlockN;
         for (int kb = 0; kb < k_stages; ++kb) {
+          if constexpr (PROMOTE) {  // every K128 block gets a fresh accumulator buffer
+            ok = mbar_wait(tmem_empty + acc, acc_phase ^ 1, abort_flag, args.status, kStatusTimeoutTmemEmpty);
+            if (!ok) break;
+            tmem_d = tmem_base + acc * C::kBlockN;
+          }
           ok = mbar_wait(full_bar + stage, phase, abort_flag, args.status, kStatusTimeoutSmemFull);
           if (!ok) break;
           tc_fence_after();
@@ -182,7 +209,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             if (K_GROUPED && k >= mmas) break;
-            const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
+            const uint32_t accumulate = ((PROMOTE ? 0 : kb) | k) != 0 ? 1u : 0u;
             if constexpr (KIND == kKindFp8) {
               // one chunk per stage: byte k of each row's word is the scale of 32-element group k
               const uint32_t idesc = umma_idesc_block_scaled(0u, 1u, kBlockM, C::kBlockN, k, k);
@@ -197,10 +224,16 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
           umma_commit(empty_bar + stage);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
+          if constexpr (PROMOTE) {
+            umma_commit(tmem_full + acc);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+          }
         }
         if (!ok) break;
-        umma_commit(tmem_full + acc);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        if constexpr (!PROMOTE) {
+          umma_commit(tmem_full + acc);
+          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
       }
     }
   } else {
@@ -211,6 +244,50 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     for (int tile = first_tile + blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
       const TileCoord t = decode_tile<K_GROUPED>(args, tile);
       const int k_stages = (k_groups_of(t) + 3) / 4;
+      if constexpr (PROMOTE) {
+        const uint32_t lanes = static_cast<uint32_t>(q * 32) << 16;
+        const int kblocks = args.k_total / 128;
+        const int a_row = (t.m_tile * kBlockM + q * 32 + lane) / bs.a_block_rows;
+        const float* a_scale = bs.a_scales != nullptr && a_row < bs.a_scale_rows
+                                   ? bs.a_scales + static_cast<size_t>(a_row) * kblocks : nullptr;
+        const float* b_scale = bs.b_scales +
+            (static_cast<size_t>(t.group) * args.b_group_rows / 128 + t.n_tile) * kblocks;
+        float sum[C::kBlockN];
+#pragma unroll
+        for (int j = 0; j < C::kBlockN; ++j) sum[j] = 0.0f;
+        for (int kb = 0; kb < k_stages; ++kb) {
+          ok = mbar_wait(tmem_full + acc, acc_phase, abort_flag, args.status, kStatusTimeoutTmemFull);
+          if (!ok) break;
+          tc_fence_after();
+          const float factor = scale_mantissa(__ldg(b_scale + kb)) *
+                               (a_scale != nullptr ? scale_mantissa(__ldg(a_scale + kb)) : 1.0f);
+#pragma unroll
+          for (int c = 0; c < C::kBlockN / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_base + lanes + acc * C::kBlockN + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sum[c * 32 + j] = fmaf(factor, __uint_as_float(v[j]), sum[c * 32 + j]);
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tmem_empty + acc);
+          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+        if (!ok) break;
+        // The finished sums go back to TMEM (columns no accumulator uses; each warp its own lanes), so that
+        // the epilogues read them exactly as they read an accumulator.
+#pragma unroll
+        for (int c = 0; c < C::kBlockN / 32; ++c) {
+          uint32_t v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[c * 32 + j]);
+          tmem_st_32x32(tmem_base + lanes + C::kTmemResult + c * 32, v);
+        }
+        tmem_st_wait();
+        epilogue(tmem_base + lanes + C::kTmemResult, t, q, lane, k_stages == 0, staging + (warp - 2) * (32 * 256));
+        continue;
+      }
       ok = mbar_wait(tmem_full + acc, acc_phase, abort_flag, args.status, kStatusTimeoutTmemFull);
       if (!ok) break;
       tc_fence_after();
@@ -273,10 +350,10 @@ struct EpilogueBounded {
 
 // Host launcher (needs kernels.h for WM_CUDA / count_launch; include it before this header).
 #ifdef WM_CUDA
-template <int KIND, bool K_GROUPED = false, class Epi>
+template <int KIND, bool K_GROUPED = false, bool PROMOTE = false, class Epi>
 int launch_bs(const CUtensorMap& ta, const CUtensorMap& tb, const BsArgs& args, const Epi& epi, int sms,
               cudaStream_t stream) {
-  auto kernel = gemm_bs_kernel<KIND, K_GROUPED, Epi>;
+  auto kernel = gemm_bs_kernel<KIND, K_GROUPED, Epi, PROMOTE>;
   constexpr int smem = BsConfig<KIND>::kTotal;
   static PerDeviceOnce configured;  // one table per template instantiation
   if (int rc = opt_in_dynamic_smem(kernel, smem, configured)) return rc;

@@ -262,7 +262,7 @@ __global__ void fp8_dequantize_rows_kernel(DeviceRange range, const uint8_t* __r
 template <int KIND>
 int launch_bs_grouped(const Schedule& s, const void* a, const SfLayout& sfa, const void* b, const SfLayout& sfb,
                       __nv_bfloat16* out, const PushTarget* push, int n, int k, float alpha, int* status,
-                      int sms, cudaStream_t stream) {
+                      int sms, cudaStream_t stream, const float* b_scales) {
   const int kbytes = KIND == kKindFp8 ? k : k / 2;
   CUtensorMap ta, tb;
   if (int rc = make_tmap_2d(&ta, a, 1, kbytes, s.row_capacity, kbytes, 128, 128)) return rc;
@@ -278,6 +278,10 @@ int launch_bs_grouped(const Schedule& s, const void* a, const SfLayout& sfa, con
   args.base.status = status;
   args.sfa = sfa;
   args.sfb = sfb;
+  args.a_block_rows = 1;
+  args.b_scales = b_scales;
+  // FP8 weight scales with mantissas: the promotion form of the kernel (gemm_bs.cuh).
+  constexpr bool kCanPromote = KIND == kKindFp8;
   if (push) {
     EpiloguePushScaled<128> epi{};
     for (int r = 0; r < kMaxPeers; ++r) epi.push.mailbox[r] = push->mailbox[r];
@@ -286,9 +290,13 @@ int launch_bs_grouped(const Schedule& s, const void* a, const SfLayout& sfa, con
     epi.push.top_k = push->top_k;
     epi.push.ld = n;
     epi.alpha = alpha;
+    if constexpr (kCanPromote)
+      if (b_scales != nullptr) return launch_bs<KIND, false, true>(ta, tb, args, epi, sms, stream);
     return launch_bs<KIND>(ta, tb, args, epi, sms, stream);
   }
   EpilogueStoreScaled<128> epi{out, n, alpha, 0};
+  if constexpr (kCanPromote)
+    if (b_scales != nullptr) return launch_bs<KIND, false, true>(ta, tb, args, epi, sms, stream);
   return launch_bs<KIND>(ta, tb, args, epi, sms, stream);
 }
 
@@ -435,15 +443,15 @@ int launch_block_scaled_kgrouped(int kind, const Schedule& s, const void* a, con
 
 int launch_block_scaled(int kind, const Schedule& s, const void* a, const SfLayout& sfa, const void* b,
                         const SfLayout& sfb, __nv_bfloat16* out, const PushTarget* push, int n, int k,
-                        float alpha, int* status, int sms, cudaStream_t stream) {
+                        float alpha, int* status, int sms, cudaStream_t stream, const float* b_scales) {
   if (n % 128 || k % (kind == kKindFp8 ? 128 : 256)) {
     set_error("block-scaled grouped GEMM needs N %% 128 == 0 and K %% %d == 0 (N=%d, K=%d)",
               kind == kKindFp8 ? 128 : 256, n, k);
     return 2;
   }
   return kind == kKindFp8
-             ? launch_bs_grouped<kKindFp8>(s, a, sfa, b, sfb, out, push, n, k, alpha, status, sms, stream)
-             : launch_bs_grouped<kKindNvfp4>(s, a, sfa, b, sfb, out, push, n, k, alpha, status, sms, stream);
+             ? launch_bs_grouped<kKindFp8>(s, a, sfa, b, sfb, out, push, n, k, alpha, status, sms, stream, b_scales)
+             : launch_bs_grouped<kKindNvfp4>(s, a, sfa, b, sfb, out, push, n, k, alpha, status, sms, stream, nullptr);
 }
 
 }  // namespace wm

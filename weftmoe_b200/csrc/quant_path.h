@@ -57,9 +57,11 @@ int launch_block_scaled_kgrouped(int kind, const Schedule& s, const void* a, con
 int swiglu_quantize(DeviceRange rows, const __nv_bfloat16* ab, const float* prob, int inter, int kind,
                     float layer_scale, uint8_t* uq, uint32_t* sfa_out, int sms, cudaStream_t stream);
 // out[rows, n] = alpha * A[rows, k] * B[e][n, k]^T with quantised operands; `push` != nullptr sends the
-// rows to the source ranks' mailboxes instead of storing them.
+// rows to the source ranks' mailboxes instead of storing them.  `b_scales` (FP8 only, optional): the FP32
+// 128 x 128 block scales of B, [groups * n / 128][k / 128], when they are not powers of two -- the kernel then
+// promotes every K128 block in FP32 by the scales' mantissas.
 int launch_block_scaled(int kind, const Schedule& s, const void* a, const SfLayout& sfa, const void* b,
                         const SfLayout& sfb, __nv_bfloat16* out, const PushTarget* push, int n, int k,
-                        float alpha, int* status, int sms, cudaStream_t stream);
+                        float alpha, int* status, int sms, cudaStream_t stream, const float* b_scales = nullptr);
 
 }  // namespace wm

@@ -1201,14 +1201,17 @@ extern "C" int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t
                       stage_chunks * chunk, chunk};
   const float alpha1 = kind == kKindFp8 ? 1.0f : weights->x_scale * weights->w1_scale;
   const float alpha2 = kind == kKindFp8 ? 1.0f : weights->u_scale * weights->w2_scale;
+  // FP8 weights whose block scales carry mantissas (imported checkpoints) come with the FP32 scales as well
+  const float* w1_scales = kind == kKindFp8 ? weights->w1_scales : nullptr;
+  const float* w2_scales = kind == kKindFp8 ? weights->w2_scales : nullptr;
   if (int rc = launch_block_scaled(kind, sched, xq, sfa1, weights->w1, sfb1, abq, nullptr, 2 * I, H, alpha1,
-                                   status, rt->sms, stream))
+                                   status, rt->sms, stream, w1_scales))
     return rc;
   if (int rc = swiglu_quantize(split_range(tables.split, 2, kWhole), abq, prob, I, kind,
                                kind == kKindFp8 ? 1.0f : weights->u_scale, uq, sfa_u, rt->sms, stream))
     return rc;
   if (int rc = launch_block_scaled(kind, sched, uq, sfa2, weights->w2, sfb2, nullptr, &push, H, I, alpha2,
-                                   status, rt->sms, stream))
+                                   status, rt->sms, stream, w2_scales))
     return rc;
   if (world > 1) {
     if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;
@@ -1471,7 +1474,7 @@ extern "C" int wm_backward_quantized(wm_runtime* rt, const void* tape, const voi
   const SfLayout sfb_w2t{static_cast<const uint8_t*>(transposed->w2_sf), (1ll * I / 128) * kh * chunk, kh * chunk,
                          chunk, chunk};
   if (int rc = launch_block_scaled(kKindFp8, sched, qrows, sfa_dy, transposed->w2, sfb_w2t, du, nullptr, I, H,
-                                   1.0f, status, rt->sms, stream))
+                                   1.0f, status, rt->sms, stream, transposed->w2_scales))
     return rc;
   if (int rc = fp8_dequantize_rows(all_rows, qrows, sfa_q, H, dy_bf16, rt->sms, stream)) return rc;
   // 4. SwiGLU backward on the saved BF16 gate/up rows: U, dAB, dprob -> sources.
@@ -1485,7 +1488,7 @@ extern "C" int wm_backward_quantized(wm_runtime* rt, const void* tape, const voi
   const SfLayout sfb_w1t{static_cast<const uint8_t*>(transposed->w1_sf), (1ll * H / 128) * ki2 * chunk,
                          ki2 * chunk, chunk, chunk};
   if (int rc = launch_block_scaled(kKindFp8, sched, qrows, sfa_dab, transposed->w1, sfb_w1t, nullptr, &push, H,
-                                   2 * I, 1.0f, status, rt->sms, stream))
+                                   2 * I, 1.0f, status, rt->sms, stream, transposed->w1_scales))
     return rc;
   if (world > 1)
     if (int rc = signal_peers(flag_group(rt, kContrib), world, c.rank, gen, stream)) return rc;

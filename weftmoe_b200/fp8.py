@@ -197,12 +197,15 @@ class PreparedFP8Weights:
     After an optimizer step prepare a NEW object; tapes of earlier forwards keep the object they were
     made with.  Writing into any of the tensors afterwards is detected (`_validate_version`)."""
 
-    __slots__ = ("w1", "w2", "w1_t", "w2_t", "version", "_ready", "_stamps", "_origin", "_wm_chunks",
-                 "_wm_chunks_t", "__weakref__")
+    __slots__ = ("w1", "w2", "w1_t", "w2_t", "version", "scale_mantissas", "_ready", "_stamps", "_origin",
+                 "_wm_chunks", "_wm_chunks_t", "__weakref__")
 
-    def __init__(self, w1, w2, w1_t, w2_t, version, origin=()):
+    def __init__(self, w1, w2, w1_t, w2_t, version, origin=(), scale_mantissas=False):
         self.w1, self.w2, self.w1_t, self.w2_t = w1, w2, w1_t, w2_t
         self.version = version
+        # True: some block scale is not a power of two (an imported checkpoint); the kernels then take
+        # the FP32 scales beside the packed exponents and promote every K128 block in FP32.
+        self.scale_mantissas = bool(scale_mantissas)
         self._origin = tuple(origin)            # _ParameterStamp or None per weight
         self._wm_chunks = self._wm_chunks_t = None   # packed scale chunks, filled lazily by the runtime
         with torch.cuda.device(w1.data.device):
@@ -211,7 +214,7 @@ class PreparedFP8Weights:
         self._stamps = tuple(t._version for t in self.tensors())
 
     def __setattr__(self, name, value):
-        if name in ("w1", "w2", "w1_t", "w2_t", "version") and hasattr(self, "_stamps"):
+        if name in ("w1", "w2", "w1_t", "w2_t", "version", "scale_mantissas") and hasattr(self, "_stamps"):
             raise AttributeError("PreparedFP8Weights is immutable; prepare a new weight version")
         object.__setattr__(self, name, value)
 
@@ -252,26 +255,25 @@ def _import_quantised(weight: FP8Tensor) -> FP8Tensor:
         return FP8Tensor(weight.data.clone(), weight.scales.clone(), tuple(weight.shape), 128)
 
 
-def _check_imported(weights):
-    """Imported bytes must be finite E4M3 and their scales finite, positive powers of two (one host sync).
+def _check_imported(weights) -> bool:
+    """Imported bytes must be finite E4M3 and their scales finite and positive (one host sync).  Returns whether
+    any scale carries a mantissa (is not a power of two).
 
-    The block-scaled tensor-core kernels of this library apply the scales INSIDE the MMA as UE8M0 (power-of-two)
-    factors; a scale with a mantissa, as some checkpoints carry, would need the per-K128 FP32 promotion of the
-    reference's Hopper kernel (src/cuda/fp8/gemm.cuh:68-70), which is not built here.  Such weights are refused
-    rather than silently rounded or quantised again."""
+    The block-scaled tensor-core kernels apply a scale's exponent INSIDE the MMA (UE8M0).  Weights whose
+    scales have mantissas, as some checkpoints carry, are neither rounded nor quantised again: their FP32
+    scales go to the kernels as well, which then promote every K128 block in FP32 by the mantissas (the
+    reference's Hopper kernel promotes by the whole scale, src/cuda/fp8/gemm.cuh:68-70)."""
     if not weights:
-        return
+        return False
     healthy, pow2 = [], []
     for w in weights:
         healthy.append((w.scales > 0).logical_and(torch.isfinite(w.scales)).all())
         healthy.append((w.data.view(torch.uint8).bitwise_and(0x7F) != 0x7F).all())   # 0x7f / 0xff = NaN
         pow2.append((w.scales.view(torch.int32).bitwise_and(0x007FFFFF) == 0).all())  # FP32 mantissa field empty
-    verdict = torch.stack([torch.stack(healthy).all(), torch.stack(pow2).all()]).tolist()
-    if not verdict[0]:
+    findings = torch.stack([torch.stack(healthy).all(), torch.stack(pow2).all()]).tolist()
+    if not findings[0]:
         raise ValueError("FP8 weights must be finite and scales finite and positive")
-    if not verdict[1]:
-        raise ValueError("Imported FP8 block scales must be powers of two: this library scales inside the MMA "
-                         "(UE8M0) and does not re-quantise imported weights")
+    return not findings[1]
 
 
 @torch.inference_mode(False)
@@ -307,9 +309,9 @@ def prepare_fp8_weights(w1, w2, *, training: bool = True, version: int = 0) -> P
     if not consistent:
         raise ValueError("Expected W1 [E,2I,H], W2 [E,H,I], H/I multiples of 128")
     with torch.cuda.device(a.data.device):
-        _check_imported(imported)
+        mantissas = _check_imported(imported)
         if training:
             backward = [qt if qt is not None else transpose_fp8_weight(q) for q, qt in zip(forward, backward)]
         else:
             backward = [None, None]
-        return PreparedFP8Weights(a, b, backward[0], backward[1], version, origin)
+        return PreparedFP8Weights(a, b, backward[0], backward[1], version, origin, mantissas)

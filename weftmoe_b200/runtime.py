@@ -209,9 +209,11 @@ class NativeRuntime:
                 if len(self.tapes) >= self.max_saved:
                     raise RuntimeError("Blackwell training tape capacity exhausted")
                 blob = torch.empty(self.sizes.tape_bytes, dtype=torch.uint8, device=x.device)
-            w1, w1_sf, w2, w2_sf, sx, s1, su, s2 = packed
+            w1, w1_sf, w2, w2_sf, sx, s1, su, s2 = packed[:8]
             weights = _lib.WmQuantWeights(w1=w1.data_ptr(), w1_sf=w1_sf.data_ptr(), w2=w2.data_ptr(),
                                           w2_sf=w2_sf.data_ptr(), x_scale=sx, w1_scale=s1, u_scale=su, w2_scale=s2)
+            if len(packed) > 8:   # FP8 block scales with mantissas: the FP32 scales go along
+                weights.w1_scales, weights.w2_scales = packed[8].data_ptr(), packed[9].data_ptr()
             if source is not None:
                 weights.source_q, weights.source_scales = source.data.data_ptr(), source.scales.data_ptr()
             _lib.check(self.lib.wm_forward_quantized(self.handle, None if source is not None else _lib.ptr(x),
@@ -240,7 +242,10 @@ class NativeRuntime:
                 chunks.append(out)
             cached = tuple(chunks)
             object.__setattr__(weights, "_wm_chunks", cached)
-        return (weights.w1.data, cached[0], weights.w2.data, cached[1], 1.0, 1.0, 1.0, 1.0)
+        packed = (weights.w1.data, cached[0], weights.w2.data, cached[1], 1.0, 1.0, 1.0, 1.0)
+        if getattr(weights, "scale_mantissas", False):
+            packed += (weights.w1.scales, weights.w2.scales)
+        return packed
 
     def _fp8_packed_transposed(self, weights):
         """The same for W1^T / W2^T (backward operands)."""
@@ -290,6 +295,8 @@ class NativeRuntime:
                                      w2_sf=w2t_sf.data_ptr(), x_scale=1.0, w1_scale=1.0, u_scale=1.0, w2_scale=1.0)
         if source is not None:
             packed.source_q, packed.source_scales = source.data.data_ptr(), source.scales.data_ptr()
+        if getattr(weights, "scale_mantissas", False):
+            packed.w1_scales, packed.w2_scales = weights.w1_t.scales.data_ptr(), weights.w2_t.scales.data_ptr()
         _lib.check(self.lib.wm_backward_quantized(self.handle, _lib.ptr(blob),
                                                   None if source is not None else _lib.ptr(dy), ctypes.byref(packed),
                                                   tokens, _lib.ptr(dx), _lib.ptr(dgates), _lib.ptr(dw1),
