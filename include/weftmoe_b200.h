@@ -128,6 +128,10 @@ typedef struct wm_quant_weights {
    * in FP32 by the mantissas (reference: src/cuda/fp8/gemm.cuh:68-70). */
   const float* w1_scales;
   const float* w2_scales;
+  /* wm_backward_quantized, blockwise FP8 only: non-zero = dw1 / dw2 are FP32 buffers and receive the
+   * unrounded FP32 accumulators (FP32 master parameters; reference: weight_grad_dtype of forward_fp8,
+   * weftmoe/runtime.py:303-352); zero = BF16. */
+  int32_t wgrad_f32;
 } wm_quant_weights;
 WM_API int wm_forward_quantized(wm_runtime* rt, const void* x, const int32_t* routes, const float* gates,
                                 const wm_quant_weights* weights, int32_t tokens, void* y, void* tape,

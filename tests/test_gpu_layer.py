@@ -36,6 +36,8 @@ def bits(t):
     dict(experts=16, top_k=4, hidden=768, intermediate=384, tokens=301),     # 128-wide N tiles, ragged T
     dict(experts=32, top_k=8, hidden=2048, intermediate=512, tokens=96),     # mostly idle experts
     dict(experts=4, top_k=1, hidden=256, intermediate=128, tokens=5),
+    dict(experts=512, top_k=32, hidden=256, intermediate=128, tokens=40),    # most experts per rank, largest top-k
+    dict(experts=4, top_k=2, hidden=5120, intermediate=4096, tokens=130),    # hidden > 4096, largest intermediate
 ])
 def test_forward_backward_against_oracle(cfg):
     d = O.make_inputs(cfg, seed=1, bias_std=0.5)

@@ -31,7 +31,7 @@ class WmQuantWeights(Structure):
                 ("x_scale", c_float), ("w1_scale", c_float), ("u_scale", c_float), ("w2_scale", c_float),
                 ("dy_scale", c_float), ("dab_scale", c_float),
                 ("source_q", c_void_p), ("source_scales", c_void_p),
-                ("w1_scales", c_void_p), ("w2_scales", c_void_p)]
+                ("w1_scales", c_void_p), ("w2_scales", c_void_p), ("wgrad_f32", c_int32)]
 
 
 class WmRouteOut(Structure):

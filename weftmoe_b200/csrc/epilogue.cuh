@@ -146,6 +146,54 @@ struct EpilogueStoreTma {
   }
 };
 
+// FP32 store through TMA (weight gradients for FP32 master parameters: the accumulator leaves unrounded).
+// Same scheme as EpilogueStoreTma with 32-column units: a 32 x 32 FP32 box has the same 128-byte rows, so
+// the swizzle and the two alternating 4 KB boxes per warp are unchanged.  `out` is described by a 2-D map
+// over [all rows][ld] FP32 with box {32, 32}.
+template <int BLOCK_N>
+struct EpilogueStoreTmaF32 {
+  alignas(64) CUtensorMap tmap;
+  int rows_per_group;  // K-grouped: M (rows of one expert's output); 0 for M-grouped
+
+  __device__ __forceinline__ void operator()(uint32_t taddr, const TileCoord& t, int q, int lane,
+                                             bool zero, uint8_t* stage) const {
+    const int row0 = t.group * rows_per_group + t.m_tile * kBlockM + q * 32;
+    const int col0 = t.n_tile * BLOCK_N;
+    constexpr int kUnits = BLOCK_N / 32;
+    uint32_t v[32];
+    if (!zero) tmem_ld_32x32(taddr, v);
+#pragma unroll
+    for (int unit = 0; unit < kUnits; ++unit) {
+      uint32_t w[32];
+      if (zero) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) w[j] = 0;
+      } else {
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) w[j] = v[j];
+        if (unit + 1 < kUnits) tmem_ld_32x32(taddr + (unit + 1) * 32, v);
+      }
+      uint8_t* box = stage + (unit & 1) * 4096;
+      if (lane == 0) bulk_wait_group_read<1>();  // the store issued from this box two units ago
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(box + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+            make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(&tmap, box, col0 + unit * 32, row0);
+        bulk_commit_group();
+      }
+    }
+  }
+  __device__ __forceinline__ void finish(int lane) const {
+    if (lane == 0) bulk_wait_group_read<0>();
+  }
+};
+
 // FC1 epilogue (reference: src/cuda/blackwell/fused/impls/routed_bf16.cuh:874-1027):
 // accumulator columns [0,128) are gate, [128,256) are up for intermediate columns
 // n_tile*128 .. +127.  gate and up are rounded to BF16 first (that rounded pair is what the

@@ -108,7 +108,10 @@ static int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, ui
   cuuint64_t strides[1] = {row_stride_bytes};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+  const CUtensorMapDataType type = elem_bytes == 2   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                   : elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                     : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = fn(out, type,
                   2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -368,12 +371,13 @@ int launch_mgrouped_nn(const Schedule& s, const __nv_bfloat16* a, const __nv_bfl
 }
 
 int launch_kgrouped_tn(const Schedule& s, const __nv_bfloat16* a_ptr, const __nv_bfloat16* b_ptr,
-                       __nv_bfloat16* out, int m, int n, int* status, int sms,
-                       cudaStream_t stream) {
+                       void* out_any, int m, int n, int* status, int sms,
+                       cudaStream_t stream, bool out_is_f32) {
   if (m % 128 || n % 128) {
     set_error("K-grouped GEMM needs M %% 128 == 0 and N %% 128 == 0, got %d x %d", m, n);
     return 2;
   }
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(out_any);
   CUtensorMap ta, tb;
   if (int rc = make_tmap_2d(&ta, a_ptr, 2, m, s.row_capacity, (uint64_t)m * 2, 64, 64)) return rc;
   if (int rc = make_tmap_2d(&tb, b_ptr, 2, n, s.row_capacity, (uint64_t)n * 2, 64, 64)) return rc;
@@ -388,6 +392,16 @@ int launch_kgrouped_tn(const Schedule& s, const __nv_bfloat16* a_ptr, const __nv
     a.group_end = experts.end;
   }
   TimelineScope timeline("wgrad", a);
+  if (out_is_f32) {  // FP32 master parameters: the accumulators leave unrounded
+    CUtensorMap map;
+    if (int rc = make_tmap_2d(&map, out_any, 4, n, (uint64_t)s.groups * m, (uint64_t)n * 4, 32, 32)) return rc;
+    if (bn == 256) {
+      EpilogueStoreTmaF32<256> epi{map, m};
+      return launch<256, true, true, false, true>(pair, ta, tb, a, s, epi, sms, stream);
+    }
+    EpilogueStoreTmaF32<128> epi{map, m};
+    return launch<128, true, true, false, true>(pair, ta, tb, a, s, epi, sms, stream);
+  }
   if (bn == 256 && tma_epilogue()) {
     EpilogueStoreTma<256> epi{};
     if (int rc = make_tmap_2d(&epi.tmap, out, 2, n, (uint64_t)s.groups * m, (uint64_t)n * 2, 64, 32)) return rc;

@@ -95,9 +95,10 @@ int launch_du_swiglu_backward(const Schedule& s, const __nv_bfloat16* dy_rows, c
                               const __nv_bfloat16* ab, const float* row_prob, __nv_bfloat16* u,
                               __nv_bfloat16* dab, float* dprob_part, int inter, int hidden, int* status,
                               int sms, cudaStream_t stream);
-// K-grouped: out[e][m, n] = sum over the expert's rows r of a[r, m] * b[r, n].
+// K-grouped: out[e][m, n] = sum over the expert's rows r of a[r, m] * b[r, n]; out is BF16, or FP32
+// (the accumulators unrounded) with out_is_f32.
 int launch_kgrouped_tn(const Schedule& s, const __nv_bfloat16* a, const __nv_bfloat16* b,
-                       __nv_bfloat16* out, int m, int n, int* status, int sms,
-                       cudaStream_t stream);
+                       void* out, int m, int n, int* status, int sms,
+                       cudaStream_t stream, bool out_is_f32 = false);
 
 }  // namespace wm

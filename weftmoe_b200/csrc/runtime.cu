@@ -1500,7 +1500,10 @@ extern "C" int wm_backward_quantized(wm_runtime* rt, const void* tape, const voi
     const char* v = std::getenv("WM_FP8_WGRAD");
     return v && v[0] == '1';
   }();
-  if (fp8_wgrad) {
+  // FP32 gradients (FP32 master parameters) always take the BF16-operand contraction: its accumulators
+  // leave unrounded, where the block-scaled recipe's epilogue writes BF16.
+  const bool wgrad_f32 = transposed->wgrad_f32 != 0;
+  if (fp8_wgrad && !wgrad_f32) {
     uint8_t* qa = at<uint8_t>(S, rt->sl.wq_a);
     uint8_t* qb = at<uint8_t>(S, rt->sl.wq_b);
     auto* sa = at<uint32_t>(S, rt->sl.wsf_a);
@@ -1519,12 +1522,9 @@ extern "C" int wm_backward_quantized(wm_runtime* rt, const void* tape, const voi
                                               I, 1.0f, status, rt->sms, stream))
       return rc;
   } else {
-    if (int rc = launch_kgrouped_tn(sched, dab, x_bf16, static_cast<__nv_bfloat16*>(dw1), 2 * I, H, status,
-                                    rt->sms, stream))
+    if (int rc = launch_kgrouped_tn(sched, dab, x_bf16, dw1, 2 * I, H, status, rt->sms, stream, wgrad_f32))
       return rc;
-    if (int rc = launch_kgrouped_tn(sched, dy_bf16, u, static_cast<__nv_bfloat16*>(dw2), H, I, status, rt->sms,
-                                    stream))
-      return rc;
+    if (int rc = launch_kgrouped_tn(sched, dy_bf16, u, dw2, H, I, status, rt->sms, stream, wgrad_f32)) return rc;
   }
   // 7. source side: ordered combine of dX, dprob back to the original slots.
   if (world > 1)

@@ -289,10 +289,12 @@ class NativeRuntime:
         _, _, hidden, inter = self.shape
         dx = torch.empty(tuple(dy.shape), dtype=torch.bfloat16, device=dy.device)
         dgates = torch.empty((tokens, k), dtype=torch.float32, device=dy.device)
-        dw1 = torch.empty((e, 2 * inter, hidden), dtype=torch.bfloat16, device=dy.device)
-        dw2 = torch.empty((e, hidden, inter), dtype=torch.bfloat16, device=dy.device)
+        wgrad = torch.float32 if fp32_wgrad else torch.bfloat16   # FP32: the accumulators, unrounded
+        dw1 = torch.empty((e, 2 * inter, hidden), dtype=wgrad, device=dy.device)
+        dw2 = torch.empty((e, hidden, inter), dtype=wgrad, device=dy.device)
         packed = _lib.WmQuantWeights(w1=w1t.data_ptr(), w1_sf=w1t_sf.data_ptr(), w2=w2t.data_ptr(),
-                                     w2_sf=w2t_sf.data_ptr(), x_scale=1.0, w1_scale=1.0, u_scale=1.0, w2_scale=1.0)
+                                     w2_sf=w2t_sf.data_ptr(), x_scale=1.0, w1_scale=1.0, u_scale=1.0, w2_scale=1.0,
+                                     wgrad_f32=int(bool(fp32_wgrad)))
         if source is not None:
             packed.source_q, packed.source_scales = source.data.data_ptr(), source.scales.data_ptr()
         if getattr(weights, "scale_mantissas", False):
@@ -303,8 +305,6 @@ class NativeRuntime:
                                                   _lib.ptr(dw2), self.stream.cuda_stream))
         tape.state = None
         self.tapes.discard(tape)
-        if fp32_wgrad:
-            dw1, dw2 = dw1.float(), dw2.float()
         return dx, dgates, dw1, dw2
 
     def inference(self, x, routes, gates, weights, x_scale, intermediate_scale):
