@@ -65,3 +65,29 @@ def test_wait_budget_setter_is_exported_and_restores_its_default():
     lib = _lib.load()
     assert lib.wm_debug_set_wait_budget(1000) == _lib.WM_OK
     assert lib.wm_debug_set_wait_budget(0) == _lib.WM_OK   # back to the default
+
+
+def test_ctypes_structures_match_the_header_layout(tmp_path):
+    """The Python mirrors of the header's structs have the C compiler's sizes and field offsets (gcc on the
+    header itself: a field added on one side only would shift every pointer behind it)."""
+    import ctypes
+    import subprocess
+    structs = {"wm_config": _lib.WmConfig, "wm_sizes": _lib.WmSizes, "wm_quant_weights": _lib.WmQuantWeights,
+               "wm_route_out": _lib.WmRouteOut}
+    header = ROOT / "include" / "weftmoe_b200.h"
+    lines = ["#include <stdio.h>", "#include <stddef.h>", f'#include "{header}"', "int main(void) {"]
+    for name, mirror in structs.items():
+        lines.append(f'  printf("{name} %zu\\n", sizeof({name}));')
+        for field, _ in mirror._fields_:
+            lines.append(f'  printf("{name}.{field} %zu\\n", offsetof({name}, {field}));')
+    lines += ["  return 0;", "}"]
+    source = tmp_path / "layout.c"
+    source.write_text("\n".join(lines))
+    binary = tmp_path / "layout"
+    subprocess.run(["gcc", "-std=c11", "-o", str(binary), str(source)], check=True)
+    found = dict(line.split() for line in subprocess.run([str(binary)], check=True, capture_output=True,
+                                                         text=True).stdout.splitlines())
+    for name, mirror in structs.items():
+        assert int(found[name]) == ctypes.sizeof(mirror), name
+        for field, _ in mirror._fields_:
+            assert int(found[f"{name}.{field}"]) == getattr(mirror, field).offset, (name, field)
