@@ -38,7 +38,10 @@ def main():
     E = max(E, 2 * world)
     e_local = E // world
     # ---- per-rank inputs; rank 1 holds no tokens in the second scenario
-    for scenario, counts in (("ragged", [37 + 11 * r for r in range(world)]),
+    # "mixed planners": rank 0 holds more than 4096 routes and plans with the general kernels, the other
+    # ranks stay below and plan in one launch with the hand-shakes inside; both must speak one protocol
+    for scenario, counts in (("mixed planners", [1200 if r == 0 else 90 + 7 * r for r in range(world)]),
+                             ("ragged", [37 + 11 * r for r in range(world)]),
                              ("zero-token rank", [0 if r == 1 else 20 + r for r in range(world)])):
         g = torch.Generator().manual_seed(1234)
         w1 = (torch.randn(E, 2 * I, H, generator=g) * 0.03).bfloat16()

@@ -21,5 +21,5 @@ def test_expert_parallel_parity(world):
            "--master-addr", "127.0.0.1", "--master-port", str(29700 + world), str(ROOT / "tests" / "ep_worker.py")]
     done = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
-    for scenario in ("overflow reporting passed", "headline shape", "absent rank"):
+    for scenario in ("mixed planners", "overflow reporting passed", "headline shape", "absent rank"):
         assert scenario in done.stdout, scenario

@@ -409,10 +409,12 @@ extern "C" int wm_runtime_create(const wm_config* config, wm_runtime** out) {
     // stream beside the GEMMs of the chunks before it (WM_CHUNKS = 2..8).  Measured at 2 and 4 ranks on the
     // headline shape: 2 chunks 2.20 / 2.43 ms per step, 3 chunks 2.49 ms (4 ranks), 4 chunks 2.35 / 2.57 ms:
     // smaller GEMM launches and more copy kernels beside them cost more than the shorter first pull saves.
-    rt->chunks = 2;
+    // A runtime whose capacity is a small call (at most kSmallPlanRoutes routes per rank: decode) moves too
+    // few rows to gain from the pipeline and takes one chunk: fewer launches and stream hand-offs per call.
+    rt->chunks = 1ll * config->max_tokens * config->top_k <= kSmallPlanRoutes ? 1 : 2;
     if (const char* v = std::getenv("WM_CHUNKS")) {
       const int n = std::atoi(v);
-      if (n >= 2 && n <= kMaxChunks) rt->chunks = n;
+      if (n >= 1 && n <= kMaxChunks) rt->chunks = n;
     }
     // SMs of the push GEMM when it runs beside the next chunk's compute (forward) or beside the chunk's own
     // weight gradients (backward).  Measured on the headline shape with skewed routing: forward at 8 ranks
@@ -745,6 +747,8 @@ extern "C" int wm_forward(wm_runtime* rt, const void* x, const int32_t* routes, 
       StageScope scope(timing, kStageGather, stream);
       if (int rc = pull(kWhole, stream)) return rc;
     }
+    if (world > 1)  // every row of this call has been read from the sources' staging buffers
+      if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
     if (int rc = fc1(kWhole, rt->sms)) return rc;
     if (int rc = fc2(kWhole, rt->sms, stream)) return rc;
   } else {
@@ -947,6 +951,8 @@ extern "C" int wm_backward(wm_runtime* rt, const void* tape, const void* dy, con
       StageScope scope(timing, kStageGatherDy, stream);
       if (int rc = pull(kWhole, stream)) return rc;
     }
+    if (world > 1)
+      if (int rc = signal_peers(flag_group(rt, kPulled), world, c.rank, gen, stream)) return rc;
     if (int rc = du_and_swiglu(kWhole, rt->sms)) return rc;
     if (int rc = dx_push(kWhole, rt->sms, stream)) return rc;
   } else {
