@@ -420,7 +420,9 @@ extern "C" int wm_runtime_create(const wm_config* config, wm_runtime** out) {
     // weight gradients (backward).  Measured on the headline shape with skewed routing: forward at 8 ranks
     // 72 SMs 2.98 ms per step, none 3.08 ms, 48 SMs 3.06 ms; at 2 ranks 48 SMs 2.15 ms against 2.22 ms with
     // none; backward (beside the weight gradients) at 2 / 4 ranks: 48 SMs 2.22 / 2.34 ms, 74 SMs 2.38 / 2.42 ms,
-    // 32 SMs 2.43 ms (2 ranks), 96 SMs 2.63 ms (4 ranks), weight gradients at the end 2.29 / 2.43 ms.
+    // 32 SMs 2.43 ms (2 ranks), 96 SMs 2.63 ms (4 ranks), weight gradients at the end 2.29 / 2.43 ms.  At 8 ranks
+    // with this pipeline: 72 / 48 SMs (forward / backward) 2.60 ms, 48 / 48 2.58 ms, 72 / 72 2.64 ms, no SM split
+    // 2.72 ms, weight gradients at the end 2.88 ms, four chunks 2.77 ms.
     rt->push_sms = config->world == 8 ? 72 : 48;
     rt->push_sms_bwd = 48;
     auto knob = [&](const char* name, int* value) {
